@@ -1,0 +1,314 @@
+"""Benchmark driver: python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
+
+Prints ONE JSON line (rank 0).  A "step" is one pass of the hot path over one
+batch of seeded synthetic input.  `value` is device-timed with inputs resident
+in HBM; `e2e` is the same metric through the C ABI with HOST buffers (pinned
+host memory, host->device and device->host copies inside the timed region).
+`roofline` describes the dominant kernel against the measured HBM peak;
+`cpu_baseline` is the CPU oracle timed on a bounded sample on this box's cores.
+`--impl reference` times the reference's CPU path (restated in oracle/: the
+reference is Rust + Metal and cannot be built here) on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.proc, self.device = None, device
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.device), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- workloads
+class QuantMatvec:
+    """Configs 1 and 2 at batch 1: a fused-dequant matvec over `copies` distinct weight
+    matrices whose total size exceeds L2 twice over, launched back to back from one CUDA graph
+    (the reference's own microbenchmark cycles 35 distinct weight sets so each read is cold,
+    local-metal/src/kernels.rs:8898-8902).  One step = one pass over all copies."""
+
+    def __init__(self, la, ctx, kernels, fmt: str, rows: int, cols: int, m: int = 1):
+        self.la, self.ctx, self.k, self.fmt, self.rows, self.cols, self.m = la, ctx, kernels, fmt, rows, cols, m
+        l2 = ctx.caps()["l2_bytes"]
+        gen = la.synth.q4_0_weights if fmt == "q4_0" else la.synth.tq2_0_weights
+        w0 = gen(rows, cols, seed=1)
+        self.wbytes = w0.size
+        self.copies = max(8, int(np.ceil(2.2 * l2 / self.wbytes)))
+        self.weights = []
+        for c in range(self.copies):
+            w = w0 if c == 0 else np.roll(w0, c * 4099 * (18 if fmt == "q4_0" else 66))  # distinct rows order, same blocks
+            self.weights.append(la.CudaBuffer.from_slice(ctx, w))
+        self.w0 = w0
+        self.x_host = la.synth.normal_f16((m, cols), seed=2)
+        self.x = la.CudaBuffer.from_slice(ctx, self.x_host)
+        self.out = [la.CudaBuffer.empty(ctx, m * rows * 2) for _ in range(self.copies)]
+        self.alg_bytes_per_launch = self.wbytes + m * cols * 2 + m * rows * 2
+        self.units_per_step = self.copies
+        self.name = f"{fmt} fused dequant mat{'vec' if m == 1 else 'mul'} {rows}x{cols} batch {m}"
+        self.graph = None
+        self.launches_per_step = self.copies
+
+    def _enqueue(self, b, c):
+        if self.m == 1:
+            fn = self.k.matvec_q4_0_into if self.fmt == "q4_0" else self.k.matvec_tq2_0_into
+            fn(b, self.weights[c], self.x, self.out[c], self.rows, self.cols)
+        else:
+            fn = self.k.matmul_nt_q4_0_into if self.fmt == "q4_0" else self.k.matmul_nt_tq2_0_into
+            fn(b, self.x, self.weights[c], self.out[c], self.m, self.cols, self.rows)
+
+    def prepare(self):
+        b = self.la.CommandBatch.new(self.ctx)
+        self._enqueue(b, 0)
+        b.commit_and_wait()
+        b = self.la.CommandBatch.capture(self.ctx)
+        for c in range(self.copies):
+            self._enqueue(b, c)
+        self.graph = b.end_capture()
+
+    def step(self):
+        self.graph.launch()
+
+    def check(self, orc):
+        got = self.out[0].as_slice(np.float16).astype(np.float32).reshape(self.m, self.rows)
+        f = orc.Q4_0 if self.fmt == "q4_0" else orc.TQ2_0
+        want = orc.matmul_nt(f, self.x_host, self.w0, self.m, self.cols, self.rows)
+        assert np.all(np.abs(got - want) <= 1e-3 * np.maximum(np.abs(want), 1.0)), "bench output differs from the oracle"
+
+    # end to end through the C ABI with host buffers: upload x, run, download y, per copy
+    def prepare_e2e(self):
+        self.hx = self.la.PinnedHost(self.m * self.cols * 2)
+        self.hy = self.la.PinnedHost(self.m * self.rows * 2)
+        self.hx.array[:] = self.x_host.view(np.uint8).reshape(-1)
+        self.h2d, self.d2h = self.m * self.cols * 2 * self.copies, self.m * self.rows * 2 * self.copies
+
+    def step_e2e(self):
+        b = self.la.CommandBatch.new(self.ctx)
+        for c in range(self.copies):
+            b.upload(self.x, 0, self.hx.ptr, self.hx.nbytes)
+            self._enqueue(b, c)
+            b.download(self.out[c], 0, self.hy.ptr, self.hy.nbytes)
+        b.commit_and_wait()
+
+    def metric(self):
+        return "fused_quant_matvec_hbm_gbs", "GB/s"
+
+    def value(self, ms_per_step: float) -> float:
+        return self.alg_bytes_per_launch * self.units_per_step / (ms_per_step * 1e-3) / 1e9
+
+    def cpu_sample(self, orc, threads: int):
+        """One matrix (all rows) on the CPU: returns (seconds, GB/s-equivalent, description)."""
+        f = orc.Q4_0 if self.fmt == "q4_0" else orc.TQ2_0
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            orc.baseline_matmul_nt(f, self.x_host, self.w0, self.m, self.cols, self.rows, threads)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > 3.0 or reps >= 200:
+                break
+        return dt / reps, self.alg_bytes_per_launch / (dt / reps) / 1e9, f"{reps} passes over one {self.rows}x{self.cols} matrix"
+
+
+WORKLOADS = {
+    "matvec_tq2_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 1),
+    "matvec_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 6144, 1536, 1),
+    "matmul_tq2_0_m16": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 16),
+    "matmul_tq2_0_m64": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 64),
+    "matvec_vocab_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 262144, 1536, 1),
+}
+DEFAULT_WORKLOAD = "matvec_tq2_0"
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference's CPU path for this workload on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    orc = entry.load_oracle()
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("la_synth", ROOT / "local-ai_b200" / "synth.py")
+    synth = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(synth)
+    name = args.workload
+    shapes = {"matvec_tq2_0": ("tq2_0", 8192, 1536, 1), "matvec_q4_0": ("q4_0", 6144, 1536, 1),
+              "matmul_tq2_0_m16": ("tq2_0", 8192, 1536, 16), "matmul_tq2_0_m64": ("tq2_0", 8192, 1536, 64),
+              "matvec_vocab_q4_0": ("q4_0", 262144, 1536, 1)}
+    fmt, rows, cols, m = shapes[name]
+    w = (synth.q4_0_weights if fmt == "q4_0" else synth.tq2_0_weights)(rows, cols, seed=1)
+    x = synth.normal_f16((m, cols), seed=2)
+    f = orc.Q4_0 if fmt == "q4_0" else orc.TQ2_0
+    alg = w.size + m * cols * 2 + m * rows * 2
+    threads = orc.num_threads()
+    for _ in range(args.warmup):
+        orc.baseline_matmul_nt(f, x, w, m, cols, rows, 0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.baseline_matmul_nt(f, x, w, m, cols, rows, 0)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = alg / dt / 1e9
+    sample = f"each step = one {rows}x{cols} {fmt} matrix (dequant to f16 + naive f32 dot), {threads} OpenMP threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_quant_matvec_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "note": "CPU restatement of the reference's qat_recover dequant + test-checker dot; "
+                   "the reference's Metal path is unavailable on this box"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, local_rank, world = dist_env()
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    la = entry.load_package()
+    ctx = la.CudaContext.new(local_rank)
+    kernels = la.Kernels.new(ctx)
+    wl = WORKLOADS[args.workload](la, ctx, kernels)
+    wl.prepare()
+    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
+
+    def barrier():
+        ctx.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def timed(step_fn, steps: int, warmup: int) -> float:
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step_fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(wl.step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    wl.prepare_e2e()
+    ms_e2e = timed(wl.step_e2e, max(3, args.steps // 4), 3)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    orc = entry.load_oracle()
+    wl.check(orc)
+    peak, peak_kind = measured_peaks()
+    metric, unit = wl.metric()
+    value = wl.value(ms) * world
+    launch_ms = ms / wl.launches_per_step
+    achieved = wl.alg_bytes_per_launch / (launch_ms * 1e-3) / 1e9
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": wl.name, "copies": wl.copies, "l2_policy": "inputs larger than L2 "
+                   f"({wl.copies} distinct weight copies, {wl.copies * wl.wbytes / 1e6:.0f} MB per pass)",
+                   "launch": "one CUDA graph per step", "replicas": world},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "qgemv_kernel",
+                     "frac_of_nominal_8tbs": achieved / 8000.0},
+        "e2e": {"value": wl.value(ms_e2e) * world, "unit": unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
+        "gpu_launches": wl.launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        threads = orc.num_threads()
+        sec, gbs, desc = wl.cpu_sample(orc, 0)
+        line["cpu_baseline"] = {"value": gbs, "unit": unit, "cores": threads, "kind": "port",
+                                "sample": desc + f"; {sec * 1e3:.2f} ms per matrix"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,337 @@
+/*
+ * local_cuda.h — C ABI of the B200 (sm_100a) backend for local-ai's decode hot path.
+ *
+ * Every entry point replaces one item of the reference's `local-metal` crate
+ * (the kernel-dispatch layer local-engine's forward pass calls).  The citation
+ * after each declaration is the reference interface it stands in for, as
+ * file:line relative to the reference project root.  Argument order and meaning
+ * follow the Rust method of the same name; buffers are opaque handles
+ * (`MetalBuffer` -> `lc_buf`), scalars are uint32_t / float, the result is an
+ * `lc_status` (`local_metal::Error` -> integer code + `lc_last_error()` text).
+ *
+ * Conventions
+ *  - `*_into` entry points enqueue onto the batch's stream and return at once
+ *    (the reference encodes into a `CommandBatch`); the same name without
+ *    `_into` takes the context, runs and waits (the reference's `ctx` variants).
+ *  - All device work of one context is issued in call order on one stream, the
+ *    serial-encoder semantics of batch.rs:59-66.
+ *  - Buffers must outlive the batch / graph that references them.
+ *  - Handles are not thread-safe; use one context per host thread, one per GPU.
+ *  - There is no CPU fallback: every compute entry point launches a CUDA kernel
+ *    or fails with a status.
+ */
+#ifndef LOCAL_CUDA_H
+#define LOCAL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LC_API __attribute__((visibility("default")))
+
+/* local-metal/src/error.rs:2-32 (+ CUDA / NCCL / TIMEOUT, which have no Metal twin) */
+typedef enum lc_status {
+    LC_OK = 0,
+    LC_ERR_NO_DEVICE = 1,          /* NoMetalDevice / NoDevice */
+    LC_ERR_NO_COMMAND_QUEUE = 2,   /* NoCommandQueue */
+    LC_ERR_BUFFER_ALLOCATION = 3,  /* BufferAllocation{size,reason} */
+    LC_ERR_LIBRARY_CREATION = 4,   /* LibraryCreation */
+    LC_ERR_PIPELINE_CREATION = 5,  /* PipelineCreation */
+    LC_ERR_SHADER_NOT_FOUND = 6,   /* ShaderNotFound */
+    LC_ERR_COMMAND_BUFFER = 7,     /* CommandBuffer */
+    LC_ERR_INVALID_ARGUMENT = 8,   /* InvalidArgument */
+    LC_ERR_IO = 9,                 /* Io */
+    LC_ERR_CUDA = 10,
+    LC_ERR_NCCL = 11,
+    LC_ERR_TIMEOUT = 12
+} lc_status;
+
+typedef struct lc_ctx lc_ctx;         /* MetalContext    local-metal/src/context.rs:31-101 */
+typedef struct lc_buf lc_buf;         /* MetalBuffer     local-metal/src/buffer.rs:17-144 */
+typedef struct lc_batch lc_batch;     /* CommandBatch    local-metal/src/batch.rs:147-292 */
+typedef struct lc_pending lc_pending; /* PendingCommandBuffer  batch.rs:120-145 */
+typedef struct lc_graph lc_graph;     /* no twin: a captured batch that can be replayed */
+typedef struct lc_kernels lc_kernels; /* Kernels         local-metal/src/kernels.rs:18-219 */
+
+/* Text of the last failure on the calling thread ("" if none). */
+LC_API const char *lc_last_error(void);
+LC_API const char *lc_status_name(int status);
+/* Build identification: "local-cuda <ver> sm_100a". */
+LC_API const char *lc_version(void);
+
+/* ------------------------------------------------------------- context -- */
+/* MetalContext::new (context.rs:37-62). `device` is the CUDA ordinal. */
+LC_API int lc_ctx_create(int device, lc_ctx **out);
+LC_API void lc_ctx_destroy(lc_ctx *ctx);
+/* MetalContext::caps (context.rs:70-90): SM count, opt-in shared memory per
+ * CTA, L2 bytes, total device memory. Any out pointer may be NULL. */
+LC_API int lc_ctx_caps(const lc_ctx *ctx, int *sm_count, size_t *smem_per_cta,
+                       size_t *l2_bytes, size_t *total_mem);
+/* The context's stream as a cudaStream_t, for callers that time with events. */
+LC_API void *lc_ctx_stream(const lc_ctx *ctx);
+LC_API int lc_ctx_synchronize(lc_ctx *ctx);
+
+/* -------------------------------------------------------------- buffer -- */
+/* MetalBuffer::empty (buffer.rs:45-62): zero-filled device allocation. */
+LC_API int lc_buf_alloc(lc_ctx *ctx, size_t bytes, lc_buf **out);
+/* MetalBuffer::from_slice (buffer.rs:21-43): allocate + copy from host. */
+LC_API int lc_buf_from_host(lc_ctx *ctx, const void *src, size_t bytes, lc_buf **out);
+/* Wrap device memory the caller owns (never freed by the library). */
+LC_API int lc_buf_wrap(lc_ctx *ctx, void *device_ptr, size_t bytes, lc_buf **out);
+LC_API void lc_buf_free(lc_buf *buf);
+LC_API size_t lc_buf_length(const lc_buf *buf);   /* MetalBuffer::length buffer.rs:64-67 */
+LC_API void *lc_buf_device_ptr(const lc_buf *buf); /* MetalBuffer::raw    buffer.rs:139-143 */
+/* MetalBuffer::copy_from_bytes (buffer.rs:112-131); out of range -> status, not a panic. */
+LC_API int lc_buf_upload(lc_buf *buf, size_t offset, const void *src, size_t bytes);
+/* MetalBuffer::as_slice (buffer.rs:78-94): the CPU read of GPU results. */
+LC_API int lc_buf_download(const lc_buf *buf, size_t offset, void *dst, size_t bytes);
+/* Zero a byte range (the containers' reset paths, kv_cache/quant_cache.rs:364-380). */
+LC_API int lc_buf_zero(lc_buf *buf, size_t offset, size_t bytes);
+
+/* --------------------------------------------------------------- batch -- */
+LC_API int lc_batch_begin(lc_ctx *ctx, lc_batch **out);           /* CommandBatch::new batch.rs:160-172 */
+LC_API uint32_t lc_batch_dispatch_count(const lc_batch *batch);   /* batch.rs:174-182 */
+/* CommandBatch::blit_buffer_copies (batch.rs:196-226), one copy per call. */
+LC_API int lc_batch_copy(lc_batch *batch, const lc_buf *src, size_t src_off, lc_buf *dst,
+                         size_t dst_off, size_t bytes);
+/* Async host<->device copies in batch order (host memory should be pinned). */
+LC_API int lc_batch_upload(lc_batch *batch, lc_buf *dst, size_t dst_off, const void *src,
+                           size_t bytes);
+LC_API int lc_batch_download(lc_batch *batch, const lc_buf *src, size_t src_off, void *dst,
+                             size_t bytes);
+LC_API int lc_batch_commit_and_wait(lc_batch *batch);             /* batch.rs:258-272; frees batch */
+LC_API int lc_batch_commit_async(lc_batch *batch, lc_pending **out); /* batch.rs:274-291; frees batch */
+LC_API int lc_pending_wait(lc_pending *pending);                  /* batch.rs:126-144; frees pending */
+/* Record everything enqueued between begin_capture and end_capture into a CUDA
+ * graph instead of running it; lc_graph_launch replays it on the context's
+ * stream (the reference re-encodes every token; a graph removes that cost). */
+LC_API int lc_batch_begin_capture(lc_ctx *ctx, lc_batch **out);
+LC_API int lc_batch_end_capture(lc_batch *batch, lc_graph **out); /* frees batch */
+LC_API int lc_graph_launch(lc_graph *graph);
+LC_API void lc_graph_destroy(lc_graph *graph);
+/* Pinned host memory for lc_batch_upload / lc_batch_download. */
+LC_API int lc_host_alloc(size_t bytes, void **out);
+LC_API void lc_host_free(void *ptr);
+
+/* ------------------------------------------------------------- kernels -- */
+/* Kernels::new (kernels.rs:116-219). Reads the routing switches LOCAL_AI_BATCHM,
+ * LOCAL_AI_SMALLM, LOCAL_AI_MMA once (kernels.rs:6277-6304). */
+LC_API int lc_kernels_create(lc_ctx *ctx, lc_kernels **out);
+LC_API void lc_kernels_destroy(lc_kernels *k);
+
+/* Quantized matvec: output[rows] = matrix[rows, cols] x vector[cols], f16 input,
+ * f32 accumulate.  matrix holds verbatim GGUF blocks (Q4_0: 18 B / 32 weights,
+ * cols % 32 == 0; TQ2_0: 66 B / 256 weights, cols % 256 == 0), else
+ * LC_ERR_INVALID_ARGUMENT. */
+LC_API int lc_matvec_q4_0(lc_kernels *k, lc_ctx *ctx, const lc_buf *matrix, const lc_buf *vector,
+                          lc_buf *output, uint32_t rows, uint32_t cols);           /* kernels.rs:5711 */
+LC_API int lc_matvec_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *matrix,
+                               const lc_buf *vector, lc_buf *output, uint32_t rows,
+                               uint32_t cols);                                      /* kernels.rs:5744 */
+LC_API int lc_matvec_q4_0_f32out(lc_kernels *k, lc_ctx *ctx, const lc_buf *matrix,
+                                 const lc_buf *vector, lc_buf *output, uint32_t rows,
+                                 uint32_t cols);                                    /* kernels.rs:5778 */
+LC_API int lc_matvec_q4_0_f32out_into(lc_kernels *k, lc_batch *b, const lc_buf *matrix,
+                                      const lc_buf *vector, lc_buf *output, uint32_t rows,
+                                      uint32_t cols);                               /* kernels.rs:5811 */
+LC_API int lc_matvec_tq2_0(lc_kernels *k, lc_ctx *ctx, const lc_buf *matrix, const lc_buf *vector,
+                           lc_buf *output, uint32_t rows, uint32_t cols);          /* kernels.rs:5848 */
+LC_API int lc_matvec_tq2_0_into(lc_kernels *k, lc_batch *b, const lc_buf *matrix,
+                                const lc_buf *vector, lc_buf *output, uint32_t rows,
+                                uint32_t cols);                                     /* kernels.rs:5881 */
+LC_API int lc_matvec_tq2_0_f32out(lc_kernels *k, lc_ctx *ctx, const lc_buf *matrix,
+                                  const lc_buf *vector, lc_buf *output, uint32_t rows,
+                                  uint32_t cols);                                   /* kernels.rs:5978 */
+LC_API int lc_matvec_tq2_0_f32out_into(lc_kernels *k, lc_batch *b, const lc_buf *matrix,
+                                       const lc_buf *vector, lc_buf *output, uint32_t rows,
+                                       uint32_t cols);                              /* kernels.rs:6011 */
+/* SoA TQ2_0: qs = rows*blocks*64 bytes, scales = rows*blocks f16. */
+LC_API int lc_matvec_tq2_0_soa_into(lc_kernels *k, lc_batch *b, const lc_buf *qs,
+                                    const lc_buf *scales, const lc_buf *vector, lc_buf *output,
+                                    uint32_t rows, uint32_t cols);                  /* kernels.rs:5919 */
+
+/* Quantized batched matmul: output[m, n] (f16) = input[m, k] (f16) x weight[n, k]^T.
+ * Routing by m follows kernels.rs:6459-6563 (register-resident small-M path,
+ * then the tensor-core path). */
+LC_API int lc_matmul_nt_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                  const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk,
+                                  uint32_t n);                                      /* kernels.rs:6459 */
+LC_API int lc_matmul_nt_tq2_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                   const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk,
+                                   uint32_t n);                                     /* kernels.rs:6509 */
+/* 1 <= m <= 16, one pass over the weights for all m rows. */
+LC_API int lc_multivec_nt_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                    const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk,
+                                    uint32_t n);                                    /* kernels.rs:6378 */
+LC_API int lc_multivec_nt_tq2_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                     const lc_buf *weight, lc_buf *output, uint32_t m,
+                                     uint32_t kk, uint32_t n);                      /* kernels.rs:6419 */
+/* Same contraction with f32 output: the vocabulary projection of n_lanes rows
+ * in ONE pass over the table.  The reference issues one matvec_q4_0_f32out per
+ * lane (pipeline/batched.rs:427-447), re-reading the table n_lanes times. */
+LC_API int lc_matmul_nt_q4_0_f32out_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                         const lc_buf *weight, lc_buf *output, uint32_t m,
+                                         uint32_t kk, uint32_t n);
+
+/* out[i] = scales[i/4] * ((packed[i/4] >> 2(i%4)) & 3), f16.  The reference
+ * launches a single threadgroup of <= 256 threads whatever num_elements is
+ * (kernels.rs:6788-6797); this entry point covers all num_elements. */
+LC_API int lc_tq2_dequant(lc_kernels *k, lc_ctx *ctx, const lc_buf *packed, const lc_buf *scales,
+                          lc_buf *output, uint32_t num_elements);                   /* kernels.rs:6753 */
+
+/* ---------------------------------------------------------- TurboQuant -- */
+/* Host-side codec set-up, what TurboQuant::new computes on the CPU
+ * (local-engine/src/turboquant.rs:187-199): the caller uploads the results as
+ * the `levels` / `signs` buffers below. */
+LC_API size_t lc_tq_code_bytes(uint32_t head_dim, uint32_t bits);          /* turboquant.rs:203-205 */
+LC_API int lc_tq_signs(uint32_t dim, uint64_t seed, float *signs);         /* turboquant.rs:66-80 */
+LC_API int lc_tq_levels(uint32_t dim, uint32_t bits, float *levels);       /* turboquant.rs:114-166,187-192 */
+LC_API size_t lc_swa_ring_capacity(size_t window, size_t max_positions);   /* kv_cache/quant_cache.rs:48-54 */
+LC_API uint32_t lc_kv_bits_from_env(void);                                 /* kv_cache/quant_cache.rs:60-66 */
+#define LC_TQ_SEED 0x7459C0DEull                                           /* kv_cache/quant_cache.rs:30 */
+/* Summation order of the row norm in the encode kernels: 0 (default) = the Rust
+ * codec's sequential order, bit-exact with TurboQuant::encode_into
+ * (turboquant.rs:241-276); 1 = the Metal kernel's pairwise tree
+ * (shaders/dequantize_kv.metal:247-257).  Also read once from LOCAL_CUDA_TQ_NORM=tree. */
+LC_API int lc_kernels_set_kv_norm_mode(lc_kernels *k, int mode);
+
+/* input f16 [num_tokens, n_kv_heads, head_dim] -> packed codes + f16 norms at slot
+ * ((position + tok) % ring) * n_kv + head, or (position + tok) * n_kv + head when ring == 0. */
+LC_API int lc_encode_kv_turboquant_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                        const lc_buf *levels, const lc_buf *signs, lc_buf *packed,
+                                        lc_buf *norms, uint32_t head_dim, uint32_t n_kv_heads,
+                                        uint32_t num_tokens, uint32_t bits, uint32_t position,
+                                        uint32_t ring_capacity);                    /* kernels.rs:4819 */
+LC_API int lc_encode_kv_turboquant(lc_kernels *k, lc_ctx *ctx, const lc_buf *input,
+                                   const lc_buf *levels, const lc_buf *signs, lc_buf *packed,
+                                   lc_buf *norms, uint32_t head_dim, uint32_t n_kv_heads,
+                                   uint32_t num_tokens, uint32_t bits, uint32_t position,
+                                   uint32_t ring_capacity);                         /* kernels.rs:4988 */
+/* One new row per lane: slot (lane * lane_capacity + positions[lane] % ring) * n_kv + head. */
+LC_API int lc_encode_kv_turboquant_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                                const lc_buf *levels, const lc_buf *signs,
+                                                lc_buf *packed, lc_buf *norms, const lc_buf *positions,
+                                                uint32_t head_dim, uint32_t n_kv_heads,
+                                                uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes,
+                                                uint32_t ring_capacity);            /* kernels.rs:4901 */
+LC_API int lc_dequantize_kv_turboquant_into(lc_kernels *k, lc_batch *b, const lc_buf *packed,
+                                            const lc_buf *norms, const lc_buf *levels,
+                                            const lc_buf *signs, lc_buf *output, uint32_t head_dim,
+                                            uint32_t n_kv_heads, uint32_t num_tokens, uint32_t bits,
+                                            uint32_t token_start, uint32_t ring_capacity); /* kernels.rs:4732 */
+LC_API int lc_dequantize_kv_turboquant(lc_kernels *k, lc_ctx *ctx, const lc_buf *packed,
+                                       const lc_buf *norms, const lc_buf *levels, const lc_buf *signs,
+                                       lc_buf *output, uint32_t head_dim, uint32_t n_kv_heads,
+                                       uint32_t num_tokens, uint32_t bits, uint32_t token_start,
+                                       uint32_t ring_capacity);                     /* kernels.rs:4641 */
+/* y = (1/sqrt d) H(pre_sign ? s*x : x), then * s when post_sign; f32->f32, f16->f32, f32->f16. */
+LC_API int lc_hadamard_rotate_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *signs,
+                                   lc_buf *output, uint32_t head_dim, uint32_t num_heads,
+                                   uint32_t pre_sign, uint32_t post_sign);          /* kernels.rs:5032 */
+LC_API int lc_hadamard_rotate_hf_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                      const lc_buf *signs, lc_buf *output, uint32_t head_dim,
+                                      uint32_t num_heads, uint32_t pre_sign, uint32_t post_sign); /* kernels.rs:5060 */
+LC_API int lc_hadamard_rotate_fh_into(lc_kernels *k, lc_batch *b, const lc_buf *input,
+                                      const lc_buf *signs, lc_buf *output, uint32_t head_dim,
+                                      uint32_t num_heads, uint32_t pre_sign, uint32_t post_sign); /* kernels.rs:5088 */
+
+/* ------------------------------------------------- attention over codes -- */
+/* Decode attention of one query position over packed TurboQuant rows.
+ * rq = rotated query f32 [n_q, hd]; out = rotated-space accumulation f32 [n_q, hd].
+ * Same arguments as the reference plus a trailing softmax_scale (the reference
+ * hard-codes 1.0: attention_flash_tq.metal has no scale); pass 1.0f for the
+ * reference's behaviour.  Split-K partials live in scratch owned by `k`. */
+LC_API int lc_flash_attention_tq_into(lc_kernels *k, lc_batch *b, const lc_buf *rq,
+                                      const lc_buf *k_codes, const lc_buf *k_norms,
+                                      const lc_buf *v_codes, const lc_buf *v_norms, const lc_buf *levels,
+                                      lc_buf *out, uint32_t head_dim, uint32_t kv_len,
+                                      uint32_t current_pos, uint32_t num_q_heads, uint32_t num_kv_heads,
+                                      uint32_t window, uint32_t bits, uint32_t ring_capacity,
+                                      float softmax_scale);                         /* kernels.rs:5176 */
+/* Per-lane form over a unified pool [n_lanes, lane_capacity, n_kv, code_bytes]. */
+LC_API int lc_flash_attention_tq_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *rq,
+                                              const lc_buf *k_codes, const lc_buf *k_norms,
+                                              const lc_buf *v_codes, const lc_buf *v_norms,
+                                              const lc_buf *levels, lc_buf *out, const lc_buf *positions,
+                                              uint32_t head_dim, uint32_t lane_capacity,
+                                              uint32_t num_q_heads, uint32_t num_kv_heads, uint32_t window,
+                                              uint32_t bits, uint32_t n_lanes, uint32_t ring_capacity,
+                                              float softmax_scale);                 /* kernels.rs:5434 */
+/* Fused rotate -> attend -> inverse-rotate: q f16 [n_q, hd] in, attn_out f16 out.
+ * One call for the three dispatches QuantizedKvCache::fused_attention_into
+ * always issues together (kv_cache/quant_cache.rs:548-598). */
+LC_API int lc_tq_attention_into(lc_kernels *k, lc_batch *b, const lc_buf *q, const lc_buf *k_codes,
+                                const lc_buf *k_norms, const lc_buf *v_codes, const lc_buf *v_norms,
+                                const lc_buf *levels, const lc_buf *signs, lc_buf *attn_out,
+                                uint32_t head_dim, uint32_t kv_len, uint32_t current_pos,
+                                uint32_t num_q_heads, uint32_t num_kv_heads, uint32_t window, uint32_t bits,
+                                uint32_t ring_capacity, float softmax_scale);
+/* The same for QuantizedUnifiedKvPool::attention_into (kv_cache/quant_unified_pool.rs:194-258). */
+LC_API int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *q,
+                                        const lc_buf *k_codes, const lc_buf *k_norms,
+                                        const lc_buf *v_codes, const lc_buf *v_norms, const lc_buf *levels,
+                                        const lc_buf *signs, lc_buf *attn_out, const lc_buf *positions,
+                                        uint32_t head_dim, uint32_t lane_capacity, uint32_t num_q_heads,
+                                        uint32_t num_kv_heads, uint32_t window, uint32_t bits,
+                                        uint32_t n_lanes, uint32_t ring_capacity, float softmax_scale);
+
+/* ---------------------------------------------------- FP16-KV attention -- */
+/* K/V f16 [kv_len, n_kv, hd]; q, output f16 [n_q, hd]; softmax scale 1.0 as in the shaders. */
+LC_API uint32_t lc_flash_split_count(const lc_kernels *k, uint32_t eff_seq_len);    /* kernels.rs:1265 */
+LC_API int lc_flash_attention_windowed_split_into(lc_kernels *k, lc_batch *b, const lc_buf *q,
+                                                  const lc_buf *kk, const lc_buf *v, lc_buf *output,
+                                                  lc_buf *partial_max, lc_buf *partial_sum,
+                                                  lc_buf *partial_acc, uint32_t head_dim, uint32_t kv_len,
+                                                  uint32_t current_pos, uint32_t num_q_heads,
+                                                  uint32_t num_kv_heads, uint32_t window,
+                                                  uint32_t num_splits);             /* kernels.rs:1292 */
+LC_API int lc_flash_decoding_into(lc_kernels *k, lc_ctx *ctx, lc_batch *b, const lc_buf *q,
+                                  const lc_buf *kk, const lc_buf *v, lc_buf *output, uint32_t head_dim,
+                                  uint32_t kv_len, uint32_t current_pos, uint32_t num_q_heads,
+                                  uint32_t num_kv_heads);                           /* kernels.rs:1397 */
+LC_API int lc_attention_sliding(lc_kernels *k, lc_ctx *ctx, const lc_buf *q, const lc_buf *kk,
+                                const lc_buf *v, lc_buf *output, uint32_t head_dim, uint32_t kv_len,
+                                uint32_t current_pos, uint32_t window, uint32_t num_q_heads,
+                                uint32_t num_kv_heads);                             /* kernels.rs:691 */
+
+/* ------------------------------------------------------ per-layer small ops -- */
+LC_API int lc_rms_norm_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                            lc_buf *output, uint32_t dim, uint32_t rows, float eps); /* kernels.rs:2142 */
+LC_API int lc_rms_norm_add_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                                const lc_buf *residual, lc_buf *output, uint32_t dim, uint32_t rows,
+                                float eps);                                         /* kernels.rs:6663 */
+LC_API int lc_qk_norm_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *qk_data, const lc_buf *weight,
+                               uint32_t head_dim, uint32_t num_heads, float eps);   /* kernels.rs:2215 */
+LC_API int lc_rope_into(lc_kernels *k, lc_batch *b, const lc_buf *input, lc_buf *output,
+                        uint32_t head_dim, uint32_t position, float theta, float partial_rotary_factor,
+                        uint32_t num_heads);                                        /* kernels.rs:509 */
+LC_API int lc_rope_batch_decode_into(lc_kernels *k, lc_batch *b, lc_buf *qk, const lc_buf *positions,
+                                     float theta, uint32_t head_dim, uint32_t num_heads, uint32_t seq_len,
+                                     float partial_rotary_factor);                  /* kernels.rs:4311 */
+LC_API int lc_gelu_mul_into(lc_kernels *k, lc_batch *b, const lc_buf *a, const lc_buf *bb, lc_buf *out,
+                            uint32_t count);                                        /* kernels.rs:6648 */
+LC_API int lc_residual_add_into(lc_kernels *k, lc_batch *b, const lc_buf *a, const lc_buf *bb,
+                                lc_buf *output, uint32_t count);                    /* kernels.rs:2592 */
+LC_API int lc_scale_in_place_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, float scalar,
+                                      uint32_t count);                              /* kernels.rs:2845 */
+LC_API int lc_logit_softcap_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, float cap,
+                                     uint32_t count);                               /* kernels.rs:2749 */
+LC_API int lc_gather_strided_f16_into(lc_kernels *k, lc_batch *b, const lc_buf *src, lc_buf *dst,
+                                      uint32_t row_stride, uint32_t base_off, uint32_t pld,
+                                      uint32_t n_rows);                             /* kernels.rs:2801 */
+/* Device-side stand-ins for two CPU steps the reference performs through unified
+ * memory: the embedding-row gather (QuantWeight::dequant_row, local-engine/src/layer.rs:255-281,
+ * followed by scale_in_place) and greedy first-max argmax (sampler.rs:148-158). */
+LC_API int lc_embed_rows_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *table, const lc_buf *tokens,
+                                   lc_buf *output, uint32_t n_rows, uint32_t cols, uint32_t vocab,
+                                   float scale);
+LC_API int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc_buf *out_index,
+                                   uint32_t rows, uint32_t cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOCAL_CUDA_H */

@@ -1,0 +1,325 @@
+// The small per-layer ops of a decode step.  Stand in for shaders/rms_norm.metal
+// (:4-88), qk_norm.metal (:6-55), rope.metal (:14-53, :157-196), gelu.metal
+// (:23-37), residual_add.metal, scale_in_place.metal (scale, gather_strided_f16,
+// logit_softcap_f32), plus two device-side replacements for work the reference
+// does on the CPU through unified memory: the embedding-row gather
+// (local-engine/src/layer.rs:255-281) and greedy argmax (sampler.rs:148-158).
+// All activations are f16 with f32 internals; every kernel rounds once on store.
+#include <math.h>
+
+#include "lc_internal.h"
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float *sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < (unsigned)nw) ? sh[threadIdx.x] : 0.f;
+    if (warp == 0) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) sh[0] = t;
+    }
+    __syncthreads();
+    const float r = sh[0];
+    __syncthreads();
+    return r;
+}
+
+// out[row] = x * rsqrt(mean(x^2) + eps) * w (+ residual). One CTA per row.
+// In-place (out == in) is allowed: each thread reads its elements before writing them.
+__global__ void rms_norm_kernel(const __half *in, const __half *__restrict__ weight,
+                                const __half *__restrict__ residual, __half *out, unsigned dim, float eps) {
+    __shared__ float sh[32];
+    const size_t base = (size_t)blockIdx.x * dim;
+    float s = 0.f;
+    for (unsigned i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = __half2float(in[base + i]);
+        s = fmaf(v, v, s);
+    }
+    s = block_sum(s, sh);
+    const float rms = rsqrtf(s / (float)dim + eps);
+    for (unsigned i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = __half2float(in[base + i]) * rms * __half2float(weight[i]);
+        if (residual) v += __half2float(residual[base + i]);
+        out[base + i] = __float2half_rn(v);
+    }
+}
+
+// NEOX half-split RoPE; rows of [heads, hd]; position from positions[row] or the scalar.
+__global__ void rope_kernel(const __half *in, __half *out, const uint32_t *__restrict__ positions,
+                            unsigned position, float theta, unsigned hd, unsigned heads, unsigned rows, float factor,
+                            int copy_tail) {
+    const unsigned half = hd / 2;
+    const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * heads * half) return;
+    const unsigned i = idx % half, rh = idx / half;  // rh = row*heads + head
+    const unsigned row = rh / heads;
+    const size_t i0 = (size_t)rh * hd + i, i1 = i0 + half;
+    const unsigned angles = (unsigned)((float)hd * factor) / 2;
+    if (i >= angles) {
+        if (copy_tail) {
+            out[i0] = in[i0];
+            out[i1] = in[i1];
+        }
+        return;
+    }
+    const float x0 = __half2float(in[i0]), x1 = __half2float(in[i1]);
+    const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)hd);
+    const float ang = (float)(positions ? positions[row] : position) * freq;
+    const float c = cosf(ang), s = sinf(ang);
+    out[i0] = __float2half_rn(x0 * c - x1 * s);
+    out[i1] = __float2half_rn(x0 * s + x1 * c);
+}
+
+__global__ void gelu_mul_kernel(const __half *a, const __half *b, __half *out, unsigned n) {
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float x = __half2float(a[i]);
+    const float x3 = x * x * x;
+    float inner = 0.7978845608f * (x + 0.044715f * x3);
+    inner = fminf(fmaxf(inner, -10.0f), 10.0f);
+    const float g = 0.5f * x * (1.0f + tanhf(inner));
+    out[i] = __float2half_rn(g * __half2float(b[i]));
+}
+
+__global__ void residual_add_kernel(const __half *a, const __half *b, __half *out, unsigned n) {
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2half_rn(__half2float(a[i]) + __half2float(b[i]));
+}
+
+__global__ void scale_in_place_kernel(__half *data, float scalar, unsigned n) {
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) data[i] = __float2half_rn(__half2float(data[i]) * scalar);
+}
+
+__global__ void logit_softcap_kernel(float *data, float cap, unsigned n) {
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) data[i] = cap * tanhf(data[i] / cap);
+}
+
+__global__ void gather_strided_kernel(const __half *__restrict__ src, __half *__restrict__ dst, unsigned row_stride,
+                                      unsigned base_off, unsigned pld, unsigned n_rows) {
+    const unsigned gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= n_rows * pld) return;
+    const unsigned i = gid / pld, p = gid - i * pld;
+    dst[gid] = src[(size_t)i * row_stride + base_off + p];
+}
+
+// out[r, :] = f16(f16((q-8)*d) * scale) for row tokens[r] of a Q4_0 table.
+// Two roundings, like dequant-to-f16 followed by scale_in_place.
+__global__ void embed_rows_q4_0_kernel(const uint8_t *__restrict__ table, const uint32_t *__restrict__ tokens,
+                                       __half *__restrict__ out, unsigned cols, float scale, int apply_scale) {
+    const unsigned r = blockIdx.x;
+    const size_t rb = (size_t)cols / 32 * 18;
+    const uint8_t *row = table + (size_t)tokens[r] * rb;
+    for (unsigned e = threadIdx.x; e < cols; e += blockDim.x) {
+        const unsigned blk = e >> 5, j = e & 31;
+        const uint8_t *p = row + (size_t)blk * 18;
+        const float d = __half2float(*reinterpret_cast<const __half *>(p));
+        const unsigned byte = p[2 + (j & 15)];
+        const unsigned qv = j < 16 ? (byte & 15u) : (byte >> 4);
+        __half h = __float2half_rn(((float)qv - 8.0f) * d);
+        if (apply_scale) h = __float2half_rn(__half2float(h) * scale);
+        out[(size_t)r * cols + e] = h;
+    }
+}
+
+// First maximum of each row (strict '>' scan order => lowest index wins ties).
+__global__ void argmax_rows_kernel(const float *__restrict__ v, uint32_t *__restrict__ out, unsigned cols) {
+    __shared__ float bv_s[32];
+    __shared__ unsigned bi_s[32];
+    const float *row = v + (size_t)blockIdx.x * cols;
+    float bv = -INFINITY;
+    unsigned bi = 0xffffffffu;
+    for (unsigned i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float x = row[i];
+        if (x > bv) { bv = x; bi = i; }
+    }
+    auto better = [](float a, unsigned ai, float b, unsigned bi2) { return a > b || (a == b && ai < bi2); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { bv_s[warp] = bv; bi_s[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < nw ? bv_s[lane] : -INFINITY;
+        bi = lane < nw ? bi_s[lane] : 0xffffffffu;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        // All -inf / NaN rows: the scalar scan returns index 0.
+        if (lane == 0) out[blockIdx.x] = bi == 0xffffffffu ? 0u : bi;
+    }
+}
+
+inline unsigned cdiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
+
+int rms_norm_common(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                    const lc_buf *residual, lc_buf *output, uint32_t dim, uint32_t rows, float eps) {
+    if (!k || !b || !input || !weight || !output) return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    LC_REQUIRE(dim >= 1, "%s: dim must be >= 1", name);
+    const size_t n = (size_t)dim * rows * 2;
+    LC_REQUIRE(input->bytes >= n && output->bytes >= n && weight->bytes >= (size_t)dim * 2 &&
+                   (!residual || residual->bytes >= n),
+               "%s: buffers too small for %u rows of %u", name, rows, dim);
+    if (rows == 0) return LC_OK;
+    const unsigned threads = dim >= 1024 ? 512 : (dim >= 256 ? 256 : 64);
+    rms_norm_kernel<<<rows, threads, 0, b->stream>>>((const __half *)input->dptr, (const __half *)weight->dptr,
+                                                     residual ? (const __half *)residual->dptr : nullptr,
+                                                     (__half *)output->dptr, dim, eps);
+    LC_CHECK_LAUNCH(name);
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lc_rms_norm_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight, lc_buf *output,
+                     uint32_t dim, uint32_t rows, float eps) {
+    return rms_norm_common("rms_norm", k, b, input, weight, nullptr, output, dim, rows, eps);
+}
+
+int lc_rms_norm_add_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                         const lc_buf *residual, lc_buf *output, uint32_t dim, uint32_t rows, float eps) {
+    if (!residual) return lc_fail(LC_ERR_INVALID_ARGUMENT, "rms_norm_add: residual is NULL");
+    return rms_norm_common("rms_norm_add", k, b, input, weight, residual, output, dim, rows, eps);
+}
+
+int lc_qk_norm_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *qk_data, const lc_buf *weight, uint32_t head_dim,
+                        uint32_t num_heads, float eps) {
+    return rms_norm_common("qk_norm", k, b, qk_data, weight, nullptr, qk_data, head_dim, num_heads, eps);
+}
+
+int lc_rope_into(lc_kernels *k, lc_batch *b, const lc_buf *input, lc_buf *output, uint32_t head_dim,
+                 uint32_t position, float theta, float partial_rotary_factor, uint32_t num_heads) {
+    if (!k || !b || !input || !output) return lc_fail(LC_ERR_INVALID_ARGUMENT, "rope: NULL argument");
+    LC_REQUIRE(head_dim >= 2 && head_dim % 2 == 0, "rope: head_dim %u must be even", head_dim);
+    const size_t n = (size_t)head_dim * num_heads * 2;
+    LC_REQUIRE(input->bytes >= n && output->bytes >= n, "rope: buffers too small");
+    const unsigned total = num_heads * (head_dim / 2);
+    if (total == 0) return LC_OK;
+    rope_kernel<<<cdiv(total, 256), 256, 0, b->stream>>>((const __half *)input->dptr, (__half *)output->dptr, nullptr,
+                                                         position, theta, head_dim, num_heads, 1,
+                                                         partial_rotary_factor, 1);
+    LC_CHECK_LAUNCH("rope");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_rope_batch_decode_into(lc_kernels *k, lc_batch *b, lc_buf *qk, const lc_buf *positions, float theta,
+                              uint32_t head_dim, uint32_t num_heads, uint32_t seq_len, float partial_rotary_factor) {
+    if (!k || !b || !qk || !positions) return lc_fail(LC_ERR_INVALID_ARGUMENT, "rope_batch_decode: NULL argument");
+    LC_REQUIRE(head_dim >= 2 && head_dim % 2 == 0, "rope_batch_decode: head_dim %u must be even", head_dim);
+    LC_REQUIRE(qk->bytes >= (size_t)seq_len * num_heads * head_dim * 2 && positions->bytes >= (size_t)seq_len * 4,
+               "rope_batch_decode: buffers too small");
+    const unsigned total = seq_len * num_heads * (head_dim / 2);
+    if (total == 0) return LC_OK;
+    rope_kernel<<<cdiv(total, 256), 256, 0, b->stream>>>((const __half *)qk->dptr, (__half *)qk->dptr,
+                                                         (const uint32_t *)positions->dptr, 0, theta, head_dim,
+                                                         num_heads, seq_len, partial_rotary_factor, 0);
+    LC_CHECK_LAUNCH("rope_batch_decode");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_gelu_mul_into(lc_kernels *k, lc_batch *b, const lc_buf *a, const lc_buf *bb, lc_buf *out, uint32_t count) {
+    if (!k || !b || !a || !bb || !out) return lc_fail(LC_ERR_INVALID_ARGUMENT, "gelu_mul: NULL argument");
+    const size_t n = (size_t)count * 2;
+    LC_REQUIRE(a->bytes >= n && bb->bytes >= n && out->bytes >= n, "gelu_mul: buffers too small for %u", count);
+    if (count == 0) return LC_OK;
+    gelu_mul_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((const __half *)a->dptr, (const __half *)bb->dptr,
+                                                             (__half *)out->dptr, count);
+    LC_CHECK_LAUNCH("gelu_mul");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_residual_add_into(lc_kernels *k, lc_batch *b, const lc_buf *a, const lc_buf *bb, lc_buf *output,
+                         uint32_t count) {
+    if (!k || !b || !a || !bb || !output) return lc_fail(LC_ERR_INVALID_ARGUMENT, "residual_add: NULL argument");
+    const size_t n = (size_t)count * 2;
+    LC_REQUIRE(a->bytes >= n && bb->bytes >= n && output->bytes >= n, "residual_add: buffers too small for %u", count);
+    if (count == 0) return LC_OK;
+    residual_add_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((const __half *)a->dptr, (const __half *)bb->dptr,
+                                                                 (__half *)output->dptr, count);
+    LC_CHECK_LAUNCH("residual_add");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_scale_in_place_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, float scalar, uint32_t count) {
+    if (!k || !b || !data) return lc_fail(LC_ERR_INVALID_ARGUMENT, "scale_in_place: NULL argument");
+    LC_REQUIRE(data->bytes >= (size_t)count * 2, "scale_in_place: buffer too small for %u", count);
+    if (count == 0) return LC_OK;
+    scale_in_place_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((__half *)data->dptr, scalar, count);
+    LC_CHECK_LAUNCH("scale_in_place");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_logit_softcap_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, float cap, uint32_t count) {
+    if (!k || !b || !data) return lc_fail(LC_ERR_INVALID_ARGUMENT, "logit_softcap: NULL argument");
+    LC_REQUIRE(data->bytes >= (size_t)count * 4, "logit_softcap: buffer too small for %u", count);
+    if (count == 0) return LC_OK;
+    logit_softcap_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((float *)data->dptr, cap, count);
+    LC_CHECK_LAUNCH("logit_softcap");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_gather_strided_f16_into(lc_kernels *k, lc_batch *b, const lc_buf *src, lc_buf *dst, uint32_t row_stride,
+                               uint32_t base_off, uint32_t pld, uint32_t n_rows) {
+    if (!k || !b || !src || !dst) return lc_fail(LC_ERR_INVALID_ARGUMENT, "gather_strided_f16: NULL argument");
+    if (n_rows == 0 || pld == 0) return LC_OK;
+    LC_REQUIRE(src->bytes >= ((size_t)(n_rows - 1) * row_stride + base_off + pld) * 2 &&
+                   dst->bytes >= (size_t)n_rows * pld * 2,
+               "gather_strided_f16: buffers too small");
+    gather_strided_kernel<<<cdiv(n_rows * pld, 256), 256, 0, b->stream>>>(
+        (const __half *)src->dptr, (__half *)dst->dptr, row_stride, base_off, pld, n_rows);
+    LC_CHECK_LAUNCH("gather_strided_f16");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_embed_rows_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *table, const lc_buf *tokens, lc_buf *output,
+                            uint32_t n_rows, uint32_t cols, uint32_t vocab, float scale) {
+    if (!k || !b || !table || !tokens || !output) return lc_fail(LC_ERR_INVALID_ARGUMENT, "embed_rows_q4_0: NULL argument");
+    if (cols == 0 || cols % 32 != 0) return lc_fail(LC_ERR_INVALID_ARGUMENT, "embed_rows_q4_0: cols %u not /32", cols);
+    LC_REQUIRE(table->bytes >= (size_t)vocab * (cols / 32) * 18 && tokens->bytes >= (size_t)n_rows * 4 &&
+                   output->bytes >= (size_t)n_rows * cols * 2,
+               "embed_rows_q4_0: buffers too small");
+    if (n_rows == 0) return LC_OK;
+    embed_rows_q4_0_kernel<<<n_rows, 256, 0, b->stream>>>((const uint8_t *)table->dptr, (const uint32_t *)tokens->dptr,
+                                                          (__half *)output->dptr, cols, scale, scale != 1.0f);
+    LC_CHECK_LAUNCH("embed_rows_q4_0");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc_buf *out_index, uint32_t rows,
+                            uint32_t cols) {
+    if (!k || !b || !values || !out_index) return lc_fail(LC_ERR_INVALID_ARGUMENT, "argmax_rows_f32: NULL argument");
+    LC_REQUIRE(cols >= 1, "argmax_rows_f32: cols must be >= 1");
+    LC_REQUIRE(values->bytes >= (size_t)rows * cols * 4 && out_index->bytes >= (size_t)rows * 4,
+               "argmax_rows_f32: buffers too small");
+    if (rows == 0) return LC_OK;
+    argmax_rows_kernel<<<rows, 1024, 0, b->stream>>>((const float *)values->dptr, (uint32_t *)out_index->dptr, cols);
+    LC_CHECK_LAUNCH("argmax_rows_f32");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+}  // extern "C"

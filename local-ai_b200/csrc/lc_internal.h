@@ -1,0 +1,99 @@
+// Internal definitions shared by the translation units of liblocal_cuda.so.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "../../include/local_cuda.h"
+
+struct lc_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    size_t l2_bytes = 0;
+    size_t total_mem = 0;
+};
+
+struct lc_buf {
+    lc_ctx *ctx = nullptr;
+    void *dptr = nullptr;
+    size_t bytes = 0;
+    bool owned = false;
+};
+
+struct lc_batch {
+    lc_ctx *ctx = nullptr;
+    cudaStream_t stream = nullptr;
+    uint32_t dispatch_count = 0;
+    bool capturing = false;
+};
+
+struct lc_pending {
+    lc_ctx *ctx = nullptr;
+    cudaEvent_t ev = nullptr;
+};
+
+struct lc_graph {
+    lc_ctx *ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+struct lc_kernels {
+    lc_ctx *ctx = nullptr;
+    // Routing switches, read once like the reference's OnceLock-cached env flags.
+    bool batchm = true;  // LOCAL_AI_BATCHM: register-resident small-M path
+    bool smallm = true;  // LOCAL_AI_SMALLM
+    bool mma = true;     // LOCAL_AI_MMA: tensor-core path for larger M
+    int kv_norm_mode = 0;  // LOCAL_CUDA_TQ_NORM: 0 sequential (Rust codec order), 1 tree (Metal order)
+    // Library-owned scratch for split-K partials (grown outside graph capture).
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    unsigned int *counters = nullptr;  // per-(lane,head) arrival counters, zero between launches
+    size_t counters_len = 0;
+    int *dev_status = nullptr;  // device-side error word (bounded waits report here)
+};
+
+// Record a failure for lc_last_error() and return `code`.
+int lc_fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+void lc_clear_error();
+
+#define LC_CUDA_TRY(expr)                                                              \
+    do {                                                                               \
+        cudaError_t _e = (expr);                                                       \
+        if (_e != cudaSuccess)                                                         \
+            return lc_fail(LC_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e));      \
+    } while (0)
+
+#define LC_REQUIRE(cond, ...)                                          \
+    do {                                                               \
+        if (!(cond)) return lc_fail(LC_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+// After a kernel launch: surface launch-configuration errors as a status.
+#define LC_CHECK_LAUNCH(name)                                                          \
+    do {                                                                               \
+        cudaError_t _e = cudaGetLastError();                                           \
+        if (_e != cudaSuccess)                                                         \
+            return lc_fail(LC_ERR_CUDA, "launch %s: %s", name, cudaGetErrorString(_e)); \
+    } while (0)
+
+static inline bool lc_aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+// Grow the kernels object's split-K scratch (no-op when large enough). Fails
+// during graph capture if growth would be needed.
+int lc_reserve_scratch(lc_kernels *k, lc_batch *b, size_t bytes, size_t counters);
+
+// Run `body(batch)` on a fresh batch and wait: the shape of the reference's
+// ctx-taking dispatchers (e.g. kernels.rs:5711-5742).
+template <typename F>
+static inline int lc_run_and_wait(lc_ctx *ctx, F body) {
+    lc_batch *b = nullptr;
+    int st = lc_batch_begin(ctx, &b);
+    if (st != LC_OK) return st;
+    st = body(b);
+    int st2 = lc_batch_commit_and_wait(b);
+    return st != LC_OK ? st : st2;
+}

@@ -1,0 +1,49 @@
+// Routing of the quantized batched matmul C[m, n] = A[m, k] x W[n, k]^T, the
+// stand-in for Kernels::matmul_nt_q4_0_into / matmul_nt_tq2_0_into
+// (local-metal/src/kernels.rs:6459-6563).  The reference picks between four
+// Metal kernels by m (batchm <= 4, smallm <= 8, simdgroup MMA, scalar tile);
+// here the choice is between two: the register-resident CUDA-core path that
+// streams the weights once for up to 16 rows (qmatvec.cu) and the tcgen05
+// tensor-core path for larger m (qmatmul_tc.cu).  LOCAL_AI_MMA=0 forces the
+// CUDA-core path for every m, as it forces the non-MMA kernels in the reference.
+#include "lc_internal.h"
+
+int lc_qgemm_cuda_core(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
+                       const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n);
+int lc_check_qargs(int fmt, const char *name, lc_kernels *k, lc_batch *b, const lc_buf *w, const lc_buf *x,
+                   const lc_buf *out, uint32_t m, uint32_t kk, uint32_t n, size_t out_elem);
+// qmatmul_tc.cu: returns LC_OK when it launched, or a negative value when the
+// shape is outside what the tensor-core kernel covers (caller falls through).
+int lc_qgemm_tcgen05(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
+                     const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n);
+
+static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch *b, const lc_buf *input,
+                 const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    int st = lc_check_qargs(fmt, name, k, b, weight, input, output, m, kk, n, f32out ? 4 : 2);
+    if (st != LC_OK) return st;
+    if (n == 0) return LC_OK;
+    if (k->mma && m > 8) {
+        st = lc_qgemm_tcgen05(fmt, f32out, k, b, input, weight, output, m, kk, n);
+        if (st >= 0) return st;
+    }
+    return lc_qgemm_cuda_core(fmt, f32out, k, b, input, weight, output, m, kk, n);
+}
+
+extern "C" {
+
+int lc_matmul_nt_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                           lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    return route(0, false, "matmul_nt_q4_0", k, b, input, weight, output, m, kk, n);
+}
+
+int lc_matmul_nt_tq2_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                            lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    return route(1, false, "matmul_nt_tq2_0", k, b, input, weight, output, m, kk, n);
+}
+
+int lc_matmul_nt_q4_0_f32out_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                                  lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    return route(0, true, "matmul_nt_q4_0_f32out", k, b, input, weight, output, m, kk, n);
+}
+
+}  // extern "C"

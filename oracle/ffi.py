@@ -1,0 +1,282 @@
+"""numpy-facing ctypes wrapper of the CPU oracle (oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+benchmark's CPU-baseline leg.  The CUDA library and its Python mirror never
+import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import build as _build
+
+Q4_0, TQ2_0 = 0, 1
+_lib = None
+
+u8p = C.c_void_p
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(str(_build.build()))
+        _lib.orc_f16_to_f32.restype = C.c_float
+        _lib.orc_f16_to_f32.argtypes = [C.c_uint16]
+        _lib.orc_f32_to_f16.restype = C.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [C.c_float]
+        _lib.orc_tq_encode.restype = C.c_uint16
+        _lib.orc_tq_code_bytes.restype = C.c_size_t
+        _lib.orc_tq_code_bytes.argtypes = [C.c_size_t, C.c_uint]
+        _lib.orc_swa_ring_capacity.restype = C.c_size_t
+        _lib.orc_swa_ring_capacity.argtypes = [C.c_size_t, C.c_size_t]
+        _lib.orc_argmax.restype = C.c_uint32
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a: np.ndarray):
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
+def _c(a, dtype) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _h(a) -> np.ndarray:
+    """f16 array viewed as uint16 (the oracle's f16 carrier)."""
+    return np.ascontiguousarray(a, dtype=np.float16).view(np.uint16)
+
+
+def _sz(v):
+    return C.c_size_t(int(v))
+
+
+def _u(v):
+    return C.c_uint(int(v))
+
+
+def _f(v):
+    return C.c_float(float(v))
+
+
+def row_bytes(fmt: int, cols: int) -> int:
+    return cols // 32 * 18 if fmt == Q4_0 else cols // 256 * 66
+
+
+def dequant(fmt: int, data, num_elements: int) -> np.ndarray:
+    data = _c(data, np.uint8)
+    out = np.zeros(num_elements, dtype=np.uint16)
+    fn = lib().orc_dequant_q4_0 if fmt == Q4_0 else lib().orc_dequant_tq2_0
+    fn(_p(data), _sz(data.size), _sz(num_elements), _p(out))
+    return out.view(np.float16)
+
+
+def expand_f32(fmt: int, w, rows: int, cols: int) -> np.ndarray:
+    w = _c(w, np.uint8)
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().orc_expand_f32(C.c_int(fmt), _p(w), _sz(rows), _sz(cols), _p(out))
+    return out
+
+
+def matmul_nt(fmt: int, a, w, m: int, k: int, n: int) -> np.ndarray:
+    """c[m, n] f32 (f64 accumulate) = a[m, k] f16 x W[n, k]^T."""
+    a, w = _h(a), _c(w, np.uint8)
+    out = np.empty((m, n), dtype=np.float32)
+    lib().orc_matmul_nt_quant(C.c_int(fmt), _p(a), _p(w), _sz(m), _sz(k), _sz(n), _p(out))
+    return out
+
+
+def matvec(fmt: int, w, x, rows: int, cols: int) -> np.ndarray:
+    return matmul_nt(fmt, x, w, 1, cols, rows).reshape(rows)
+
+
+def baseline_matmul_nt(fmt: int, a, w, m: int, k: int, n: int, threads: int = 0) -> np.ndarray:
+    a, w = _h(a), _c(w, np.uint8)
+    out = np.empty((m, n), dtype=np.float32)
+    lib().orc_baseline_matmul_nt(C.c_int(fmt), _p(a), _p(w), _sz(m), _sz(k), _sz(n), _p(out), C.c_int(threads))
+    return out
+
+
+def tq2_dequant(packed, scales, n: int) -> np.ndarray:
+    packed, scales = _c(packed, np.uint8), _h(scales)
+    out = np.empty(n, dtype=np.uint16)
+    lib().orc_tq2_dequant(_p(packed), _p(scales), _p(out), _sz(n))
+    return out.view(np.float16)
+
+
+def fwht_normalized(v) -> np.ndarray:
+    v = _c(v, np.float32).copy()
+    lib().orc_fwht_normalized(_p(v), _sz(v.size))
+    return v
+
+
+def tq_signs(dim: int, seed: int) -> np.ndarray:
+    out = np.empty(dim, dtype=np.float32)
+    lib().orc_tq_signs(_sz(dim), C.c_uint64(seed), _p(out))
+    return out
+
+
+def lloyd_max_gaussian(bits: int) -> np.ndarray:
+    out = np.empty(1 << bits, dtype=np.float32)
+    lib().orc_lloyd_max_gaussian(_u(bits), _p(out))
+    return out
+
+
+def tq_levels(dim: int, bits: int) -> np.ndarray:
+    out = np.empty(1 << bits, dtype=np.float32)
+    lib().orc_tq_levels(_sz(dim), _u(bits), _p(out))
+    return out
+
+
+def tq_code_bytes(dim: int, bits: int) -> int:
+    return lib().orc_tq_code_bytes(dim, bits)
+
+
+def tq_encode(x, bits: int, signs, levels, norm_mode: int = 0):
+    """-> (codes uint8[code_bytes], norm as np.float16 scalar)."""
+    x, signs, levels = _c(x, np.float32), _c(signs, np.float32), _c(levels, np.float32)
+    codes = np.empty(tq_code_bytes(x.size, bits), dtype=np.uint8)
+    nb = lib().orc_tq_encode(_p(x), _sz(x.size), _u(bits), _p(signs), _p(levels), _p(codes), C.c_int(norm_mode))
+    return codes, np.array([nb], dtype=np.uint16).view(np.float16)[0]
+
+
+def tq_decode(codes, norm, dim: int, bits: int, signs, levels) -> np.ndarray:
+    codes, signs, levels = _c(codes, np.uint8), _c(signs, np.float32), _c(levels, np.float32)
+    nb = int(np.array([norm], dtype=np.float16).view(np.uint16)[0])
+    out = np.empty(dim, dtype=np.float32)
+    lib().orc_tq_decode(_p(codes), C.c_uint16(nb), _sz(dim), _u(bits), _p(signs), _p(levels), _p(out))
+    return out
+
+
+def encode_kv(inp, levels, signs, packed, norms, hd, n_kv, num_tokens, bits, position, ring, norm_mode=0):
+    """In place on `packed` (uint8) and `norms` (float16)."""
+    lib().orc_encode_kv(_p(_h(inp)), _p(_c(levels, np.float32)), _p(_c(signs, np.float32)), _p(packed),
+                        _p(norms.view(np.uint16)), _u(hd), _u(n_kv), _u(num_tokens), _u(bits), _u(position),
+                        _u(ring), C.c_int(norm_mode))
+
+
+def encode_kv_batched(inp, levels, signs, packed, norms, positions, hd, n_kv, lane_capacity, bits, n_lanes, ring,
+                      norm_mode=0):
+    lib().orc_encode_kv_batched(_p(_h(inp)), _p(_c(levels, np.float32)), _p(_c(signs, np.float32)), _p(packed),
+                                _p(norms.view(np.uint16)), _p(_c(positions, np.uint32)), _u(hd), _u(n_kv),
+                                _u(lane_capacity), _u(bits), _u(n_lanes), _u(ring), C.c_int(norm_mode))
+
+
+def dequantize_kv(packed, norms, levels, signs, hd, n_kv, num_tokens, bits, token_start, ring) -> np.ndarray:
+    out = np.zeros(num_tokens * n_kv * hd, dtype=np.uint16)
+    lib().orc_dequantize_kv(_p(_c(packed, np.uint8)), _p(_h(norms)), _p(_c(levels, np.float32)),
+                            _p(_c(signs, np.float32)), _p(out), _u(hd), _u(n_kv), _u(num_tokens), _u(bits),
+                            _u(token_start), _u(ring))
+    return out.view(np.float16)
+
+
+def hadamard_rotate(x, signs, hd: int, heads: int, pre: bool, post: bool) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty(heads * hd, dtype=np.float32)
+    lib().orc_hadamard_rotate(_p(x), _p(_c(signs, np.float32)), _p(out), _u(hd), _u(heads), C.c_int(pre), C.c_int(post))
+    return out
+
+
+def flash_attention_tq(rq, kc, kn, vc, vn, levels, hd, kv_len, current_pos, n_q, n_kv, window, bits, ring,
+                       scale=1.0) -> np.ndarray:
+    out = np.empty(n_q * hd, dtype=np.float32)
+    lib().orc_flash_attention_tq(_p(_c(rq, np.float32)), _p(_c(kc, np.uint8)), _p(_h(kn)), _p(_c(vc, np.uint8)),
+                                 _p(_h(vn)), _p(_c(levels, np.float32)), _p(out), _u(hd), _u(kv_len),
+                                 _u(current_pos), _u(n_q), _u(n_kv), _u(window), _u(bits), _u(ring), _f(scale))
+    return out
+
+
+def flash_attention_tq_batched(rq, kc, kn, vc, vn, levels, positions, hd, lane_capacity, n_q, n_kv, window, bits,
+                               n_lanes, ring, scale=1.0) -> np.ndarray:
+    out = np.empty(n_lanes * n_q * hd, dtype=np.float32)
+    lib().orc_flash_attention_tq_batched(_p(_c(rq, np.float32)), _p(_c(kc, np.uint8)), _p(_h(kn)),
+                                         _p(_c(vc, np.uint8)), _p(_h(vn)), _p(_c(levels, np.float32)), _p(out),
+                                         _p(_c(positions, np.uint32)), _u(hd), _u(lane_capacity), _u(n_q), _u(n_kv),
+                                         _u(window), _u(bits), _u(n_lanes), _u(ring), _f(scale))
+    return out
+
+
+def tq_attention_fused(q, kc, kn, vc, vn, levels, signs, positions, hd, lane_capacity, n_q, n_kv, window, bits,
+                       n_lanes, ring, scale=1.0, kv_len=0, current_pos=0) -> np.ndarray:
+    out = np.empty(n_lanes * n_q * hd, dtype=np.uint16)
+    pos = _p(_c(positions, np.uint32)) if positions is not None else None
+    lib().orc_tq_attention_fused(_p(_h(q)), _p(_c(kc, np.uint8)), _p(_h(kn)), _p(_c(vc, np.uint8)), _p(_h(vn)),
+                                 _p(_c(levels, np.float32)), _p(_c(signs, np.float32)), _p(out), pos, _u(hd),
+                                 _u(lane_capacity), _u(n_q), _u(n_kv), _u(window), _u(bits), _u(n_lanes), _u(ring),
+                                 _f(scale), _u(kv_len), _u(current_pos))
+    return out.view(np.float16)
+
+
+def attention_f16(q, k, v, hd, kv_len, current_pos, n_q, n_kv, window, scale=1.0) -> np.ndarray:
+    out = np.empty(n_q * hd, dtype=np.uint16)
+    lib().orc_attention_f16(_p(_h(q)), _p(_h(k)), _p(_h(v)), _p(out), _u(hd), _u(kv_len), _u(current_pos), _u(n_q),
+                            _u(n_kv), _u(window), _f(scale))
+    return out.view(np.float16)
+
+
+def swa_ring_capacity(window: int, max_positions: int) -> int:
+    return lib().orc_swa_ring_capacity(window, max_positions)
+
+
+def rms_norm(x, weight, dim, rows, eps, residual=None) -> np.ndarray:
+    out = np.empty(rows * dim, dtype=np.uint16)
+    res = _p(_h(residual)) if residual is not None else None
+    lib().orc_rms_norm(_p(_h(x)), _p(_h(weight)), res, _p(out), _u(dim), _u(rows), _f(eps))
+    return out.view(np.float16)
+
+
+def rope(qk, positions, theta, hd, heads, rows, factor=1.0) -> np.ndarray:
+    out = _h(qk).copy()
+    lib().orc_rope(_p(out), _p(_c(positions, np.uint32)), _f(theta), _u(hd), _u(heads), _u(rows), _f(factor))
+    return out.view(np.float16)
+
+
+def gelu_mul(a, b) -> np.ndarray:
+    a, b = _h(a), _h(b)
+    out = np.empty(a.size, dtype=np.uint16)
+    lib().orc_gelu_mul(_p(a), _p(b), _p(out), _sz(a.size))
+    return out.view(np.float16)
+
+
+def residual_add(a, b) -> np.ndarray:
+    a, b = _h(a), _h(b)
+    out = np.empty(a.size, dtype=np.uint16)
+    lib().orc_residual_add(_p(a), _p(b), _p(out), _sz(a.size))
+    return out.view(np.float16)
+
+
+def scale_in_place(x, scalar) -> np.ndarray:
+    out = _h(x).copy()
+    lib().orc_scale_in_place(_p(out), _f(scalar), _sz(out.size))
+    return out.view(np.float16)
+
+
+def gather_strided_f16(src, row_stride, base_off, pld, n_rows) -> np.ndarray:
+    out = np.empty(n_rows * pld, dtype=np.uint16)
+    lib().orc_gather_strided_f16(_p(_h(src)), _p(out), _u(row_stride), _u(base_off), _u(pld), _u(n_rows))
+    return out.view(np.float16)
+
+
+def logit_softcap(x, cap) -> np.ndarray:
+    out = _c(x, np.float32).copy()
+    lib().orc_logit_softcap(_p(out), _f(cap), _sz(out.size))
+    return out
+
+
+def argmax(v) -> int:
+    v = _c(v, np.float32)
+    return lib().orc_argmax(_p(v), _sz(v.size))
+
+
+def embed_rows_q4_0(table, tokens, cols) -> np.ndarray:
+    tokens = _c(tokens, np.uint32)
+    out = np.empty(tokens.size * cols, dtype=np.uint16)
+    lib().orc_embed_rows_q4_0(_p(_c(table, np.uint8)), _p(tokens), _u(tokens.size), _u(cols), _p(out))
+    return out.view(np.float16)
+
+
+def num_threads() -> int:
+    return lib().orc_num_threads()

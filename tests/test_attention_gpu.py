@@ -1,0 +1,253 @@
+"""Decode attention over TurboQuant codes (and the FP16-KV variants) vs the CPU
+oracle.  Tolerance 1e-3 * max(|want|, 1) for f32 outputs (fp32 online softmax vs
+the oracle's f64 softmax); 2e-3 for f16 outputs (one more rounding)."""
+import numpy as np
+import pytest
+
+import refgen
+from gpu_util import Guarded, rel_close
+
+pytestmark = pytest.mark.gpu
+
+
+class Cache:
+    """Oracle-encoded K/V rows in the single-sequence or pool layout."""
+
+    def __init__(self, la, orc, ctx, hd, n_kv, bits, rows, seed):
+        self.hd, self.n_kv, self.bits = hd, n_kv, bits
+        self.levels, self.signs = la.tq_levels(hd, bits), la.tq_signs(hd, la.TQ_SEED)
+        self.cb = la.tq_code_bytes(hd, bits)
+        self.kc, self.vc = np.zeros(rows * n_kv * self.cb, np.uint8), np.zeros(rows * n_kv * self.cb, np.uint8)
+        self.kn, self.vn = np.zeros(rows * n_kv, np.float16), np.zeros(rows * n_kv, np.float16)
+        self.la, self.orc, self.ctx, self.seed = la, orc, ctx, seed
+
+    def fill_single(self, total, ring):
+        """Write logical positions 0..total-1 (wrapping when ring != 0)."""
+        k = self.la.synth.normal_f16((total, self.n_kv, self.hd), self.seed)
+        v = self.la.synth.normal_f16((total, self.n_kv, self.hd), self.seed + 1)
+        self.orc.encode_kv(k, self.levels, self.signs, self.kc, self.kn, self.hd, self.n_kv, total, self.bits, 0, ring)
+        self.orc.encode_kv(v, self.levels, self.signs, self.vc, self.vn, self.hd, self.n_kv, total, self.bits, 0, ring)
+
+    def fill_pool(self, positions, lane_rows, ring):
+        """Every lane gets rows for positions 0..positions[lane]."""
+        for lane, pos in enumerate(positions):
+            n = int(pos) + 1
+            k = self.la.synth.normal_f16((n, self.n_kv, self.hd), self.seed + 10 * lane)
+            v = self.la.synth.normal_f16((n, self.n_kv, self.hd), self.seed + 10 * lane + 1)
+            off_c, off_n = lane * lane_rows * self.n_kv * self.cb, lane * lane_rows * self.n_kv
+            span_c, span_n = lane_rows * self.n_kv * self.cb, lane_rows * self.n_kv
+            kc, kn = self.kc[off_c:off_c + span_c], self.kn[off_n:off_n + span_n]
+            vc, vn = self.vc[off_c:off_c + span_c], self.vn[off_n:off_n + span_n]
+            self.orc.encode_kv(k, self.levels, self.signs, kc, kn, self.hd, self.n_kv, n, self.bits, 0, ring)
+            self.orc.encode_kv(v, self.levels, self.signs, vc, vn, self.hd, self.n_kv, n, self.bits, 0, ring)
+
+    def device(self):
+        f = lambda a: self.la.CudaBuffer.from_slice(self.ctx, a)
+        return f(self.kc), f(self.kn), f(self.vc), f(self.vn), f(self.levels), f(self.signs)
+
+
+SINGLE_CASES = [
+    # hd, n_q, n_kv, bits, total, window, ring, scale
+    (256, 8, 1, 2, 300, 0, 0, 1.0),          # the model's shape, full attention, < one split
+    (256, 8, 1, 2, 5000, 0, 0, 0.0625),      # long enough for several splits
+    (256, 8, 1, 3, 777, 0, 0, 1.0),
+    (256, 8, 1, 4, 777, 0, 0, 0.0625),
+    (256, 8, 1, 2, 2000, 512, 512, 0.0625),  # SWA layer: 512 window in a 512-slot ring, wrapped
+    (256, 8, 1, 2, 2000, 512, 1024, 1.0),    # the reference's 1024-row ring
+    (256, 8, 1, 2, 100, 512, 512, 1.0),      # window not yet full
+    (128, 4, 2, 4, 333, 0, 0, 1.0),          # 2 kv heads, group of 2
+    (64, 6, 2, 3, 200, 50, 64, 1.0),         # group of 3 (padded to 4), odd window
+    (512, 8, 8, 2, 150, 0, 0, 1.0),          # MHA: group of 1, head_dim 512
+    (512, 16, 1, 4, 90, 0, 0, 1.0),          # group of 16 -> two chunks of 8
+    (256, 8, 1, 2, 1, 0, 0, 1.0),            # a single key
+]
+
+
+@pytest.mark.parametrize("hd,n_q,n_kv,bits,total,window,ring,scale", SINGLE_CASES)
+def test_flash_attention_tq_matches_oracle(la, orc, ctx, kernels, hd, n_q, n_kv, bits, total, window, ring, scale):
+    rows = ring if ring else total
+    c = Cache(la, orc, ctx, hd, n_kv, bits, rows, seed=1000 + total)
+    c.fill_single(total, ring)
+    kc, kn, vc, vn, lv, sg = c.device()
+    q = (la.synth.normal(55, n_q * hd) * 1.0).astype(np.float32)
+    rq = orc.hadamard_rotate(q, c.signs, hd, n_q, True, False)
+    out = Guarded(la, ctx, n_q * hd * 4)
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_attention_tq_into(b, la.CudaBuffer.from_slice(ctx, rq), kc, kn, vc, vn, lv, out.view, hd, total,
+                                    total - 1, n_q, n_kv, window, bits, ring, scale)
+    b.commit_and_wait()
+    want = orc.flash_attention_tq(rq, c.kc, c.kn, c.vc, c.vn, c.levels, hd, total, total - 1, n_q, n_kv, window, bits, ring, scale)
+    rel_close(out.read(np.float32), want, 1e-3, "flash_attention_tq")
+
+
+def test_kv_len_shorter_than_position(la, orc, ctx, kernels):
+    """seq_len = min(kv_len, pos + 1) (attention_flash_tq.metal:178)."""
+    hd, n_q, n_kv, bits, total = 256, 8, 1, 2, 64
+    c = Cache(la, orc, ctx, hd, n_kv, bits, total, seed=5)
+    c.fill_single(total, 0)
+    kc, kn, vc, vn, lv, sg = c.device()
+    rq = la.synth.normal(56, n_q * hd).astype(np.float32)
+    out = Guarded(la, ctx, n_q * hd * 4)
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_attention_tq_into(b, la.CudaBuffer.from_slice(ctx, rq), kc, kn, vc, vn, lv, out.view, hd, 40, 63, n_q, n_kv, 0, bits, 0, 1.0)
+    b.commit_and_wait()
+    want = orc.flash_attention_tq(rq, c.kc, c.kn, c.vc, c.vn, c.levels, hd, 40, 63, n_q, n_kv, 0, bits, 0, 1.0)
+    rel_close(out.read(np.float32), want, 1e-3, "kv_len < pos + 1")
+
+
+@pytest.mark.parametrize("bits,window,ring,lane_rows", [(2, 0, 0, 600), (2, 512, 512, 512), (3, 64, 128, 128), (4, 0, 0, 300)])
+def test_batched_pool_attention_ragged(la, orc, ctx, kernels, bits, window, ring, lane_rows):
+    """Ragged lanes over the unified pool (kernels.rs:10457-10711); also each lane equals a single-sequence call."""
+    hd, n_q, n_kv = 256, 8, 1
+    cap = lane_rows
+    positions = np.array([0, 17, 299, 150, 64, 511 if ring else 299, 1100 if ring else 5], np.uint32)
+    n_lanes = positions.size
+    c = Cache(la, orc, ctx, hd, n_kv, bits, n_lanes * lane_rows, seed=300 + bits)
+    c.fill_pool(positions, lane_rows, ring)
+    kc, kn, vc, vn, lv, sg = c.device()
+    q16 = la.synth.normal_f16((n_lanes, n_q, hd), 57)
+    rq = orc.hadamard_rotate(q16.astype(np.float32), c.signs, hd, n_lanes * n_q, True, False)
+    out = Guarded(la, ctx, n_lanes * n_q * hd * 4)
+    pos_b = la.CudaBuffer.from_slice(ctx, positions)
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_attention_tq_batched_into(b, la.CudaBuffer.from_slice(ctx, rq), kc, kn, vc, vn, lv, out.view, pos_b,
+                                            hd, cap, n_q, n_kv, window, bits, n_lanes, ring, 0.0625)
+    b.commit_and_wait()
+    got = out.read(np.float32)
+    want = orc.flash_attention_tq_batched(rq, c.kc, c.kn, c.vc, c.vn, c.levels, positions, hd, cap, n_q, n_kv, window,
+                                          bits, n_lanes, ring, 0.0625)
+    rel_close(got, want, 1e-3, "flash_attention_tq_batched")
+    # fused form: f16 q in, f16 attention output out
+    fo = Guarded(la, ctx, n_lanes * n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.tq_attention_batched_into(b, la.CudaBuffer.from_slice(ctx, q16), kc, kn, vc, vn, lv, sg, fo.view, pos_b, hd,
+                                      cap, n_q, n_kv, window, bits, n_lanes, ring, 0.0625)
+    b.commit_and_wait()
+    wantf = orc.tq_attention_fused(q16, c.kc, c.kn, c.vc, c.vn, c.levels, c.signs, positions, hd, cap, n_q, n_kv,
+                                   window, bits, n_lanes, ring, 0.0625)
+    rel_close(fo.read(np.float16), wantf.astype(np.float32), 2e-3, "tq_attention_batched")
+
+
+def test_fused_single_equals_three_call_sequence(la, orc, ctx, kernels):
+    """lc_tq_attention_into == rotate_hf -> flash_attention_tq -> rotate_fh (quant_cache.rs:565-596)."""
+    hd, n_q, n_kv, bits, total = 256, 8, 1, 2, 3000
+    c = Cache(la, orc, ctx, hd, n_kv, bits, total, seed=9)
+    c.fill_single(total, 0)
+    kc, kn, vc, vn, lv, sg = c.device()
+    q16 = la.synth.normal_f16((n_q, hd), 58)
+    qb = la.CudaBuffer.from_slice(ctx, q16)
+    rq, vacc = la.CudaBuffer.empty(ctx, n_q * hd * 4), la.CudaBuffer.empty(ctx, n_q * hd * 4)
+    three, fused = Guarded(la, ctx, n_q * hd * 2), Guarded(la, ctx, n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.hadamard_rotate_hf_into(b, qb, sg, rq, hd, n_q, 1, 0)
+    kernels.flash_attention_tq_into(b, rq, kc, kn, vc, vn, lv, vacc, hd, total, total - 1, n_q, n_kv, 0, bits, 0, 1.0)
+    kernels.hadamard_rotate_fh_into(b, vacc, sg, three.view, hd, n_q, 0, 1)
+    kernels.tq_attention_into(b, qb, kc, kn, vc, vn, lv, sg, fused.view, hd, total, total - 1, n_q, n_kv, 0, bits, 0, 1.0)
+    b.commit_and_wait()
+    want = orc.tq_attention_fused(q16, c.kc, c.kn, c.vc, c.vn, c.levels, c.signs, None, hd, 0, n_q, n_kv, 0, bits, 1, 0,
+                                  1.0, total, total - 1).astype(np.float32)
+    rel_close(three.read(np.float16), want, 2e-3, "three-call sequence")
+    rel_close(fused.read(np.float16), want, 2e-3, "fused call")
+
+
+def test_fused_attention_close_to_exact_attention_over_decoded_rows(la, orc, ctx, kernels):
+    """kernels.rs:9936-10114: code-space attention vs dequantize + plain attention, <= 0.02 * |ref|_inf."""
+    hd, n_q, n_kv, bits, total = 256, 8, 1, 4, 512
+    c = Cache(la, orc, ctx, hd, n_kv, bits, total, seed=12)
+    c.fill_single(total, 0)
+    kc, kn, vc, vn, lv, sg = c.device()
+    q16 = la.synth.normal_f16((n_q, hd), 59)
+    fused = Guarded(la, ctx, n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.tq_attention_into(b, la.CudaBuffer.from_slice(ctx, q16), kc, kn, vc, vn, lv, sg, fused.view, hd, total,
+                              total - 1, n_q, n_kv, 0, bits, 0, 1.0)
+    b.commit_and_wait()
+    kd = orc.dequantize_kv(c.kc, c.kn, c.levels, c.signs, hd, n_kv, total, bits, 0, 0)
+    vd = orc.dequantize_kv(c.vc, c.vn, c.levels, c.signs, hd, n_kv, total, bits, 0, 0)
+    ref = orc.attention_f16(q16, kd, vd, hd, total, total - 1, n_q, n_kv, 0).astype(np.float32)
+    assert np.max(np.abs(fused.read(np.float16).astype(np.float32) - ref)) <= 0.02 * np.max(np.abs(ref))
+
+
+def test_attention_rejects_bad_arguments(la, ctx, kernels):
+    buf = la.CudaBuffer.empty(ctx, 1 << 16)
+    b = la.CommandBatch.new(ctx)
+    for args in ((100, 8, 1, 2), (256, 8, 3, 2), (256, 8, 1, 5)):  # head_dim, n_q, n_kv, bits
+        hd, n_q, n_kv, bits = args
+        with pytest.raises(la.Error) as ei:
+            kernels.flash_attention_tq_into(b, buf, buf, buf, buf, buf, buf, buf, hd, 4, 3, n_q, n_kv, 0, bits, 0, 1.0)
+        assert ei.value.kind == "InvalidArgument"
+    small = la.CudaBuffer.empty(ctx, 64)
+    with pytest.raises(la.Error):
+        kernels.flash_attention_tq_into(b, buf, small, buf, buf, buf, buf, buf, 256, 100, 99, 8, 1, 0, 2, 0, 1.0)
+    b.commit_and_wait()
+
+
+# ---- FP16-KV kernels ----
+def f16_case(la, hd, n_q, n_kv, total, seed):
+    q = (la.synth.normal(seed, n_q * hd) * 0.3).astype(np.float16)
+    k = (la.synth.normal(seed + 1, total * n_kv * hd) * 0.3).astype(np.float16)
+    v = la.synth.normal_f16((total * n_kv * hd,), seed + 2)
+    return q, k, v
+
+
+@pytest.mark.parametrize("hd,n_q,n_kv,total", [(256, 8, 1, 1500), (128, 4, 2, 100), (256, 8, 1, 256), (512, 2, 2, 700)])
+def test_flash_decoding(la, orc, ctx, kernels, hd, n_q, n_kv, total):
+    q, k, v = f16_case(la, hd, n_q, n_kv, total, 70)
+    out = Guarded(la, ctx, n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_decoding_into(ctx, b, la.CudaBuffer.from_slice(ctx, q), la.CudaBuffer.from_slice(ctx, k),
+                                la.CudaBuffer.from_slice(ctx, v), out.view, hd, total, total - 1, n_q, n_kv)
+    b.commit_and_wait()
+    rel_close(out.read(np.float16), orc.attention_f16(q, k, v, hd, total, total - 1, n_q, n_kv, 0).astype(np.float32), 2e-3, "flash_decoding")
+
+
+@pytest.mark.parametrize("window,total", [(512, 2000), (512, 300), (0, 900), (64, 64)])
+def test_flash_attention_windowed_split(la, orc, ctx, kernels, window, total):
+    hd, n_q, n_kv = 256, 8, 1
+    q, k, v = f16_case(la, hd, n_q, n_kv, total, 80)
+    eff = min(total, window) if window else total
+    splits = kernels.flash_split_count(eff)
+    assert 1 <= splits <= 16 and splits == min(16, max(1, -(-eff // 16)))
+    out = Guarded(la, ctx, n_q * hd * 2)
+    pm, ps, pa = (la.CudaBuffer.empty(ctx, n_q * splits * 4), la.CudaBuffer.empty(ctx, n_q * splits * 4),
+                  la.CudaBuffer.empty(ctx, n_q * splits * hd * 4))
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_attention_windowed_split_into(b, la.CudaBuffer.from_slice(ctx, q), la.CudaBuffer.from_slice(ctx, k),
+                                                la.CudaBuffer.from_slice(ctx, v), out.view, pm, ps, pa, hd, total,
+                                                total - 1, n_q, n_kv, window, splits)
+    assert b.dispatch_count() == 2
+    b.commit_and_wait()
+    rel_close(out.read(np.float16), orc.attention_f16(q, k, v, hd, total, total - 1, n_q, n_kv, window).astype(np.float32), 2e-3, "windowed split")
+
+
+def test_attention_sliding(la, orc, ctx, kernels):
+    hd, n_q, n_kv, total, window = 256, 8, 1, 1300, 512
+    q, k, v = f16_case(la, hd, n_q, n_kv, total, 90)
+    out = Guarded(la, ctx, n_q * hd * 2)
+    kernels.attention_sliding(ctx, la.CudaBuffer.from_slice(ctx, q), la.CudaBuffer.from_slice(ctx, k),
+                              la.CudaBuffer.from_slice(ctx, v), out.view, hd, total, total - 1, window, n_q, n_kv)
+    rel_close(out.read(np.float16), orc.attention_f16(q, k, v, hd, total, total - 1, n_q, n_kv, window).astype(np.float32), 2e-3, "attention_sliding")
+
+
+def test_attention_is_convex_combination_at_32k(la, orc, ctx, kernels):
+    """Size-independent properties at the benchmark context (32768 rows, tq2): with every V row equal
+    the output equals that row whatever the scores; and splits agree with the oracle on a strided subsample."""
+    hd, n_q, n_kv, bits, total = 256, 8, 1, 2, 32768
+    levels, signs = la.tq_levels(hd, bits), la.tq_signs(hd, la.TQ_SEED)
+    cb = la.tq_code_bytes(hd, bits)
+    kc = la.synth.splitmix64(1, total * cb // 8).view(np.uint8)
+    kn = np.abs(la.synth.normal_f16((total,), 2)) + np.float16(0.5)
+    one_c, one_n = orc.tq_encode(la.synth.normal(3, hd).astype(np.float32), bits, signs, levels)
+    vc = np.tile(one_c, total)
+    vn = np.full(total, one_n, np.float16)
+    rq = (la.synth.normal(4, n_q * hd) * 0.5).astype(np.float32)
+    out = Guarded(la, ctx, n_q * hd * 4)
+    f = lambda a: la.CudaBuffer.from_slice(ctx, a)
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_attention_tq_into(b, f(rq), f(kc), f(kn), f(vc), f(vn), f(levels), out.view, hd, total, total - 1,
+                                    n_q, n_kv, 0, bits, 0, 0.0625)
+    b.commit_and_wait()
+    got = out.read(np.float32).reshape(n_q, hd)
+    row = np.float32(one_n) * levels[(np.unpackbits(one_c, bitorder="little").reshape(hd, bits) * (1 << np.arange(bits))).sum(1)]
+    for h in range(n_q):
+        rel_close(got[h], row, 1e-3, f"constant-V head {h}")

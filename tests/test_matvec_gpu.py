@@ -1,0 +1,172 @@
+"""Fused-dequant matvec / small-M matmul parity: CUDA path through the C ABI vs
+the CPU oracle, on the reference tests' own generators and shapes
+(local-metal/src/kernels.rs:9233-9760) and on the benchmark configurations.
+Tolerance: 1e-3 * max(|want|, 1) — fp32 accumulate, one f16 rounding on store."""
+import numpy as np
+import pytest
+
+import refgen
+from gpu_util import Guarded, rel_close
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def run_matvec(la, ctx, kernels, name, raw, v, rows, cols, f32out, into):
+    m, x = la.CudaBuffer.from_slice(ctx, raw), la.CudaBuffer.from_slice(ctx, v)
+    out = Guarded(la, ctx, rows * (4 if f32out else 2))
+    if into:
+        b = la.CommandBatch.new(ctx)
+        getattr(kernels, name + "_into")(b, m, x, out.view, rows, cols)
+        assert b.dispatch_count() == 1
+        b.commit_and_wait()
+    else:
+        getattr(kernels, name)(ctx, m, x, out.view, rows, cols)
+    return out.read(np.float32 if f32out else np.float16).astype(np.float32)
+
+
+@pytest.mark.parametrize("into", [False, True])
+@pytest.mark.parametrize("f32out", [False, True])
+@pytest.mark.parametrize("rows,cols", [(5, 96), (33, 1536), (100, 6144), (1, 32)])
+def test_matvec_q4_0_matches_cpu_reference(la, orc, ctx, kernels, rows, cols, f32out, into):
+    raw, dq = refgen.q4_0_payload(rows, cols, 0xBEEF)
+    v = refgen.test_vector(cols)
+    got = run_matvec(la, ctx, kernels, "matvec_q4_0" + ("_f32out" if f32out else ""), raw, v, rows, cols, f32out, into)
+    rel_close(got, orc.matvec(orc.Q4_0, raw, v, rows, cols), TOL, "matvec_q4_0")
+    refgen.assert_close(got, refgen.cpu_matvec(dq, v.astype(np.float32)), 0.01 if f32out else 0.02, "vs kernels.rs tolerance")
+
+
+@pytest.mark.parametrize("into", [False, True])
+@pytest.mark.parametrize("f32out", [False, True])
+@pytest.mark.parametrize("rows,cols", [(5, 512), (7, 256), (37, 1536), (100, 6144), (13, 2048)])
+def test_matvec_tq2_0_matches_cpu_reference(la, orc, ctx, kernels, rows, cols, f32out, into):
+    raw, dq = refgen.tq2_0_payload(rows, cols, 0xC0DE)
+    v = refgen.test_vector(cols)
+    got = run_matvec(la, ctx, kernels, "matvec_tq2_0" + ("_f32out" if f32out else ""), raw, v, rows, cols, f32out, into)
+    rel_close(got, orc.matvec(orc.TQ2_0, raw, v, rows, cols), TOL, "matvec_tq2_0")
+    refgen.assert_close(got, refgen.cpu_matvec(dq, v.astype(np.float32)), 0.01 if f32out else 0.02, "vs kernels.rs tolerance")
+
+
+def test_matvec_tq2_0_soa_matches_cpu_reference(la, orc, ctx, kernels):
+    rows, cols = 37, 1536
+    raw, _ = refgen.tq2_0_payload(rows, cols, 0x50A)
+    qs, scales = refgen.tq2_0_repack_soa(raw, rows, cols)
+    v = refgen.test_vector(cols)
+    out = Guarded(la, ctx, rows * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.matvec_tq2_0_soa_into(b, la.CudaBuffer.from_slice(ctx, qs), la.CudaBuffer.from_slice(ctx, scales),
+                                  la.CudaBuffer.from_slice(ctx, v), out.view, rows, cols)
+    b.commit_and_wait()
+    rel_close(out.read(np.float16), orc.matvec(orc.TQ2_0, raw, v, rows, cols), TOL, "matvec_tq2_0_soa")
+
+
+def test_config1_q4_0_6144x1536(la, orc, ctx, kernels):
+    rows, cols = 6144, 1536
+    w = la.synth.q4_0_weights(rows, cols, seed=101)
+    x = la.synth.normal_f16((cols,), seed=102)
+    got = run_matvec(la, ctx, kernels, "matvec_q4_0", w, x, rows, cols, False, True)
+    rel_close(got, orc.matvec(orc.Q4_0, w, x, rows, cols), TOL, "config 1")
+
+
+def test_config2_tq2_0_8192x1536_m1(la, orc, ctx, kernels):
+    rows, cols = 8192, 1536
+    w = la.synth.tq2_0_weights(rows, cols, seed=201)
+    x = la.synth.normal_f16((cols,), seed=202)
+    got = run_matvec(la, ctx, kernels, "matvec_tq2_0", w, x, rows, cols, False, True)
+    rel_close(got, orc.matvec(orc.TQ2_0, w, x, rows, cols), TOL, "config 2, M=1")
+
+
+def run_matmul(la, ctx, kernels, name, a, raw, m, k, n, f32out=False):
+    out = Guarded(la, ctx, m * n * (4 if f32out else 2))
+    b = la.CommandBatch.new(ctx)
+    getattr(kernels, name)(b, la.CudaBuffer.from_slice(ctx, a), la.CudaBuffer.from_slice(ctx, raw), out.view, m, k, n)
+    b.commit_and_wait()
+    return out.read(np.float32 if f32out else np.float16).astype(np.float32).reshape(m, n)
+
+
+@pytest.mark.parametrize("k,n", [(1536, 6144), (6144, 1536), (1536, 100)])
+def test_matmul_nt_q4_0_small_m(la, orc, ctx, kernels, k, n):
+    """kernels.rs:9429-9461: M = 1..8, gate/up-like, down-like and ragged N."""
+    raw, _ = refgen.q4_0_payload(n, k, (0x5A1D + n) & 0xFFFFFFFF)
+    for m in range(1, 9):
+        a = refgen.sin_matrix(m, k, 0.011, 0.6)
+        got = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_into", a, raw, m, k, n)
+        rel_close(got, orc.matmul_nt(orc.Q4_0, a, raw, m, k, n), TOL, f"matmul_nt_q4_0 m={m}")
+
+
+@pytest.mark.parametrize("k,n", [(1536, 6144), (6144, 1536), (1536, 100), (256, 37)])
+def test_matmul_nt_tq2_0_small_m(la, orc, ctx, kernels, k, n):
+    """kernels.rs:9468-9533."""
+    raw, _ = refgen.tq2_0_payload(n, k, (0x2B19 + n) & 0xFFFFFFFF)
+    for m in range(1, 9):
+        a = refgen.sin_matrix(m, k, 0.017, 0.6, np.cos)
+        got = run_matmul(la, ctx, kernels, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+        rel_close(got, orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n), TOL, f"matmul_nt_tq2_0 m={m}")
+
+
+@pytest.mark.parametrize("m", [1, 3, 16])
+def test_multivec_nt(la, orc, ctx, kernels, m):
+    """kernels.rs:9652-9698: M <= 16, N = 33 (not a multiple of any tile)."""
+    k, n = 512, 33
+    a = refgen.sin_matrix(m, k, 0.013, 0.7)
+    raw, _ = refgen.q4_0_payload(n, k, 0x77)
+    rel_close(run_matmul(la, ctx, kernels, "multivec_nt_q4_0_into", a, raw, m, k, n),
+              orc.matmul_nt(orc.Q4_0, a, raw, m, k, n), TOL, "multivec_nt_q4_0")
+    raw, _ = refgen.tq2_0_payload(n, k, 0x78)
+    rel_close(run_matmul(la, ctx, kernels, "multivec_nt_tq2_0_into", a, raw, m, k, n),
+              orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n), TOL, "multivec_nt_tq2_0")
+
+
+def test_multivec_rejects_m_out_of_range(la, ctx, kernels):
+    k, n = 256, 8
+    raw, _ = refgen.tq2_0_payload(n, k, 1)
+    a = la.CudaBuffer.from_slice(ctx, np.zeros((17, k), np.float16))
+    out = la.CudaBuffer.empty(ctx, 17 * n * 2)
+    b = la.CommandBatch.new(ctx)
+    with pytest.raises(la.Error) as ei:
+        kernels.multivec_nt_tq2_0_into(b, a, la.CudaBuffer.from_slice(ctx, raw), out, 17, k, n)
+    assert ei.value.kind == "InvalidArgument"
+    b.commit_and_wait()
+
+
+def test_quant_kernels_reject_misaligned_cols(la, ctx, kernels):
+    """kernels.rs:9752-9760."""
+    buf = la.CudaBuffer.empty(ctx, 4096)
+    with pytest.raises(la.Error) as ei:
+        kernels.matvec_q4_0(ctx, buf, buf, buf, 4, 33)
+    assert ei.value.kind == "InvalidArgument" and "not /32" in str(ei.value)
+    with pytest.raises(la.Error) as ei:
+        kernels.matvec_tq2_0(ctx, buf, buf, buf, 4, 128)
+    assert ei.value.kind == "InvalidArgument" and "not /256" in str(ei.value)
+
+
+def test_short_buffers_are_rejected(la, ctx, kernels):
+    small, big = la.CudaBuffer.empty(ctx, 64), la.CudaBuffer.empty(ctx, 1 << 16)
+    with pytest.raises(la.Error):
+        kernels.matvec_q4_0(ctx, small, big, big, 64, 1536)   # weights too small
+    with pytest.raises(la.Error):
+        kernels.matvec_q4_0(ctx, big, big, small, 64, 32)     # output too small
+
+
+def test_tq2_dequant(la, orc, ctx, kernels):
+    n = 4 * 1000 + 2
+    packed = refgen.xorshift_bytes(5, (n + 3) // 4)
+    scales = (refgen.seeded_vec((n + 3) // 4, 3) + 1.0).astype(np.float16)
+    out = Guarded(la, ctx, n * 2)
+    kernels.tq2_dequant(ctx, la.CudaBuffer.from_slice(ctx, packed), la.CudaBuffer.from_slice(ctx, scales), out.view, n)
+    assert np.array_equal(out.read(np.uint16), orc.tq2_dequant(packed, scales, n).view(np.uint16))
+
+
+def test_matvec_is_linear_at_full_size(la, ctx, kernels):
+    """Size-independent property at the benchmark shape: W(a + b) = Wa + Wb up to rounding."""
+    rows, cols = 8192, 1536
+    w = la.synth.tq2_0_weights(rows, cols, seed=7)
+    a = la.synth.normal_f16((cols,), 8, 0.25)
+    b = la.synth.normal_f16((cols,), 9, 0.25)
+    ab = (a.astype(np.float32) + b.astype(np.float32)).astype(np.float16)
+    exact = np.flatnonzero(ab.astype(np.float32) == a.astype(np.float32) + b.astype(np.float32))
+    a, b, ab = [np.where(np.isin(np.arange(cols), exact), v, 0).astype(np.float16) for v in (a, b, ab)]
+    ya = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", w, a, rows, cols, True, True)
+    yb = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", w, b, rows, cols, True, True)
+    yab = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", w, ab, rows, cols, True, True)
+    rel_close(yab, ya + yb, 1e-4, "linearity")

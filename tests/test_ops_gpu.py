@@ -1,0 +1,126 @@
+"""The small per-layer ops, the embedding gather and greedy argmax vs the CPU oracle.
+f16 outputs may differ by one rounding: tolerance 2e-3 * max(|want|, 1)."""
+import numpy as np
+import pytest
+
+import refgen
+from gpu_util import Guarded, rel_close
+
+pytestmark = pytest.mark.gpu
+EPS = 1e-6
+
+
+def dev(la, ctx, a):
+    return la.CudaBuffer.from_slice(ctx, a)
+
+
+@pytest.mark.parametrize("dim,rows", [(1536, 64), (256, 8), (100, 3), (6144, 2)])
+def test_rms_norm_and_add(la, orc, ctx, kernels, dim, rows):
+    x = la.synth.normal_f16((rows, dim), 1, 3.0)
+    w = (1.0 + 0.1 * la.synth.normal(2, dim)).astype(np.float16)
+    r = la.synth.normal_f16((rows, dim), 3)
+    out = Guarded(la, ctx, rows * dim * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.rms_norm_into(b, dev(la, ctx, x), dev(la, ctx, w), out.view, dim, rows, EPS)
+    b.commit_and_wait()
+    rel_close(out.read(np.float16), orc.rms_norm(x, w, dim, rows, EPS).astype(np.float32), 2e-3, "rms_norm")
+    out = Guarded(la, ctx, rows * dim * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.rms_norm_add_into(b, dev(la, ctx, x), dev(la, ctx, w), dev(la, ctx, r), out.view, dim, rows, EPS)
+    b.commit_and_wait()
+    rel_close(out.read(np.float16), orc.rms_norm(x, w, dim, rows, EPS, residual=r).astype(np.float32), 2e-3, "rms_norm_add")
+
+
+def test_qk_norm_in_place(la, orc, ctx, kernels):
+    hd, heads = 256, 24
+    x = la.synth.normal_f16((heads, hd), 4, 2.0)
+    w = (1.0 + 0.1 * la.synth.normal(5, hd)).astype(np.float16)
+    buf = dev(la, ctx, x)
+    b = la.CommandBatch.new(ctx)
+    kernels.qk_norm_gpu_into(b, buf, dev(la, ctx, w), hd, heads, EPS)
+    b.commit_and_wait()
+    rel_close(buf.as_slice(np.float16), orc.rms_norm(x, w, hd, heads, EPS).astype(np.float32), 2e-3, "qk_norm")
+
+
+@pytest.mark.parametrize("factor", [1.0, 0.25])
+def test_rope_single_and_batched(la, orc, ctx, kernels, factor):
+    hd, heads, theta = 256, 8, 1e6
+    x = la.synth.normal_f16((heads, hd), 6)
+    out = Guarded(la, ctx, heads * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.rope_into(b, dev(la, ctx, x), out.view, hd, 8191, theta, factor, heads)
+    b.commit_and_wait()
+    want = orc.rope(x, np.array([8191], np.uint32), theta, hd, heads, 1, factor)
+    rel_close(out.read(np.float16), want.astype(np.float32), 2e-3, "rope")
+    rows = 5
+    positions = np.array([0, 1, 511, 8192, 131071], np.uint32)
+    xb = la.synth.normal_f16((rows, heads, hd), 7)
+    buf = dev(la, ctx, xb)
+    b = la.CommandBatch.new(ctx)
+    kernels.rope_batch_decode_into(b, buf, dev(la, ctx, positions), theta, hd, heads, rows, factor)
+    b.commit_and_wait()
+    want = orc.rope(xb, positions, theta, hd, heads, rows, factor)
+    # cos/sin of angles up to 1.3e5 rad: allow for last-bit differences between libm and CUDA
+    rel_close(buf.as_slice(np.float16), want.astype(np.float32), 4e-3, "rope_batch_decode")
+
+
+def test_elementwise(la, orc, ctx, kernels):
+    n = 64 * 6144 + 3
+    a = la.synth.normal_f16((n,), 8, 3.0)
+    c = la.synth.normal_f16((n,), 9)
+    out = Guarded(la, ctx, n * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.gelu_mul_into(b, dev(la, ctx, a), dev(la, ctx, c), out.view, n)
+    b.commit_and_wait()
+    rel_close(out.read(np.float16), orc.gelu_mul(a, c).astype(np.float32), 2e-3, "gelu_mul")
+    out = Guarded(la, ctx, n * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.residual_add_into(b, dev(la, ctx, a), dev(la, ctx, c), out.view, n)
+    b.commit_and_wait()
+    assert np.array_equal(out.read(np.uint16), orc.residual_add(a, c).view(np.uint16))
+    buf = dev(la, ctx, a)
+    b = la.CommandBatch.new(ctx)
+    kernels.scale_in_place_gpu_into(b, buf, float(np.sqrt(np.float32(1536))), n)
+    b.commit_and_wait()
+    assert np.array_equal(buf.as_slice(np.uint16), orc.scale_in_place(a, float(np.sqrt(np.float32(1536)))).view(np.uint16))
+    logits = (la.synth.normal(10, 5000) * 40).astype(np.float32)
+    buf = dev(la, ctx, logits)
+    b = la.CommandBatch.new(ctx)
+    kernels.logit_softcap_gpu_into(b, buf, 30.0, logits.size)
+    b.commit_and_wait()
+    rel_close(buf.as_slice(np.float32), orc.logit_softcap(logits, 30.0), 1e-5, "logit_softcap")
+
+
+def test_gather_strided(la, orc, ctx, kernels):
+    n_rows, n_layer, pld, layer = 7, 5, 256, 3
+    src = la.synth.normal_f16((n_rows, n_layer * pld), 11)
+    out = Guarded(la, ctx, n_rows * pld * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.gather_strided_f16_into(b, dev(la, ctx, src), out.view, n_layer * pld, layer * pld, pld, n_rows)
+    b.commit_and_wait()
+    assert np.array_equal(out.read(np.uint16), orc.gather_strided_f16(src, n_layer * pld, layer * pld, pld, n_rows).view(np.uint16))
+
+
+def test_embed_rows_and_argmax(la, orc, ctx, kernels):
+    vocab, cols = 1000, 1536
+    table = la.synth.q4_0_weights(vocab, cols, 12)
+    tokens = np.array([0, 999, 5, 5, 123], np.uint32)
+    out = Guarded(la, ctx, tokens.size * cols * 2)
+    b = la.CommandBatch.new(ctx)
+    scale = float(np.sqrt(np.float32(cols)))
+    kernels.embed_rows_q4_0_into(b, dev(la, ctx, table), dev(la, ctx, tokens), out.view, tokens.size, cols, vocab, scale)
+    b.commit_and_wait()
+    want = orc.scale_in_place(orc.embed_rows_q4_0(table, tokens, cols), scale)
+    assert np.array_equal(out.read(np.uint16), want.view(np.uint16))
+    rows, n = 6, 262144
+    v = la.synth.normal(13, rows * n).astype(np.float32).reshape(rows, n)
+    v[1, 1000] = v[1, 200000] = 99.0      # tie: the first index wins
+    v[2, :] = -np.inf                      # nothing beats -inf: index 0
+    v[3, n - 1] = 77.0
+    oi = Guarded(la, ctx, rows * 4)
+    b = la.CommandBatch.new(ctx)
+    kernels.argmax_rows_f32_into(b, dev(la, ctx, v), oi.view, rows, n)
+    b.commit_and_wait()
+    got = oi.read(np.uint32)
+    assert got.tolist() == [orc.argmax(v[r]) for r in range(rows)]
+    assert got[1] == 1000 and got[2] == 0 and got[3] == n - 1
