@@ -278,6 +278,23 @@ LC_API int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf
                                         uint32_t num_kv_heads, uint32_t window, uint32_t bits,
                                         uint32_t n_lanes, uint32_t ring_capacity, float softmax_scale);
 
+/* No counterpart in the reference.  lc_tq_attention_into for callers that must not
+ * allocate device memory when they run attention (an HBM budget fully handed to the KV
+ * pool, a latency-critical serving loop, host code inside a stream capture): the split-K
+ * partials live in a 4 MiB array built into the library instead of the cudaMalloc'ed
+ * scratch of `lc_kernels`, so no `lc_kernels` is needed and nothing is allocated or freed.
+ * Limit: num_q_heads * (head_dim + 2) * 4 bytes per split must fit in 4 MiB (the split count
+ * is lowered to fit, else LC_ERR_INVALID_ARGUMENT).  All calls share the array: calls that
+ * overlap on the GPU race, so keep them on one stream.  The first call on each device
+ * resolves the array's address and should be made before any stream capture. */
+LC_API int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const lc_buf *k_codes,
+                                        const lc_buf *k_norms, const lc_buf *v_codes,
+                                        const lc_buf *v_norms, const lc_buf *levels, const lc_buf *signs,
+                                        lc_buf *attn_out, uint32_t head_dim, uint32_t kv_len,
+                                        uint32_t current_pos, uint32_t num_q_heads, uint32_t num_kv_heads,
+                                        uint32_t window, uint32_t bits, uint32_t ring_capacity,
+                                        float softmax_scale);
+
 /* ---------------------------------------------------- FP16-KV attention -- */
 /* K/V f16 [kv_len, n_kv, hd]; q, output f16 [n_q, hd]; softmax scale 1.0 as in the shaders. */
 LC_API uint32_t lc_flash_split_count(const lc_kernels *k, uint32_t eff_seq_len);    /* kernels.rs:1265 */

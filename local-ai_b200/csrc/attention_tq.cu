@@ -473,3 +473,144 @@ int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *q, co
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of lc_tq_attention_into.
+//
+// Some callers of this library must not allocate device memory at the moment
+// they run attention: a serving thread that has handed every spare byte of HBM
+// to its KV pool, a latency-critical loop where cudaMalloc's implicit device
+// synchronisation is unacceptable, or host code that is running between
+// cudaStreamBeginCapture / EndCapture, where cudaMalloc is illegal.  The regular
+// entry point keeps its split-K partials in a buffer that the `lc_kernels`
+// object grows with cudaMalloc on demand; this one keeps them in the fixed
+// array below, which is part of the library image: every GPU that loads the
+// library holds these 4 MiB until the process exits.
+//
+// Rules that follow from sharing one array:
+//  * the partials of a call must fit: num_q_heads * splits * (head_dim + 2)
+//    floats <= LC_NOALLOC_SCRATCH_FLOATS.  The split count is lowered to fit;
+//    if even one split does not fit the call is refused with a status.
+//  * nothing in the array has to start at zero: every slot the merge kernel
+//    reads is written by the split kernel earlier in the same call, so stale
+//    contents of the previous call are never observed;
+//  * two calls that overlap on the GPU (different streams, or two host threads)
+//    race on the array.  Issue them on one stream, or serialise them.
+//  * the first call on each device looks up the array's device address
+//    (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make
+//    that first call before any stream capture begins.
+constexpr size_t LC_NOALLOC_SCRATCH_FLOATS = (size_t)1 << 20;  // 4 MiB
+static __device__ __align__(256) float g_noalloc_scratch[LC_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float *g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of g_noalloc_scratch, per device
+
+// The array's name is a host-side stand-in here, not a device address: resolve
+// it once per device, with that device current.
+int noalloc_scratch_for(int device, float **out) {
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "tq_attention_noalloc: device %d out of range", device);
+    if (!g_noalloc_ptr[device]) {
+        LC_CUDA_TRY(cudaSetDevice(device));
+        float *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr)
+            return lc_fail(LC_ERR_CUDA, "tq_attention_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[device] = ptr;
+    }
+    *out = g_noalloc_ptr[device];
+    return LC_OK;
+}
+
+}  // namespace
+
+extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const lc_buf *k_codes,
+                                            const lc_buf *k_norms, const lc_buf *v_codes, const lc_buf *v_norms,
+                                            const lc_buf *levels, const lc_buf *signs, lc_buf *attn_out,
+                                            uint32_t head_dim, uint32_t kv_len, uint32_t current_pos,
+                                            uint32_t num_q_heads, uint32_t num_kv_heads, uint32_t window,
+                                            uint32_t bits, uint32_t ring_capacity, float softmax_scale) {
+    const char *name = "tq_attention_noalloc";
+    if (!b || !q || !k_codes || !k_norms || !v_codes || !v_norms || !levels || !signs || !attn_out)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    if (bits < 2 || bits > 4) return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: bits %u not in 2..=4", name, bits);
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256 && head_dim != 512)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: head_dim %u must be 64, 128, 256 or 512", name, head_dim);
+    LC_REQUIRE(num_kv_heads >= 1 && num_q_heads >= 1 && num_q_heads % num_kv_heads == 0,
+               "%s: num_q_heads %u must be a multiple of num_kv_heads %u", name, num_q_heads, num_kv_heads);
+    const size_t cb = (size_t)head_dim * bits / 8, qn = (size_t)num_q_heads * head_dim;
+    LC_REQUIRE(q->bytes >= qn * 2 && attn_out->bytes >= qn * 2, "%s: query/output buffers too small", name);
+    LC_REQUIRE(levels->bytes >= (4u << bits) && signs->bytes >= head_dim * 4u, "%s: codec buffers too small", name);
+    const uint32_t seq_len = kv_len < current_pos + 1 ? kv_len : current_pos + 1;
+    const size_t rows = ring_capacity ? (ring_capacity < seq_len ? ring_capacity : seq_len) : seq_len;
+    const uint32_t ws = (window > 0 && current_pos + 1 > window) ? current_pos + 1 - window : 0;
+    uint32_t len_max = seq_len > ws ? seq_len - ws : 0;
+    if (window > 0 && len_max > window) len_max = window;
+    LC_REQUIRE(k_codes->bytes >= rows * num_kv_heads * cb && v_codes->bytes >= rows * num_kv_heads * cb &&
+                   k_norms->bytes >= rows * num_kv_heads * 2 && v_norms->bytes >= rows * num_kv_heads * 2,
+               "%s: KV buffers hold fewer than %zu rows", name, rows);
+    LC_REQUIRE(lc_aligned(k_codes->dptr, 16) && lc_aligned(v_codes->dptr, 16),
+               "%s: code buffers must be 16-byte aligned", name);
+
+    const size_t per_split = qn / head_dim * (size_t)(head_dim + 2);  // floats of partials per split
+    if (per_split > LC_NOALLOC_SCRATCH_FLOATS)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT,
+                       "%s: %u heads of %u need %zu bytes of partials per split; the built-in scratch holds %zu bytes",
+                       name, num_q_heads, head_dim, per_split * sizeof(float), LC_NOALLOC_SCRATCH_FLOATS * sizeof(float));
+    float *scratch = nullptr;
+    int st = noalloc_scratch_for(b->ctx->device, &scratch);
+    if (st != LC_OK) return st;
+
+    const uint32_t group = num_q_heads / num_kv_heads;
+    const int g = group > 4 ? 8 : (group > 2 ? 4 : (group > 1 ? 2 : 1));
+    const uint32_t gchunks = (group + g - 1) / g;
+    const uint32_t base = num_kv_heads * gchunks;
+    uint32_t n_splits = (2u * (uint32_t)b->ctx->sm_count + base - 1) / base;
+    uint32_t by_len = (len_max + NW * TILE - 1) / (NW * TILE);
+    if (by_len < 1) by_len = 1;
+    if (n_splits > by_len) n_splits = by_len;
+    if (n_splits > 64) n_splits = 64;
+    const uint32_t fit = (uint32_t)(LC_NOALLOC_SCRATCH_FLOATS / per_split);
+    if (n_splits > fit) n_splits = fit;
+    if (n_splits < 1) n_splits = 1;
+
+    TqAttnParams p;
+    p.rq = nullptr;
+    p.q = (const __half *)q->dptr;
+    p.signs = (const float *)signs->dptr;
+    p.kc = (const uint8_t *)k_codes->dptr;
+    p.vc = (const uint8_t *)v_codes->dptr;
+    p.kn = (const __half *)k_norms->dptr;
+    p.vn = (const __half *)v_norms->dptr;
+    p.levels = (const float *)levels->dptr;
+    p.out = nullptr;
+    p.partial = scratch;
+    p.positions = nullptr;
+    p.kv_len = kv_len;
+    p.current_pos = current_pos;
+    p.lane_capacity = 0;
+    p.n_q = num_q_heads;
+    p.n_kv = num_kv_heads;
+    p.window = window;
+    p.ring = ring_capacity;
+    p.n_splits = n_splits;
+    p.group = group;
+    p.fused_q = 1;
+    p.direct_out = 0;
+    p.scale = softmax_scale;
+    dim3 grid(n_splits, num_kv_heads * gchunks, 1);
+    switch (head_dim) {
+        case 64: st = launch_split_b<64>(b, p, grid, g, bits); break;
+        case 128: st = launch_split_b<128>(b, p, grid, g, bits); break;
+        case 256: st = launch_split_b<256>(b, p, grid, g, bits); break;
+        default: st = launch_split_b<512>(b, p, grid, g, bits); break;
+    }
+    if (st != LC_OK) return st;
+    tq_attn_merge_kernel<true><<<num_q_heads, head_dim, 0, b->stream>>>(scratch, (const float *)signs->dptr, nullptr,
+                                                                       (__half *)attn_out->dptr, head_dim, n_splits);
+    LC_CHECK_LAUNCH("tq_attention_noalloc merge");
+    b->dispatch_count++;
+    return LC_OK;
+}

@@ -294,3 +294,13 @@ def swa_ring_capacity(window: int, max_positions: int) -> int:
 
 
 TQ_SEED = 0x7459C0DE
+
+
+def tq_attention_noalloc_into(batch: CommandBatch, q, k_codes, k_norms, v_codes, v_norms, levels, signs, attn_out,
+                              head_dim, kv_len, current_pos, num_q_heads, num_kv_heads, window, bits, ring_capacity,
+                              softmax_scale) -> None:
+    """lc_tq_attention_noalloc_into: fused code-space attention whose split-K scratch is a fixed
+    array inside the library, for callers that cannot allocate device memory (no `Kernels` needed)."""
+    _check(_lib.load().lc_tq_attention_noalloc_into(
+        batch._h, q._h, k_codes._h, k_norms._h, v_codes._h, v_norms._h, levels._h, signs._h, attn_out._h,
+        head_dim, kv_len, current_pos, num_q_heads, num_kv_heads, window, bits, ring_capacity, softmax_scale))
