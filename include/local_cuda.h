@@ -280,7 +280,7 @@ LC_API int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf
 
 /* No counterpart in the reference.  lc_tq_attention_into for callers that must not
  * allocate device memory when they run attention (an HBM budget fully handed to the KV
- * pool, a latency-critical serving loop, host code inside a stream capture): the split-K
+ * pool, or a latency-critical serving loop that cannot take cudaMalloc's stall): the split-K
  * partials live in a 4 MiB array built into the library instead of the cudaMalloc'ed
  * scratch of `lc_kernels`, so no `lc_kernels` is needed and nothing is allocated or freed.
  * Limit: num_q_heads * (head_dim + 2) * 4 bytes per split must fit in 4 MiB (the split count

@@ -479,9 +479,8 @@ int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *q, co
 //
 // Some callers of this library must not allocate device memory at the moment
 // they run attention: a serving thread that has handed every spare byte of HBM
-// to its KV pool, a latency-critical loop where cudaMalloc's implicit device
-// synchronisation is unacceptable, or host code that is running between
-// cudaStreamBeginCapture / EndCapture, where cudaMalloc is illegal.  The regular
+// to its KV pool, or a latency-critical loop where cudaMalloc's implicit device
+// synchronisation is unacceptable.  The regular
 // entry point keeps its split-K partials in a buffer that the `lc_kernels`
 // object grows with cudaMalloc on demand; this one keeps them in the fixed
 // array below, which is part of the library image: every GPU that loads the
