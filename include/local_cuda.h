@@ -348,6 +348,46 @@ LC_API int lc_embed_rows_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *tab
 LC_API int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc_buf *out_index,
                                    uint32_t rows, uint32_t cols);
 
+/* ----------------------------------------------------------- decode step -- */
+/* One batched decode step of the dense decoder in the op order of
+ * TransformerLayer::forward_decode_batch_turbo (local-engine/src/layer.rs:731-868) inside
+ * Pipeline::decode_batch_step (local-engine/src/pipeline/batched.rs:271-456).  The model
+ * object owns the per-lane KV pools (QuantizedUnifiedKvPool, kv_cache/quant_unified_pool.rs:33-181)
+ * and the scratch (BatchScratch, layer.rs:960-1036); weights are borrowed buffers that must
+ * outlive it.  Layer i is a full-attention layer iff i % full_every == full_every - 1 (or
+ * swa_window == 0), otherwise a sliding-window layer with a ring of swa_ring rows
+ * (0 = swa_ring_capacity(window, max_context)). */
+typedef struct lc_model lc_model;
+typedef struct lc_model_config {
+    uint32_t hidden, n_q_heads, n_kv_heads, head_dim, inter, vocab, n_layers, kv_bits;
+    uint32_t max_lanes, max_context, swa_window, swa_ring, full_every;
+    float rms_eps, rope_theta, softmax_scale, embed_scale;
+} lc_model_config;
+
+LC_API int lc_model_create(lc_ctx *ctx, lc_kernels *k, const lc_model_config *cfg, lc_model **out);
+LC_API void lc_model_destroy(lc_model *m);
+/* TQ2_0 projections [out, in] and f16 norm weights of one layer (LayerWeights, layer.rs:284-352). */
+LC_API int lc_model_set_layer(lc_model *m, uint32_t layer, const lc_buf *wq, const lc_buf *wk,
+                              const lc_buf *wv, const lc_buf *wo, const lc_buf *wgate, const lc_buf *wup,
+                              const lc_buf *wdown, const lc_buf *attn_norm, const lc_buf *q_norm,
+                              const lc_buf *k_norm, const lc_buf *post_attn_norm, const lc_buf *ffn_norm,
+                              const lc_buf *post_ffn_norm);
+/* Q4_0 [vocab, hidden] table, tied with the output projection, and the final norm. */
+LC_API int lc_model_set_embedding(lc_model *m, const lc_buf *embed_q4_0, const lc_buf *final_norm);
+/* The pool buffers of a layer (owned by the model), for prefill / snapshots / tests. */
+LC_API int lc_model_kv_buffers(lc_model *m, uint32_t layer, lc_buf **k_codes, lc_buf **k_norms,
+                               lc_buf **v_codes, lc_buf **v_norms, uint32_t *lane_rows, uint32_t *ring,
+                               uint32_t *window);
+LC_API int lc_model_logits_buffer(lc_model *m, lc_buf **logits);   /* f32 [max_lanes, vocab] */
+LC_API int lc_model_hidden_buffer(lc_model *m, lc_buf **hidden);   /* f16 [max_lanes, hidden]: final normed rows */
+LC_API int lc_model_reset_lane(lc_model *m, uint32_t lane);         /* quant_unified_pool.rs:316-346 */
+/* tokens, positions: u32 [n_lanes] device buffers.  want_logits != 0 or next_tokens != NULL runs the
+ * vocabulary projection into the model's logits buffer; next_tokens (u32 [n_lanes]) receives the
+ * greedy first-max argmax. */
+LC_API int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *tokens,
+                                           const lc_buf *positions, uint32_t n_lanes, uint32_t want_logits,
+                                           lc_buf *next_tokens);                    /* batched.rs:271 */
+
 #ifdef __cplusplus
 }
 #endif

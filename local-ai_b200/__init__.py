@@ -23,3 +23,5 @@ from .kernels import (  # noqa: F401
     tq_signs,
 )
 from . import synth  # noqa: F401
+from . import model  # noqa: F401
+from .model import DecodeModel, ModelConfig, e2b_like_config  # noqa: F401

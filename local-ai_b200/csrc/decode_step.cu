@@ -1,0 +1,247 @@
+// One batched decode step of the dense decoder, composed from the kernels of
+// this library in the op order of TransformerLayer::forward_decode_batch_turbo
+// (local-engine/src/layer.rs:731-868) inside Pipeline::decode_batch_step
+// (local-engine/src/pipeline/batched.rs:271-456):
+//
+//   embed gather (device-side) -> * sqrt(hidden)
+//   per layer: rms_norm -> Q -> q_norm -> rope | K, V -> k_norm, v rms_norm(ones) -> rope(K)
+//              -> KV encode into the per-lane pool -> attention over codes (rotate, attend, rotate back)
+//              -> O -> rms_norm_add -> rms_norm -> gate, up -> gelu_mul -> down -> rms_norm_add
+//   final rms_norm -> vocabulary projection (all lanes in one pass) -> optional greedy argmax
+//
+// Everything between ops is f16, as the reference's scratch buffers are
+// (layer.rs:873-1036).  The model object owns the KV pools (QuantizedUnifiedKvPool,
+// kv_cache/quant_unified_pool.rs:33-181: [n_lanes, lane_rows, n_kv, code_bytes] with
+// lane_rows = ring capacity on sliding-window layers) and the scratch; weights are
+// borrowed buffers.  The whole step can be captured into one CUDA graph.
+#include <math.h>
+#include <vector>
+
+#include "lc_internal.h"
+
+struct lc_model_layer {
+    const lc_buf *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr,
+                 *wdown = nullptr;
+    const lc_buf *attn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *post_attn_norm = nullptr,
+                 *ffn_norm = nullptr, *post_ffn_norm = nullptr;
+    lc_buf *k_codes = nullptr, *k_norms = nullptr, *v_codes = nullptr, *v_norms = nullptr;
+    uint32_t window = 0, ring = 0, lane_rows = 0;
+};
+
+struct lc_model {
+    lc_ctx *ctx = nullptr;
+    lc_kernels *k = nullptr;
+    lc_model_config cfg;
+    std::vector<lc_model_layer> layers;
+    const lc_buf *embed = nullptr, *final_norm = nullptr;
+    lc_buf *levels = nullptr, *signs = nullptr, *ones = nullptr;
+    lc_buf *x = nullptr, *x2 = nullptr, *normed = nullptr, *q = nullptr, *kbuf = nullptr, *vbuf = nullptr,
+           *attn = nullptr, *resid = nullptr, *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
+    std::vector<lc_buf *> owned;
+};
+
+namespace {
+
+int alloc(lc_model *m, size_t bytes, lc_buf **out) {
+    int st = lc_buf_alloc(m->ctx, bytes, out);
+    if (st == LC_OK) m->owned.push_back(*out);
+    return st;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lc_model_create(lc_ctx *ctx, lc_kernels *k, const lc_model_config *cfg, lc_model **out) {
+    if (!ctx || !k || !cfg || !out) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_create: NULL argument");
+    *out = nullptr;
+    const lc_model_config &c = *cfg;
+    LC_REQUIRE(c.hidden % 256 == 0 && c.inter % 256 == 0 && (c.n_q_heads * c.head_dim) % 256 == 0,
+               "lc_model_create: hidden, inter and n_q*head_dim must be multiples of 256 (TQ2_0 blocks)");
+    LC_REQUIRE(c.n_kv_heads >= 1 && c.n_q_heads % c.n_kv_heads == 0, "lc_model_create: n_q_heads %% n_kv_heads != 0");
+    LC_REQUIRE(c.kv_bits >= 2 && c.kv_bits <= 4, "lc_model_create: kv_bits %u not in 2..=4", c.kv_bits);
+    LC_REQUIRE(c.n_layers >= 1 && c.max_lanes >= 1 && c.max_context >= 1 && c.full_every >= 1,
+               "lc_model_create: empty model");
+    LC_REQUIRE(c.swa_ring == 0 || c.swa_ring >= c.swa_window, "lc_model_create: ring %u smaller than window %u",
+               c.swa_ring, c.swa_window);
+    lc_model *m = new lc_model();
+    m->ctx = ctx;
+    m->k = k;
+    m->cfg = c;
+    m->layers.resize(c.n_layers);
+    const size_t cb = lc_tq_code_bytes(c.head_dim, c.kv_bits);
+    int st = LC_OK;
+    auto fail = [&](int s) {
+        lc_model_destroy(m);
+        return s;
+    };
+    for (uint32_t i = 0; i < c.n_layers; i++) {
+        lc_model_layer &L = m->layers[i];
+        const bool full = (i % c.full_every) == c.full_every - 1 || c.swa_window == 0;
+        L.window = full ? 0 : c.swa_window;
+        L.ring = full ? 0 : (c.swa_ring ? c.swa_ring : (uint32_t)lc_swa_ring_capacity(c.swa_window, c.max_context));
+        if (L.ring > c.max_context) L.ring = 0, L.window = c.swa_window;  // window never fills: absolute rows
+        L.lane_rows = L.ring ? L.ring : c.max_context;
+        const size_t rows = (size_t)c.max_lanes * L.lane_rows * c.n_kv_heads;
+        if ((st = alloc(m, rows * cb, &L.k_codes)) || (st = alloc(m, rows * cb, &L.v_codes)) ||
+            (st = alloc(m, rows * 2, &L.k_norms)) || (st = alloc(m, rows * 2, &L.v_norms)))
+            return fail(st);
+    }
+    // codec constants (TurboQuant::new, turboquant.rs:187-199; seed quant_cache.rs:30)
+    std::vector<float> lv(1u << c.kv_bits), sg(c.head_dim);
+    lc_tq_levels(c.head_dim, c.kv_bits, lv.data());
+    lc_tq_signs(c.head_dim, LC_TQ_SEED, sg.data());
+    std::vector<__half> ones(c.head_dim, __float2half(1.0f));
+    if ((st = alloc(m, lv.size() * 4, &m->levels)) || (st = alloc(m, sg.size() * 4, &m->signs)) ||
+        (st = alloc(m, ones.size() * 2, &m->ones)))
+        return fail(st);
+    if ((st = lc_buf_upload(m->levels, 0, lv.data(), lv.size() * 4)) ||
+        (st = lc_buf_upload(m->signs, 0, sg.data(), sg.size() * 4)) ||
+        (st = lc_buf_upload(m->ones, 0, ones.data(), ones.size() * 2)))
+        return fail(st);
+    const size_t n = c.max_lanes, qd = (size_t)c.n_q_heads * c.head_dim, kd = (size_t)c.n_kv_heads * c.head_dim;
+    if ((st = alloc(m, n * c.hidden * 2, &m->x)) || (st = alloc(m, n * c.hidden * 2, &m->x2)) ||
+        (st = alloc(m, n * c.hidden * 2, &m->normed)) || (st = alloc(m, n * qd * 2, &m->q)) ||
+        (st = alloc(m, n * kd * 2, &m->kbuf)) || (st = alloc(m, n * kd * 2, &m->vbuf)) ||
+        (st = alloc(m, n * qd * 2, &m->attn)) || (st = alloc(m, n * c.hidden * 2, &m->resid)) ||
+        (st = alloc(m, n * c.inter * 2, &m->gate)) || (st = alloc(m, n * c.inter * 2, &m->up)) ||
+        (st = alloc(m, n * c.hidden * 2, &m->ffn)) || (st = alloc(m, n * (size_t)c.vocab * 4, &m->logits)))
+        return fail(st);
+    *out = m;
+    return LC_OK;
+}
+
+void lc_model_destroy(lc_model *m) {
+    if (!m) return;
+    for (lc_buf *b : m->owned) lc_buf_free(b);
+    delete m;
+}
+
+int lc_model_set_layer(lc_model *m, uint32_t layer, const lc_buf *wq, const lc_buf *wk, const lc_buf *wv,
+                       const lc_buf *wo, const lc_buf *wgate, const lc_buf *wup, const lc_buf *wdown,
+                       const lc_buf *attn_norm, const lc_buf *q_norm, const lc_buf *k_norm,
+                       const lc_buf *post_attn_norm, const lc_buf *ffn_norm, const lc_buf *post_ffn_norm) {
+    if (!m || layer >= m->layers.size()) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_set_layer: bad layer");
+    if (!wq || !wk || !wv || !wo || !wgate || !wup || !wdown || !attn_norm || !q_norm || !k_norm || !post_attn_norm ||
+        !ffn_norm || !post_ffn_norm)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_set_layer: NULL tensor");
+    const lc_model_config &c = m->cfg;
+    const size_t qd = (size_t)c.n_q_heads * c.head_dim, kd = (size_t)c.n_kv_heads * c.head_dim;
+    auto tq = [](size_t rows, size_t cols) { return rows * (cols / 256) * 66; };
+    LC_REQUIRE(wq->bytes >= tq(qd, c.hidden) && wk->bytes >= tq(kd, c.hidden) && wv->bytes >= tq(kd, c.hidden) &&
+                   wo->bytes >= tq(c.hidden, qd) && wgate->bytes >= tq(c.inter, c.hidden) &&
+                   wup->bytes >= tq(c.inter, c.hidden) && wdown->bytes >= tq(c.hidden, c.inter),
+               "lc_model_set_layer: a TQ2_0 tensor is smaller than its shape");
+    LC_REQUIRE(attn_norm->bytes >= c.hidden * 2u && post_attn_norm->bytes >= c.hidden * 2u &&
+                   ffn_norm->bytes >= c.hidden * 2u && post_ffn_norm->bytes >= c.hidden * 2u &&
+                   q_norm->bytes >= c.head_dim * 2u && k_norm->bytes >= c.head_dim * 2u,
+               "lc_model_set_layer: a norm weight is smaller than its shape");
+    lc_model_layer &L = m->layers[layer];
+    L.wq = wq; L.wk = wk; L.wv = wv; L.wo = wo; L.wgate = wgate; L.wup = wup; L.wdown = wdown;
+    L.attn_norm = attn_norm; L.q_norm = q_norm; L.k_norm = k_norm; L.post_attn_norm = post_attn_norm;
+    L.ffn_norm = ffn_norm; L.post_ffn_norm = post_ffn_norm;
+    return LC_OK;
+}
+
+int lc_model_set_embedding(lc_model *m, const lc_buf *embed_q4_0, const lc_buf *final_norm) {
+    if (!m || !embed_q4_0 || !final_norm) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_set_embedding: NULL argument");
+    LC_REQUIRE(embed_q4_0->bytes >= (size_t)m->cfg.vocab * (m->cfg.hidden / 32) * 18 &&
+                   final_norm->bytes >= m->cfg.hidden * 2u,
+               "lc_model_set_embedding: tensor smaller than its shape");
+    m->embed = embed_q4_0;
+    m->final_norm = final_norm;
+    return LC_OK;
+}
+
+int lc_model_kv_buffers(lc_model *m, uint32_t layer, lc_buf **k_codes, lc_buf **k_norms, lc_buf **v_codes,
+                        lc_buf **v_norms, uint32_t *lane_rows, uint32_t *ring, uint32_t *window) {
+    if (!m || layer >= m->layers.size()) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_kv_buffers: bad layer");
+    lc_model_layer &L = m->layers[layer];
+    if (k_codes) *k_codes = L.k_codes;
+    if (k_norms) *k_norms = L.k_norms;
+    if (v_codes) *v_codes = L.v_codes;
+    if (v_norms) *v_norms = L.v_norms;
+    if (lane_rows) *lane_rows = L.lane_rows;
+    if (ring) *ring = L.ring;
+    if (window) *window = L.window;
+    return LC_OK;
+}
+
+int lc_model_logits_buffer(lc_model *m, lc_buf **logits) {
+    if (!m || !logits) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_logits_buffer: NULL argument");
+    *logits = m->logits;
+    return LC_OK;
+}
+
+int lc_model_hidden_buffer(lc_model *m, lc_buf **hidden) {
+    if (!m || !hidden) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_hidden_buffer: NULL argument");
+    *hidden = m->normed;
+    return LC_OK;
+}
+
+// QuantizedUnifiedKvPool::reset_lane (quant_unified_pool.rs:316-346): zero one lane's rows in every layer
+// ("a zero norm annihilates the row").
+int lc_model_reset_lane(lc_model *m, uint32_t lane) {
+    if (!m || lane >= m->cfg.max_lanes) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_model_reset_lane: bad lane");
+    const size_t cb = lc_tq_code_bytes(m->cfg.head_dim, m->cfg.kv_bits);
+    for (lc_model_layer &L : m->layers) {
+        const size_t rows = (size_t)L.lane_rows * m->cfg.n_kv_heads;
+        int st;
+        if ((st = lc_buf_zero(L.k_codes, lane * rows * cb, rows * cb)) || (st = lc_buf_zero(L.v_codes, lane * rows * cb, rows * cb)) ||
+            (st = lc_buf_zero(L.k_norms, lane * rows * 2, rows * 2)) || (st = lc_buf_zero(L.v_norms, lane * rows * 2, rows * 2)))
+            return st;
+    }
+    return LC_OK;
+}
+
+int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *tokens, const lc_buf *positions,
+                                    uint32_t n_lanes, uint32_t want_logits, lc_buf *next_tokens) {
+    if (!m || !b || !tokens || !positions) return lc_fail(LC_ERR_INVALID_ARGUMENT, "decode_batch_step: NULL argument");
+    const lc_model_config &c = m->cfg;
+    LC_REQUIRE(n_lanes >= 1 && n_lanes <= c.max_lanes, "decode_batch_step: n_lanes %u not in 1..=%u", n_lanes, c.max_lanes);
+    LC_REQUIRE(m->embed && m->final_norm, "decode_batch_step: embedding not set");
+    for (const lc_model_layer &L : m->layers) LC_REQUIRE(L.wq, "decode_batch_step: a layer has no weights");
+    lc_kernels *k = m->k;
+    const uint32_t H = c.hidden, HD = c.head_dim, NQ = c.n_q_heads, NKV = c.n_kv_heads, I = c.inter, n = n_lanes;
+    const uint32_t qd = NQ * HD, kd = NKV * HD;
+    int st;
+#define STEP(call) do { if ((st = (call)) != LC_OK) return st; } while (0)
+    STEP(lc_embed_rows_q4_0_into(k, b, m->embed, tokens, m->x, n, H, c.vocab, c.embed_scale));
+    lc_buf *x = m->x, *xn = m->x2;
+    for (lc_model_layer &L : m->layers) {
+        STEP(lc_rms_norm_into(k, b, x, L.attn_norm, m->normed, H, n, c.rms_eps));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wq, m->q, n, H, qd));
+        STEP(lc_qk_norm_gpu_into(k, b, m->q, L.q_norm, HD, n * NQ, c.rms_eps));
+        STEP(lc_rope_batch_decode_into(k, b, m->q, positions, c.rope_theta, HD, NQ, n, 1.0f));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wk, m->kbuf, n, H, kd));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wv, m->vbuf, n, H, kd));
+        STEP(lc_qk_norm_gpu_into(k, b, m->kbuf, L.k_norm, HD, n * NKV, c.rms_eps));
+        STEP(lc_rms_norm_into(k, b, m->vbuf, m->ones, m->vbuf, HD, n * NKV, c.rms_eps));
+        STEP(lc_rope_batch_decode_into(k, b, m->kbuf, positions, c.rope_theta, HD, NKV, n, 1.0f));
+        STEP(lc_encode_kv_turboquant_batched_into(k, b, m->kbuf, m->levels, m->signs, L.k_codes, L.k_norms, positions,
+                                                  HD, NKV, L.lane_rows, c.kv_bits, n, L.ring));
+        STEP(lc_encode_kv_turboquant_batched_into(k, b, m->vbuf, m->levels, m->signs, L.v_codes, L.v_norms, positions,
+                                                  HD, NKV, L.lane_rows, c.kv_bits, n, L.ring));
+        STEP(lc_tq_attention_batched_into(k, b, m->q, L.k_codes, L.k_norms, L.v_codes, L.v_norms, m->levels, m->signs,
+                                          m->attn, positions, HD, L.lane_rows, NQ, NKV, L.window, c.kv_bits, n, L.ring,
+                                          c.softmax_scale));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->attn, L.wo, m->ffn, n, qd, H));
+        STEP(lc_rms_norm_add_into(k, b, m->ffn, L.post_attn_norm, x, m->resid, H, n, c.rms_eps));
+        STEP(lc_rms_norm_into(k, b, m->resid, L.ffn_norm, m->normed, H, n, c.rms_eps));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wgate, m->gate, n, H, I));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wup, m->up, n, H, I));
+        STEP(lc_gelu_mul_into(k, b, m->gate, m->up, m->gate, n * I));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, m->gate, L.wdown, m->ffn, n, I, H));
+        STEP(lc_rms_norm_add_into(k, b, m->ffn, L.post_ffn_norm, m->resid, xn, H, n, c.rms_eps));
+        lc_buf *t = x; x = xn; xn = t;
+    }
+    STEP(lc_rms_norm_into(k, b, x, m->final_norm, m->normed, H, n, c.rms_eps));
+    if (want_logits || next_tokens) {
+        STEP(lc_matmul_nt_q4_0_f32out_into(k, b, m->normed, m->embed, m->logits, n, H, c.vocab));
+        if (next_tokens) STEP(lc_argmax_rows_f32_into(k, b, m->logits, next_tokens, n, c.vocab));
+    }
+#undef STEP
+    return LC_OK;
+}
+
+}  // extern "C"

@@ -280,3 +280,63 @@ def embed_rows_q4_0(table, tokens, cols) -> np.ndarray:
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+# ---- decode step (composition) ----
+class _OrcLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "attn_norm", "q_norm", "k_norm",
+                                          "post_attn_norm", "ffn_norm", "post_ffn_norm", "k_codes", "v_codes", "k_norms",
+                                          "v_norms")] + [(n, C.c_uint32) for n in ("window", "ring", "lane_rows")]
+
+
+class _OrcModel(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("hidden", "n_q", "n_kv", "hd", "inter", "vocab", "n_layers", "bits")] + \
+               [(n, C.c_float) for n in ("eps", "rope_theta", "softmax_scale", "embed_scale")] + \
+               [(n, C.c_void_p) for n in ("embed", "final_norm", "levels", "signs", "layers")]
+
+
+class OracleModel:
+    """Host-memory twin of the decode-step model: same weights, its own KV pools."""
+
+    def __init__(self, cfg, layers: list, embed, final_norm, pool_geometry: list):
+        """cfg: any object with the lc_model_config field names; layers: list of dicts of numpy tensors;
+        pool_geometry: per layer (lane_rows, ring, window)."""
+        self.cfg = cfg
+        self.keep = []
+        self.levels, self.signs = tq_levels(cfg.head_dim, cfg.kv_bits), tq_signs(cfg.head_dim, 0x7459C0DE)
+        cb = tq_code_bytes(cfg.head_dim, cfg.kv_bits)
+        arr = (_OrcLayer * cfg.n_layers)()
+        self.pools = []
+        for i, (t, (lane_rows, ring, window)) in enumerate(zip(layers, pool_geometry)):
+            rows = cfg.max_lanes * lane_rows * cfg.n_kv_heads
+            pool = {"k_codes": np.zeros(rows * cb, np.uint8), "v_codes": np.zeros(rows * cb, np.uint8),
+                    "k_norms": np.zeros(rows, np.float16), "v_norms": np.zeros(rows, np.float16)}
+            self.pools.append(pool)
+            for name in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown"):
+                a = _c(t[name], np.uint8)
+                self.keep.append(a)
+                setattr(arr[i], name, a.ctypes.data)
+            for name in ("attn_norm", "q_norm", "k_norm", "post_attn_norm", "ffn_norm", "post_ffn_norm"):
+                a = _h(t[name])
+                self.keep.append(a)
+                setattr(arr[i], name, a.ctypes.data)
+            for name in ("k_codes", "v_codes", "k_norms", "v_norms"):
+                setattr(arr[i], name, pool[name].ctypes.data)
+            arr[i].window, arr[i].ring, arr[i].lane_rows = window, ring, lane_rows
+        self.layer_arr = arr
+        self.embed, self.final_norm = _c(embed, np.uint8), _h(final_norm)
+        self.m = _OrcModel(hidden=cfg.hidden, n_q=cfg.n_q_heads, n_kv=cfg.n_kv_heads, hd=cfg.head_dim, inter=cfg.inter,
+                           vocab=cfg.vocab, n_layers=cfg.n_layers, bits=cfg.kv_bits, eps=cfg.rms_eps,
+                           rope_theta=cfg.rope_theta, softmax_scale=cfg.softmax_scale, embed_scale=cfg.embed_scale,
+                           embed=self.embed.ctypes.data, final_norm=self.final_norm.ctypes.data,
+                           levels=self.levels.ctypes.data, signs=self.signs.ctypes.data,
+                           layers=C.addressof(arr))
+
+    def decode_batch_step(self, tokens, positions, want_logits=True, norm_mode=0):
+        tokens, positions = _c(tokens, np.uint32), _c(positions, np.uint32)
+        n = tokens.size
+        logits = np.empty((n, self.cfg.vocab), np.float32) if want_logits else None
+        hidden = np.empty((n, self.cfg.hidden), np.uint16)
+        lib().orc_decode_batch_step(C.byref(self.m), _p(tokens), _p(positions), _u(n),
+                                    _p(logits) if want_logits else None, _p(hidden), C.c_int(norm_mode))
+        return logits, hidden.view(np.float16)
