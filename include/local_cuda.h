@@ -122,6 +122,10 @@ LC_API void lc_host_free(void *ptr);
 LC_API int lc_kernels_create(lc_ctx *ctx, lc_kernels **out);
 LC_API void lc_kernels_destroy(lc_kernels *k);
 
+/* Device-side status word: kernels that wait on hardware barriers bound every wait and record
+ * a non-zero value here instead of hanging.  Returns LC_ERR_TIMEOUT when it is set. */
+LC_API int lc_kernels_device_status(lc_kernels *k, int *status);
+
 /* Quantized matvec: output[rows] = matrix[rows, cols] x vector[cols], f16 input,
  * f32 accumulate.  matrix holds verbatim GGUF blocks (Q4_0: 18 B / 32 weights,
  * cols % 32 == 0; TQ2_0: 66 B / 256 weights, cols % 256 == 0), else

@@ -1,8 +1,436 @@
-// Tensor-core (tcgen05) path of the quantized batched matmul. Placeholder until
-// the kernel lands: reports "shape not covered" so routing uses the CUDA-core path.
+// Tensor-core (tcgen05 + TMEM) path of the quantized batched matmul
+//   C[m, n] = A[m, K] (f16) x W[n, K]^T,  W in GGUF Q4_0 / TQ2_0 blocks.
+// Stands in for the reference's simdgroup-matrix kernels matmul_nt_{q4_0,tq2_0}_mma
+// (shaders/matvec_quant.metal:447-577) for m > 8.
+//
+// Mapping.  The weights take the MMA's M dimension and the batch its N dimension:
+//   D[128 weight rows, NB batch rows] (f32, TMEM) += Wdeq[128, 16] * Act[NB, 16]^T
+// (tcgen05.mma.cta_group::1.kind::f16, both operands K-major in shared memory,
+// no-swizzle "interleave" layout: 8x16-byte core matrices, SBO = 128 B between
+// 8-row groups, LBO between 8-element k-chunks).  One CTA owns a 128-row weight tile and up to
+// 128 batch rows, and walks K in phases:
+//   1. the phase's raw weight bytes — for each of the 128 rows one contiguous run
+//      of blocks — are copied HBM -> shared with 16-byte cp.async (rows are only
+//      2-byte aligned, so each run is copied as its enclosing 16-byte range);
+//   2. per 128-wide k-tile: the activations are cp.async'ed straight into the
+//      operand layout, the weights are unpacked with the 0x6400 magic-number
+//      trick (two codes per 32-bit op) into f16 and stored into the operand
+//      layout, then one thread issues eight K=16 MMAs and commits them to an
+//      mbarrier; the two operand stages alternate so unpacking of tile t+1
+//      overlaps the MMAs of tile t.
+// The epilogue reads the accumulator with tcgen05.ld (warp w <- TMEM lanes
+// 32w..32w+31, one weight row per thread) and stores C transposed.
+//
+// Numerics: TQ2_0 weights d*(q-1) in {-d, 0, d, 2d} are exact in f16, so the
+// result equals the CUDA-core path up to f32 summation order.  Q4_0 weights
+// d*(q-8) are rounded once to f16 (relative 2^-12), as the reference's own
+// half-precision MMA kernels do (matvec_quant.metal:590-798).
+//
+// Every wait on an mbarrier is bounded; on expiry the CTA records a status
+// word, skips to the TMEM release and returns.
 #include "lc_internal.h"
 
-int lc_qgemm_tcgen05(int, bool, lc_kernels *, lc_batch *, const lc_buf *, const lc_buf *, lc_buf *, uint32_t,
-                     uint32_t, uint32_t) {
-    return -1;
+namespace {
+
+constexpr int FMT_Q4_0 = 0;
+constexpr int FMT_TQ2_0 = 1;
+constexpr int NT = 256;
+constexpr int TILE_ROWS = 128;          // weight rows per CTA (UMMA M)
+constexpr int KT = 128;                 // k per operand stage
+constexpr int RAW_RS = 448;             // bytes reserved per row of raw blocks (<= 432 data + 15 skew)
+constexpr int A_SBO = 128;
+constexpr int A_LBO = TILE_ROWS * 16 + 32;   // +32 B: consecutive k-chunks land 8 banks apart
+constexpr int A_STAGE = (KT / 8) * A_LBO;
+constexpr int MAX_NB = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+template <int FMT> struct TcFmt;
+template <> struct TcFmt<FMT_Q4_0> { static constexpr int bytes = 18, elems = 32, phase_blocks = 24; };
+template <> struct TcFmt<FMT_TQ2_0> { static constexpr int bytes = 66, elems = 256, phase_blocks = 6; };
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
+}
+// Bounded wait; false on expiry.
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// K-major, no swizzle: start address, LBO (between k-chunks), SBO (between 8-row groups), version 1.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
+__device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
+
+struct TcParams {
+    const uint8_t *w;
+    size_t w_bytes;
+    const __half *x;
+    void *out;
+    int m, n, K, nb;       // nb = blocks per row
+    int NB;                // batch rows per CTA (multiple of 16, <= 128)
+    int nstage;            // operand stages (3 when they fit, else 2)
+    int tmem_cols;         // power of two >= max(32, NB)
+    int *status;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(addr) : "memory");
+}
+
+constexpr int N_UNPACK_WARPS = 16;
+constexpr int ROWS_PER_WARP = TILE_ROWS / N_UNPACK_WARPS;  // 8
+constexpr int NT2 = (N_UNPACK_WARPS + 1) * 32;              // + one warp: activation loads and MMA issue
+constexpr int MAX_STAGE = 3;
+
+// Warp-specialised pipeline, no CTA-wide barrier inside the k loop:
+//   warps 0..15 own 8 weight rows each: cp.async their raw blocks, unpack them into operand
+//               stage s, bring in one k-chunk of the activation tile (prefetched one tile ahead) and
+//               arrive on a_full[s];
+//   warp 16     waits for a_full[s], issues the eight K=16 MMAs of the tile and commits them to
+//               mma_done[s], which frees stage s.  Nothing waits on a commit younger than S tiles:
+//               the commit -> mbarrier latency is far longer than one tile of work.
+template <int FMT, typename OutT>
+__global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int BB = TcFmt<FMT>::bytes, BE = TcFmt<FMT>::elems, PB = TcFmt<FMT>::phase_blocks;
+    const int NB = p.NB, S = p.nstage;
+    const int B_LBO = NB * 16, B_STAGE = (KT / 8) * B_LBO;
+    uint8_t *raw = smem;                                   // [128][RAW_RS]
+    uint8_t *a_s = raw + TILE_ROWS * RAW_RS;               // [S][A_STAGE]
+    uint8_t *b_s = a_s + S * A_STAGE;                      // [S][B_STAGE]
+    uint64_t *a_full = reinterpret_cast<uint64_t *>(b_s + S * B_STAGE);  // [MAX_STAGE]
+    uint64_t *mma_done = a_full + MAX_STAGE;                            // [MAX_STAGE]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(mma_done + MAX_STAGE);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * TILE_ROWS, m0 = blockIdx.y * MAX_NB;
+    const size_t rb = (size_t)p.nb * BB;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    if (tid == 0) {
+        for (int i = 0; i < MAX_STAGE; i++) {
+            mbar_init(smem_u32(&a_full[i]), N_UNPACK_WARPS);
+            mbar_init(smem_u32(&mma_done[i]), 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+    const int nphases = (p.nb + PB - 1) / PB;
+    const int total_tiles = (p.nb * BE) / KT;
+
+    if (warp < N_UNPACK_WARPS) {
+        // =============================== unpack warps ===============================
+        const int r_base = warp * ROWS_PER_WARP;
+        int tile = 0;
+        bool dead = false;
+        // This warp also brings in k-chunk `warp` (8 k values) of every activation tile, one tile ahead:
+        // lane walks batch rows lane, lane + 32, ...  Element (mrow, chunk c) lives at c*B_LBO + 16*mrow.
+        const __half *x_lane = p.x + (size_t)(m0 + lane) * p.K + warp * 8;
+        const int rows_valid = p.m - m0;
+        auto load_b = [&](int tl) {
+            uint32_t dst = smem_u32(b_s + (tl % S) * B_STAGE) + (uint32_t)(warp * B_LBO + 16 * lane);
+            const __half *src = x_lane + (size_t)tl * KT;
+            for (int mrow = lane; mrow < NB; mrow += 32) {
+                const bool ok = mrow < rows_valid;
+                cp_async16(dst, ok ? (const void *)src : (const void *)p.x, ok ? 16u : 0u);
+                dst += 512;
+                src += (size_t)32 * p.K;
+            }
+        };
+        // Stage of tile tl is free once the MMAs of tile tl - S have completed.
+        auto stage_free = [&](int tl) -> bool {
+            if (tl < S) return true;
+            uint32_t ok = 1;
+            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[tl % S]), (uint32_t)(((tl / S) - 1) & 1)) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            return ok && !*abort_flag;
+        };
+        if (total_tiles > 0) load_b(0);
+        cp_async_commit();
+        for (int ph = 0; ph < nphases && !dead; ph++) {
+            const int kb0 = ph * PB, kb1 = min(p.nb, kb0 + PB);
+            const int seg = (kb1 - kb0) * BB;
+            __syncwarp();  // the previous phase's raw bytes are no longer being read by this warp
+            for (int rr = 0; rr < ROWS_PER_WARP; rr++) {
+                const int r = r_base + rr, row = n0 + r;
+                if (row >= p.n) break;
+                const size_t g0 = (size_t)row * rb + (size_t)kb0 * BB;
+                const size_t a0 = g0 & ~(size_t)15;
+                const int npieces = (int)((g0 + seg - a0 + 15) >> 4);
+                for (int pc = lane; pc < npieces; pc += 32) {
+                    const size_t g = a0 + ((size_t)pc << 4);
+                    uint8_t *dst = raw + r * RAW_RS + (pc << 4);
+                    if (g + 16 <= p.w_bytes) {
+                        cp_async16(smem_u32(dst), p.w + g, 16);
+                    } else {
+                        for (int b = 0; b < 16; b++) dst[b] = (g + b < p.w_bytes) ? p.w[g + b] : 0;
+                    }
+                }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();
+            const int ntiles = ((kb1 - kb0) * BE) / KT;
+            // Per-thread constants of this phase: where each of its rows starts in the raw area (the row's
+            // 16-byte skew differs from row to row) and whether the row exists.
+            constexpr int NIT = (FMT == FMT_TQ2_0) ? ROWS_PER_WARP / 2 : ROWS_PER_WARP;
+            const int sub = (FMT == FMT_TQ2_0) ? (lane >> 4) : 0;      // TQ2_0: which row of the pair
+            const uint8_t *src[NIT];
+            bool valid[NIT];
+#pragma unroll
+            for (int i = 0; i < NIT; i++) {
+                const int r = r_base + ((FMT == FMT_TQ2_0) ? 2 * i + sub : i), row = n0 + r;
+                const size_t g0 = (size_t)row * rb + (size_t)kb0 * BB;
+                src[i] = raw + r * RAW_RS + (int)(g0 & 15);
+                valid[i] = row < p.n;
+            }
+            for (int t = 0; t < ntiles; t++, tile++) {
+                const int s = tile % S;
+                // Stage s was checked free when this warp prefetched its activations (previous iteration).
+                if (tile + 1 < total_tiles) {
+                    if (!stage_free(tile + 1)) { *abort_flag = 1; dead = true; break; }
+                    load_b(tile + 1);
+                }
+                cp_async_commit();
+                uint8_t *ast = a_s + s * A_STAGE;
+                if (FMT == FMT_TQ2_0) {
+                    // tile t = half h of block kb (32 code bytes per row). lane = (row of a pair, 2-byte piece u):
+                    // 8 weights k = l*32 + 2u + {0,1}, l = 0..3.  Element (r, k) lives at 16 r + (k/8) LBO + 2 (k%8).
+                    const int u = lane & 15;
+                    const int soff = (t >> 1) * BB + (t & 1) * 32 + 2 * u, doff = (t >> 1) * BB + 64;
+                    uint8_t *dst = ast + 16 * (r_base + sub) + (u & 3) * 4 + (u >> 2) * A_LBO;
+                    uint32_t w16[NIT];
+                    __half dd[NIT];
+#pragma unroll
+                    for (int i = 0; i < NIT; i++) {
+                        w16[i] = *reinterpret_cast<const uint16_t *>(src[i] + soff);
+                        dd[i] = *reinterpret_cast<const __half *>(src[i] + doff);
+                    }
+                    const __half2 c1025 = __float2half2_rn(1025.0f);
+#pragma unroll
+                    for (int i = 0; i < NIT; i++) {
+                        const __half2 d2 = __half2half2(valid[i] ? dd[i] : __float2half(0.0f));
+                        const uint32_t tlo = __byte_perm(w16[i], 0u, 0x4140);  // [b0, 0, b1, 0]
+#pragma unroll
+                        for (int l = 0; l < 4; l++) {
+                            const uint32_t hbits = ((tlo >> (2 * l)) & 0x00030003u) | 0x64006400u;   // 1024 + q
+                            const __half2 w = __hmul2(__hsub2(bits_h2(hbits), c1025), d2);           // (q - 1) d, exact
+                            *reinterpret_cast<uint32_t *>(dst + 32 * i + l * (4 * A_LBO)) = h2_bits(w);
+                        }
+                    }
+                } else {
+                    // tile t = blocks 4t..4t+3 of the phase; lane = (block b, 2-byte piece hh):
+                    // low nibbles k = 32b + 2hh + {0,1}, high nibbles 16 further (two k-chunks on).
+                    const int b = lane >> 3, hh = lane & 7;
+                    const int boff = (4 * t + b) * BB;
+                    uint8_t *dst = ast + 16 * r_base + (hh & 3) * 4 + (4 * b + (hh >> 2)) * A_LBO;
+                    uint32_t w16[NIT];
+                    __half dd[NIT];
+#pragma unroll
+                    for (int i = 0; i < NIT; i++) {
+                        dd[i] = *reinterpret_cast<const __half *>(src[i] + boff);
+                        w16[i] = *reinterpret_cast<const uint16_t *>(src[i] + boff + 2 + 2 * hh);
+                    }
+                    const __half2 c1032 = __float2half2_rn(1032.0f);
+#pragma unroll
+                    for (int i = 0; i < NIT; i++) {
+                        const __half2 d2 = __half2half2(valid[i] ? dd[i] : __float2half(0.0f));
+                        const uint32_t tlo = __byte_perm(w16[i], 0u, 0x4140);
+                        const __half2 lo = __hmul2(__hsub2(bits_h2((tlo & 0x000F000Fu) | 0x64006400u), c1032), d2);
+                        const __half2 hi = __hmul2(__hsub2(bits_h2(((tlo >> 4) & 0x000F000Fu) | 0x64006400u), c1032), d2);
+                        *reinterpret_cast<uint32_t *>(dst + 16 * i) = h2_bits(lo);
+                        *reinterpret_cast<uint32_t *>(dst + 16 * i + 2 * A_LBO) = h2_bits(hi);
+                    }
+                }
+                cp_async_wait<1>();  // this tile's activation chunk has landed (the next tile's may be in flight)
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&a_full[s]));
+            }
+        }
+    } else {
+        // ============================ MMA issue (one warp) ============================
+        bool dead = false;
+        for (int tile = 0; tile < total_tiles && !dead; tile++) {
+            const int s = tile % S, use = tile / S;
+            uint32_t ok = 1;
+            if (lane == 0) ok = mbar_wait(smem_u32(&a_full[s]), (uint32_t)(use & 1)) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
+            if (lane == 0) {
+                tc_fence_after();
+                const uint32_t abase = smem_u32(a_s + s * A_STAGE), bbase = smem_u32(b_s + s * B_STAGE);
+#pragma unroll
+                for (int j = 0; j < KT / 16; j++) {
+                    const uint64_t ad = make_desc(abase + j * 2 * A_LBO, A_LBO, A_SBO);
+                    const uint64_t bd = make_desc(bbase + j * 2 * B_LBO, (uint32_t)B_LBO, 128u);
+                    umma_f16(tmem_base, ad, bd, idesc, (tile > 0 || j > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&mma_done[s]));
+            }
+            __syncwarp();
+        }
+        // drain: the last commit covers every MMA issued before it
+        if (!dead && total_tiles > 0) {
+            const int last = total_tiles - 1;
+            uint32_t ok = 1;
+            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[last % S]), (uint32_t)((last / S) & 1)) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) *abort_flag = 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const bool failed = *abort_flag != 0;
+    if (!failed && warp < 4) {
+        const int row = n0 + warp * 32 + lane;
+        OutT *out = reinterpret_cast<OutT *>(p.out);
+        for (int c0 = 0; c0 < NB; c0 += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+            if (row < p.n) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int gm = m0 + c0 + j;
+                    if (gm < p.m) store_c(out + (size_t)gm * p.n + row, __uint_as_float(v[j]));
+                }
+            }
+        }
+    }
+    if (failed && tid == 0) atomicExch(p.status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
+                     : "memory");
+    }
+}
+
+template <int FMT, typename OutT>
+int launch_tc(lc_kernels *k, lc_batch *b, TcParams &p, dim3 grid) {
+    const size_t bstage = (size_t)(KT / 8) * p.NB * 16;
+    auto need = [&](int S) { return (size_t)TILE_ROWS * RAW_RS + (size_t)S * A_STAGE + S * bstage + 128; };
+    p.nstage = need(3) <= k->ctx->smem_optin ? 3 : 2;
+    const size_t smem = need(p.nstage);
+    auto kern = qgemm_tc_kernel<FMT, OutT>;
+    static size_t configured = 0;
+    if (smem > configured) {
+        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    kern<<<grid, NT2, smem, b->stream>>>(p);
+    LC_CHECK_LAUNCH("qgemm_tcgen05");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+}  // namespace
+
+// Returns LC_OK after a launch, a positive status on error, or -1 when the shape
+// is outside what this kernel covers (the caller then uses the CUDA-core path).
+int lc_qgemm_tcgen05(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                     lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    if (kk % KT != 0) return -1;  // Q4_0 with K not a multiple of 128
+    TcParams p;
+    p.w = (const uint8_t *)weight->dptr;
+    p.x = (const __half *)input->dptr;
+    p.out = output->dptr;
+    p.m = (int)m;
+    p.n = (int)n;
+    p.K = (int)kk;
+    if (fmt == FMT_Q4_0) {
+        p.nb = (int)(kk / 32);
+        p.w_bytes = (size_t)p.nb * 18 * n;
+    } else {
+        p.nb = (int)(kk / 256);
+        p.w_bytes = (size_t)p.nb * 66 * n;
+    }
+    const uint32_t mb = m < (uint32_t)MAX_NB ? m : (uint32_t)MAX_NB;
+    p.NB = (int)((mb + 15) / 16 * 16);
+    int cols = 32;
+    while (cols < p.NB) cols <<= 1;
+    p.tmem_cols = cols;
+    p.nstage = 2;
+    p.status = k->dev_status;
+    dim3 grid((n + TILE_ROWS - 1) / TILE_ROWS, (m + MAX_NB - 1) / MAX_NB);
+    if (fmt == FMT_Q4_0)
+        return f32out ? launch_tc<FMT_Q4_0, float>(k, b, p, grid) : launch_tc<FMT_Q4_0, __half>(k, b, p, grid);
+    return f32out ? launch_tc<FMT_TQ2_0, float>(k, b, p, grid) : launch_tc<FMT_TQ2_0, __half>(k, b, p, grid);
+}
+
+extern "C" int lc_kernels_device_status(lc_kernels *k, int *status) {
+    if (!k || !status) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_kernels_device_status: NULL argument");
+    LC_CUDA_TRY(cudaMemcpyAsync(status, k->dev_status, sizeof(int), cudaMemcpyDeviceToHost, k->ctx->stream));
+    LC_CUDA_TRY(cudaStreamSynchronize(k->ctx->stream));
+    if (*status) return lc_fail(LC_ERR_TIMEOUT, "a device-side bounded wait expired (status %d)", *status);
+    return LC_OK;
 }

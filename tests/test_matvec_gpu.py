@@ -170,3 +170,61 @@ def test_matvec_is_linear_at_full_size(la, ctx, kernels):
     yb = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", w, b, rows, cols, True, True)
     yab = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", w, ab, rows, cols, True, True)
     rel_close(yab, ya + yb, 1e-4, "linearity")
+
+
+# ---- tensor-core (tcgen05) path: m > 8 ----
+TC_TOL_TQ2 = 1e-3   # TQ2_0 operands are exact in f16
+TC_TOL_Q4 = 1e-3    # vs the f16-weight semantic of the reference's CPU dequant (qat_recover.rs:93)
+TC_TOL_Q4_F32W = 6e-3  # vs the f32-weight oracle: Q4_0 weights are rounded once to f16 before the MMA
+
+
+def device_status_ok(kernels):
+    import ctypes as C
+    st = C.c_int(0)
+    kernels.kernels_device_status(C.addressof(st))
+    assert st.value == 0
+
+
+@pytest.mark.parametrize("m,k,n", [(70, 256, 96), (70, 512, 128), (16, 1536, 8192), (64, 1536, 8192), (64, 6144, 1536),
+                                   (200, 512, 64), (9, 256, 1), (33, 2048, 1536)])
+def test_matmul_nt_tq2_0_tensor_core(la, orc, ctx, kernels, m, k, n):
+    """kernels.rs:9551-9600 (m = 70 spans tiles) plus the benchmark shapes (config 2 at M = 16 and 64)."""
+    raw, _ = refgen.tq2_0_payload(n, k, 0x2B19) if n * k <= 1 << 20 else (la.synth.tq2_0_weights(n, k, 5, ncodes=4), None)
+    a = refgen.sin_matrix(m, k, 0.017, 0.6, np.cos) if n * k <= 1 << 20 else la.synth.normal_f16((m, k), 6)
+    got = run_matmul(la, ctx, kernels, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+    rel_close(got, orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n), TC_TOL_TQ2, f"tcgen05 tq2_0 m={m} k={k} n={n}")
+    device_status_ok(kernels)
+
+
+@pytest.mark.parametrize("m,k,n", [(70, 256, 128), (70, 64, 96), (16, 1536, 300), (64, 1536, 6144), (64, 768, 129),
+                                   (130, 128, 256)])
+def test_matmul_nt_q4_0_tensor_core(la, orc, ctx, kernels, m, k, n):
+    raw, _ = refgen.q4_0_payload(n, k, 0x51A7) if n * k <= 1 << 20 else (la.synth.q4_0_weights(n, k, 7), None)
+    a = refgen.sin_matrix(m, k, 0.013, 0.7) if n * k <= 1 << 20 else la.synth.normal_f16((m, k), 8)
+    """Operands reach the tensor core as f16((q-8)*d) — the value qat_recover::dequant_q4_0 produces
+    (qat_recover.rs:86-93) — so the exact reference for this path is the f16-weight product; the
+    f32-weight oracle is met within the rounding that implies (K=64 routes to the CUDA-core path)."""
+    w16 = orc.dequant(orc.Q4_0, raw, n * k).astype(np.float64).reshape(n, k)
+    want16 = (a.astype(np.float64) @ w16.T).astype(np.float32)
+    want32 = orc.matmul_nt(orc.Q4_0, a, raw, m, k, n)
+    got = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_into", a, raw, m, k, n)
+    rel_close(got, want16 if k % 128 == 0 else want32, TC_TOL_Q4, f"tcgen05 q4_0 m={m} k={k} n={n} vs its exact reference")
+    rel_close(got, want32, TC_TOL_Q4_F32W, f"tcgen05 q4_0 m={m} k={k} n={n} vs f32 weights")
+    got32 = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_f32out_into", a, raw, m, k, n, f32out=True)
+    rel_close(got32, want16, 1e-4 if k % 128 == 0 else TC_TOL_Q4_F32W, "tcgen05 q4_0 f32 out vs f16 weights")
+    rel_close(got32, want32, TC_TOL_Q4_F32W, "tcgen05 q4_0 f32 out vs f32 weights")
+    device_status_ok(kernels)
+
+
+def test_tensor_core_and_cuda_core_paths_agree(la, orc, ctx, kernels, monkeypatch):
+    """LOCAL_AI_MMA=0 forces the CUDA-core path (kernels.rs:6290-6298); both must give the same TQ2_0 result
+    up to summation order."""
+    m, k, n = 64, 1536, 512
+    raw = la.synth.tq2_0_weights(n, k, 11)
+    a = la.synth.normal_f16((m, k), 12)
+    tc = run_matmul(la, ctx, kernels, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+    monkeypatch.setenv("LOCAL_AI_MMA", "0")
+    k2 = la.Kernels.new(ctx)
+    cc = run_matmul(la, ctx, k2, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+    k2.close()
+    assert np.max(np.abs(tc - cc)) <= 2e-3 * max(1.0, float(np.abs(cc).max()))
