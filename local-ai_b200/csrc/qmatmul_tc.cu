@@ -118,14 +118,21 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cas
 __device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
 __device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
 
+constexpr int MAX_GROUPS = 3;
 struct TcParams {
-    const uint8_t *w;
-    size_t w_bytes;
+    // Up to three weight matrices that share the activations and K (Q/K/V, gate/up) run as one launch:
+    // row tiles [tile_end[g-1], tile_end[g]) of the grid's x dimension belong to matrix g.
+    const uint8_t *w[MAX_GROUPS];
+    void *out[MAX_GROUPS];
+    int n[MAX_GROUPS], tile_end[MAX_GROUPS];
+    int ngroups;
     const __half *x;
-    void *out;
-    int m, n, K, nb;       // nb = blocks per row
+    int m, K, nb;          // nb = blocks per row
+    int ks, bps;           // split-K: grid.z = ks, bps = blocks per split
+    float *partial;        // [tile][split][NB cols][128 rows] f32, used when ks > 1
+    unsigned int *counters; // one per tile, zero between launches (the last CTA to arrive resets it)
     int NB;                // batch rows per CTA (multiple of 16, <= 128)
-    int nstage;            // operand stages (3 when they fit, else 2)
+    int sb;                // activation stages (6 when they fit, else 3); weight stages are fixed at 2
     int tmem_cols;         // power of two >= max(32, NB)
     int *status;
 };
@@ -137,7 +144,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t addr) {
 constexpr int N_UNPACK_WARPS = 16;
 constexpr int ROWS_PER_WARP = TILE_ROWS / N_UNPACK_WARPS;  // 8
 constexpr int NT2 = (N_UNPACK_WARPS + 1) * 32;              // + one warp: activation loads and MMA issue
-constexpr int MAX_STAGE = 3;
+constexpr int SA = 2;        // weight (A operand) stages
+constexpr int MAX_BAR = 6;   // mma_done barriers, one per tile index mod 6 (>= any activation stage count)
+static_assert(N_UNPACK_WARPS == KT / 8, "one unpack warp per k-chunk of the activation tile");
 
 // Warp-specialised pipeline, no CTA-wide barrier inside the k loop:
 //   warps 0..15 own 8 weight rows each: cp.async their raw blocks, unpack them into operand
@@ -150,19 +159,25 @@ template <int FMT, typename OutT>
 __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int BB = TcFmt<FMT>::bytes, BE = TcFmt<FMT>::elems, PB = TcFmt<FMT>::phase_blocks;
-    const int NB = p.NB, S = p.nstage;
+    const int NB = p.NB, SB = p.sb, PD = p.sb - 2;   // PD: activation tiles kept in flight ahead of the current one
     const int B_LBO = NB * 16, B_STAGE = (KT / 8) * B_LBO;
     uint8_t *raw = smem;                                   // [128][RAW_RS]
-    uint8_t *a_s = raw + TILE_ROWS * RAW_RS;               // [S][A_STAGE]
-    uint8_t *b_s = a_s + S * A_STAGE;                      // [S][B_STAGE]
-    uint64_t *a_full = reinterpret_cast<uint64_t *>(b_s + S * B_STAGE);  // [MAX_STAGE]
-    uint64_t *mma_done = a_full + MAX_STAGE;                            // [MAX_STAGE]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(mma_done + MAX_STAGE);
+    uint8_t *a_s = raw + TILE_ROWS * RAW_RS;               // [SA][A_STAGE]
+    uint8_t *b_s = a_s + SA * A_STAGE;                     // [SB][B_STAGE]
+    uint64_t *a_full = reinterpret_cast<uint64_t *>(b_s + SB * B_STAGE);  // [SA]
+    uint64_t *mma_done = a_full + SA;                                   // [MAX_BAR]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(mma_done + MAX_BAR);
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n0 = blockIdx.x * TILE_ROWS, m0 = blockIdx.y * MAX_NB;
+    int grp = 0;
+    while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
+    const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * TILE_ROWS, m0 = blockIdx.y * MAX_NB;
+    const int n_rows = p.n[grp];
+    const uint8_t *wmat = p.w[grp];
     const size_t rb = (size_t)p.nb * BB;
+    const size_t w_bytes = rb * (size_t)n_rows;
+    const int kbs = (int)blockIdx.z * p.bps, kbe = min(p.nb, kbs + p.bps);   // this CTA's K blocks
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
@@ -171,10 +186,8 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     if (tid == 0) {
-        for (int i = 0; i < MAX_STAGE; i++) {
-            mbar_init(smem_u32(&a_full[i]), N_UNPACK_WARPS);
-            mbar_init(smem_u32(&mma_done[i]), 1);
-        }
+        for (int i = 0; i < SA; i++) mbar_init(smem_u32(&a_full[i]), N_UNPACK_WARPS);
+        for (int i = 0; i < MAX_BAR; i++) mbar_init(smem_u32(&mma_done[i]), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -183,8 +196,9 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
-    const int nphases = (p.nb + PB - 1) / PB;
-    const int total_tiles = (p.nb * BE) / KT;
+    const int nphases = (kbe - kbs + PB - 1) / PB;
+    const int total_tiles = ((kbe - kbs) * BE) / KT;
+    const int kg_base = kbs * BE;   // first k of this CTA
 
     if (warp < N_UNPACK_WARPS) {
         // =============================== unpack warps ===============================
@@ -193,10 +207,10 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         bool dead = false;
         // This warp also brings in k-chunk `warp` (8 k values) of every activation tile, one tile ahead:
         // lane walks batch rows lane, lane + 32, ...  Element (mrow, chunk c) lives at c*B_LBO + 16*mrow.
-        const __half *x_lane = p.x + (size_t)(m0 + lane) * p.K + warp * 8;
+        const __half *x_lane = p.x + (size_t)(m0 + lane) * p.K + kg_base + warp * 8;
         const int rows_valid = p.m - m0;
         auto load_b = [&](int tl) {
-            uint32_t dst = smem_u32(b_s + (tl % S) * B_STAGE) + (uint32_t)(warp * B_LBO + 16 * lane);
+            uint32_t dst = smem_u32(b_s + (tl % SB) * B_STAGE) + (uint32_t)(warp * B_LBO + 16 * lane);
             const __half *src = x_lane + (size_t)tl * KT;
             for (int mrow = lane; mrow < NB; mrow += 32) {
                 const bool ok = mrow < rows_valid;
@@ -205,33 +219,34 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                 src += (size_t)32 * p.K;
             }
         };
-        // Stage of tile tl is free once the MMAs of tile tl - S have completed.
-        auto stage_free = [&](int tl) -> bool {
-            if (tl < S) return true;
+        // MMAs of tile tl have completed (frees weight stage tl % SA and activation stage tl % SB).
+        auto mma_finished = [&](int tl) -> bool {
             uint32_t ok = 1;
-            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[tl % S]), (uint32_t)(((tl / S) - 1) & 1)) ? 1u : 0u;
+            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[tl % MAX_BAR]), (uint32_t)((tl / MAX_BAR) & 1)) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             return ok && !*abort_flag;
         };
-        if (total_tiles > 0) load_b(0);
-        cp_async_commit();
+        for (int t = 0; t < PD; t++) {   // activation tiles 0 .. PD-1, one cp.async group each
+            if (t < total_tiles) load_b(t);
+            cp_async_commit();
+        }
         for (int ph = 0; ph < nphases && !dead; ph++) {
-            const int kb0 = ph * PB, kb1 = min(p.nb, kb0 + PB);
+            const int kb0 = kbs + ph * PB, kb1 = min(kbe, kb0 + PB);
             const int seg = (kb1 - kb0) * BB;
             __syncwarp();  // the previous phase's raw bytes are no longer being read by this warp
             for (int rr = 0; rr < ROWS_PER_WARP; rr++) {
                 const int r = r_base + rr, row = n0 + r;
-                if (row >= p.n) break;
+                if (row >= n_rows) break;
                 const size_t g0 = (size_t)row * rb + (size_t)kb0 * BB;
                 const size_t a0 = g0 & ~(size_t)15;
                 const int npieces = (int)((g0 + seg - a0 + 15) >> 4);
                 for (int pc = lane; pc < npieces; pc += 32) {
                     const size_t g = a0 + ((size_t)pc << 4);
                     uint8_t *dst = raw + r * RAW_RS + (pc << 4);
-                    if (g + 16 <= p.w_bytes) {
-                        cp_async16(smem_u32(dst), p.w + g, 16);
+                    if (g + 16 <= w_bytes) {
+                        cp_async16(smem_u32(dst), wmat + g, 16);
                     } else {
-                        for (int b = 0; b < 16; b++) dst[b] = (g + b < p.w_bytes) ? p.w[g + b] : 0;
+                        for (int b = 0; b < 16; b++) dst[b] = (g + b < w_bytes) ? wmat[g + b] : 0;
                     }
                 }
             }
@@ -250,15 +265,14 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                 const int r = r_base + ((FMT == FMT_TQ2_0) ? 2 * i + sub : i), row = n0 + r;
                 const size_t g0 = (size_t)row * rb + (size_t)kb0 * BB;
                 src[i] = raw + r * RAW_RS + (int)(g0 & 15);
-                valid[i] = row < p.n;
+                valid[i] = row < n_rows;
             }
             for (int t = 0; t < ntiles; t++, tile++) {
-                const int s = tile % S;
-                // Stage s was checked free when this warp prefetched its activations (previous iteration).
-                if (tile + 1 < total_tiles) {
-                    if (!stage_free(tile + 1)) { *abort_flag = 1; dead = true; break; }
-                    load_b(tile + 1);
-                }
+                const int s = tile % SA;
+                // One wait per tile: the MMAs of tile - 2 are done, which frees weight stage s and the
+                // activation stage that tile + PD will use (PD = SB - 2).
+                if (tile >= 2 && !mma_finished(tile - 2)) { *abort_flag = 1; dead = true; break; }
+                if (tile + PD < total_tiles) load_b(tile + PD);
                 cp_async_commit();
                 uint8_t *ast = a_s + s * A_STAGE;
                 if (FMT == FMT_TQ2_0) {
@@ -310,7 +324,8 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                         *reinterpret_cast<uint32_t *>(dst + 16 * i + 2 * A_LBO) = h2_bits(hi);
                     }
                 }
-                cp_async_wait<1>();  // this tile's activation chunk has landed (the next tile's may be in flight)
+                // this tile's activation chunk has landed; the PD younger groups may still be in flight
+                if (PD == 4) cp_async_wait<4>(); else cp_async_wait<1>();
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&a_full[s]));
@@ -320,21 +335,21 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         // ============================ MMA issue (one warp) ============================
         bool dead = false;
         for (int tile = 0; tile < total_tiles && !dead; tile++) {
-            const int s = tile % S, use = tile / S;
+            const int s = tile % SA, use = tile / SA;
             uint32_t ok = 1;
             if (lane == 0) ok = mbar_wait(smem_u32(&a_full[s]), (uint32_t)(use & 1)) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
             if (lane == 0) {
                 tc_fence_after();
-                const uint32_t abase = smem_u32(a_s + s * A_STAGE), bbase = smem_u32(b_s + s * B_STAGE);
+                const uint32_t abase = smem_u32(a_s + s * A_STAGE), bbase = smem_u32(b_s + (tile % SB) * B_STAGE);
 #pragma unroll
                 for (int j = 0; j < KT / 16; j++) {
                     const uint64_t ad = make_desc(abase + j * 2 * A_LBO, A_LBO, A_SBO);
                     const uint64_t bd = make_desc(bbase + j * 2 * B_LBO, (uint32_t)B_LBO, 128u);
                     umma_f16(tmem_base, ad, bd, idesc, (tile > 0 || j > 0) ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&mma_done[s]));
+                umma_commit(smem_u32(&mma_done[tile % MAX_BAR]));
             }
             __syncwarp();
         }
@@ -342,7 +357,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         if (!dead && total_tiles > 0) {
             const int last = total_tiles - 1;
             uint32_t ok = 1;
-            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[last % S]), (uint32_t)((last / S) & 1)) ? 1u : 0u;
+            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[last % MAX_BAR]), (uint32_t)((last / MAX_BAR) & 1)) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) *abort_flag = 1;
         }
@@ -351,17 +366,49 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     __syncthreads();
     tc_fence_after();
     const bool failed = *abort_flag != 0;
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
     if (!failed && warp < 4) {
-        const int row = n0 + warp * 32 + lane;
-        OutT *out = reinterpret_cast<OutT *>(p.out);
+        const int lrow = warp * 32 + lane, row = n0 + lrow;
+        OutT *out = reinterpret_cast<OutT *>(p.out[grp]);
+        float *part = p.partial + ((size_t)tile_id * p.ks + blockIdx.z) * (size_t)NB * TILE_ROWS;
         for (int c0 = 0; c0 < NB; c0 += 16) {
             uint32_t v[16];
             tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-            if (row < p.n) {
+            if (p.ks > 1) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) part[(size_t)(c0 + j) * TILE_ROWS + lrow] = __uint_as_float(v[j]);
+            } else if (row < n_rows) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const int gm = m0 + c0 + j;
-                    if (gm < p.m) store_c(out + (size_t)gm * p.n + row, __uint_as_float(v[j]));
+                    if (gm < p.m) store_c(out + (size_t)gm * n_rows + row, __uint_as_float(v[j]));
+                }
+            }
+        }
+    }
+    if (p.ks > 1 && !failed) {
+        // Deterministic split-K: every split stores its f32 partial tile; the last CTA to arrive adds the
+        // partials in split order and writes the result.
+        __shared__ unsigned int is_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int prev = atomicAdd(&p.counters[tile_id], 1u);
+            is_last = (prev == (unsigned int)p.ks - 1) ? 1u : 0u;
+            if (is_last) p.counters[tile_id] = 0u;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            OutT *out = reinterpret_cast<OutT *>(p.out[grp]);
+            const float *part = p.partial + (size_t)tile_id * p.ks * (size_t)NB * TILE_ROWS;
+            for (int i = tid; i < NB * TILE_ROWS; i += NT2) {
+                const int col = i / TILE_ROWS, lrow = i - col * TILE_ROWS;
+                const int gm = m0 + col, row = n0 + lrow;
+                if (gm < p.m && row < n_rows) {
+                    float acc = 0.f;
+                    for (int sp = 0; sp < p.ks; sp++) acc += __ldcg(part + (size_t)sp * NB * TILE_ROWS + i);
+                    store_c(out + (size_t)gm * n_rows + row, acc);
                 }
             }
         }
@@ -378,9 +425,9 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
 template <int FMT, typename OutT>
 int launch_tc(lc_kernels *k, lc_batch *b, TcParams &p, dim3 grid) {
     const size_t bstage = (size_t)(KT / 8) * p.NB * 16;
-    auto need = [&](int S) { return (size_t)TILE_ROWS * RAW_RS + (size_t)S * A_STAGE + S * bstage + 128; };
-    p.nstage = need(3) <= k->ctx->smem_optin ? 3 : 2;
-    const size_t smem = need(p.nstage);
+    auto need = [&](int sb) { return (size_t)TILE_ROWS * RAW_RS + (size_t)SA * A_STAGE + sb * bstage + 128; };
+    p.sb = need(6) <= k->ctx->smem_optin ? 6 : 3;
+    const size_t smem = need(p.sb);
     auto kern = qgemm_tc_kernel<FMT, OutT>;
     static size_t configured = 0;
     if (smem > configured) {
@@ -395,36 +442,69 @@ int launch_tc(lc_kernels *k, lc_batch *b, TcParams &p, dim3 grid) {
 
 }  // namespace
 
+// Grouped launch: `ng` weight matrices [n[g], kk] sharing the activations `input` [m, kk].
 // Returns LC_OK after a launch, a positive status on error, or -1 when the shape
 // is outside what this kernel covers (the caller then uses the CUDA-core path).
-int lc_qgemm_tcgen05(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
-                     lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
-    if (kk % KT != 0) return -1;  // Q4_0 with K not a multiple of 128
+int lc_qgemm_tcgen05_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
+                             const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
+                             uint32_t kk) {
+    if (kk % KT != 0 || ng < 1 || ng > MAX_GROUPS) return -1;  // Q4_0 with K not a multiple of 128
     TcParams p;
-    p.w = (const uint8_t *)weight->dptr;
     p.x = (const __half *)input->dptr;
-    p.out = output->dptr;
     p.m = (int)m;
-    p.n = (int)n;
     p.K = (int)kk;
-    if (fmt == FMT_Q4_0) {
-        p.nb = (int)(kk / 32);
-        p.w_bytes = (size_t)p.nb * 18 * n;
-    } else {
-        p.nb = (int)(kk / 256);
-        p.w_bytes = (size_t)p.nb * 66 * n;
+    p.nb = fmt == FMT_Q4_0 ? (int)(kk / 32) : (int)(kk / 256);
+    p.ngroups = ng;
+    int tiles = 0;
+    for (int g = 0; g < MAX_GROUPS; g++) {
+        const int gi = g < ng ? g : ng - 1;
+        p.w[g] = (const uint8_t *)weights[gi]->dptr;
+        p.out[g] = outputs[gi]->dptr;
+        p.n[g] = (int)ns[gi];
+        if (g < ng) tiles += ((int)ns[g] + TILE_ROWS - 1) / TILE_ROWS;
+        p.tile_end[g] = tiles;
     }
     const uint32_t mb = m < (uint32_t)MAX_NB ? m : (uint32_t)MAX_NB;
     p.NB = (int)((mb + 15) / 16 * 16);
     int cols = 32;
     while (cols < p.NB) cols <<= 1;
     p.tmem_cols = cols;
-    p.nstage = 2;
+    p.sb = 3;
     p.status = k->dev_status;
-    dim3 grid((n + TILE_ROWS - 1) / TILE_ROWS, (m + MAX_NB - 1) / MAX_NB);
+    const int mtiles = (int)((m + MAX_NB - 1) / MAX_NB);
+    // split-K so that small-n projections still fill the GPU: each split gets whole blocks and at least two k-tiles.
+    const int min_blocks = fmt == FMT_Q4_0 ? 8 : 1;   // 8 Q4_0 blocks = 256 k = 2 k-tiles; 1 TQ2_0 block = 2 k-tiles
+    int ks = k->ctx->sm_count / (tiles * mtiles);
+    const int max_ks = p.nb / min_blocks;
+    if (ks > max_ks) ks = max_ks;
+    if (ks < 1) ks = 1;
+    if (ks > 32) ks = 32;
+    int bps = (p.nb + ks - 1) / ks;
+    bps = (bps + min_blocks - 1) / min_blocks * min_blocks;   // Q4_0: whole k-tiles (4 blocks) per split
+    ks = (p.nb + bps - 1) / bps;
+    p.ks = ks;
+    p.bps = bps;
+    p.partial = nullptr;
+    p.counters = nullptr;
+    if (ks > 1) {
+        const size_t ntile = (size_t)tiles * mtiles;
+        int st = lc_reserve_scratch(k, b, ntile * ks * (size_t)p.NB * TILE_ROWS * sizeof(float), ntile);
+        if (st != LC_OK) return st;
+        p.partial = (float *)k->scratch;
+        p.counters = k->counters;
+    }
+    dim3 grid(tiles, mtiles, ks);
     if (fmt == FMT_Q4_0)
         return f32out ? launch_tc<FMT_Q4_0, float>(k, b, p, grid) : launch_tc<FMT_Q4_0, __half>(k, b, p, grid);
     return f32out ? launch_tc<FMT_TQ2_0, float>(k, b, p, grid) : launch_tc<FMT_TQ2_0, __half>(k, b, p, grid);
+}
+
+int lc_qgemm_tcgen05(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                     lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    const lc_buf *ws[1] = {weight};
+    lc_buf *os[1] = {output};
+    const uint32_t ns[1] = {n};
+    return lc_qgemm_tcgen05_grouped(fmt, f32out, k, b, input, 1, ws, os, ns, m, kk);
 }
 
 extern "C" int lc_kernels_device_status(lc_kernels *k, int *status) {

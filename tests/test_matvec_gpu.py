@@ -228,3 +228,18 @@ def test_tensor_core_and_cuda_core_paths_agree(la, orc, ctx, kernels, monkeypatc
     cc = run_matmul(la, ctx, k2, "matmul_nt_tq2_0_into", a, raw, m, k, n)
     k2.close()
     assert np.max(np.abs(tc - cc)) <= 2e-3 * max(1.0, float(np.abs(cc).max()))
+
+
+def test_split_k_is_deterministic_and_lane_isolated(la, orc, ctx, kernels):
+    """Small-n projections run split-K on the tensor-core path (deterministic last-arriver reduction):
+    repeated launches and duplicate batch rows must agree bit for bit."""
+    m, k, n = 64, 6144, 1536   # the down projection: 12 row tiles x 12 splits
+    raw = la.synth.tq2_0_weights(n, k, 21)
+    a = la.synth.normal_f16((m, k), 22)
+    a[5] = a[3]
+    r1 = run_matmul(la, ctx, kernels, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+    r2 = run_matmul(la, ctx, kernels, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+    assert np.array_equal(r1, r2)
+    assert np.array_equal(r1[5], r1[3])
+    rel_close(r1, orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n), TC_TOL_TQ2, "split-K down projection")
+    device_status_ok(kernels)
