@@ -74,6 +74,7 @@ int lc_ctx_create(int device, lc_ctx **out) {
     size_t fr = 0, tot = 0;
     cudaMemGetInfo(&fr, &tot);
     c->total_mem = tot;
+    { const char *e = getenv("LOCAL_CUDA_PDL"); c->pdl = !(e && strcmp(e, "0") == 0); }
     *out = c;
     return LC_OK;
 }
@@ -377,8 +378,8 @@ int lc_kernels_create(lc_ctx *ctx, lc_kernels **out) {
     k->mma = env_enabled("LOCAL_AI_MMA");
     const char *nm = getenv("LOCAL_CUDA_TQ_NORM");
     k->kv_norm_mode = (nm && strcmp(nm, "tree") == 0) ? 1 : 0;
-    cudaError_t e = cudaMalloc((void **)&k->dev_status, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemsetAsync(k->dev_status, 0, sizeof(int), ctx->stream);
+    cudaError_t e = cudaMalloc((void **)&k->dev_status, 128);  // status word + tuning stamps
+    if (e == cudaSuccess) e = cudaMemsetAsync(k->dev_status, 0, 128, ctx->stream);
     if (e != cudaSuccess) {
         delete k;
         return lc_fail(LC_ERR_PIPELINE_CREATION, "status word: %s", cudaGetErrorString(e));

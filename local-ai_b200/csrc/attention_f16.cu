@@ -24,6 +24,8 @@ f16_attn_split_kernel(const __half *__restrict__ q, const __half *__restrict__ k
                       float *__restrict__ pmax, float *__restrict__ psum, float *__restrict__ pacc, unsigned hd,
                       unsigned kv_len, unsigned current_pos, unsigned n_q, unsigned n_kv, unsigned window,
                       unsigned num_splits, float scale) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float m_s[NW], l_s[NW];
     __shared__ float acc_s[NW][512];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -113,6 +115,8 @@ f16_attn_split_kernel(const __half *__restrict__ q, const __half *__restrict__ k
 __global__ void f16_attn_reduce_kernel(const float *__restrict__ pmax, const float *__restrict__ psum,
                                        const float *__restrict__ pacc, __half *__restrict__ out, unsigned hd,
                                        unsigned num_splits) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned qh = blockIdx.x;
     float gmax = -INFINITY;
     for (unsigned s = 0; s < num_splits; s++) gmax = fmaxf(gmax, pmax[(size_t)qh * num_splits + s]);
@@ -145,13 +149,12 @@ int f16_attention(const char *name, lc_batch *b, const lc_buf *q, const lc_buf *
     LC_REQUIRE(k->bytes >= (size_t)seq_len * n_kv * hd * 2 && v->bytes >= (size_t)seq_len * n_kv * hd * 2,
                "%s: K/V hold fewer than %u rows", name, seq_len);
     LC_REQUIRE(lc_aligned(q->dptr, 4) && lc_aligned(k->dptr, 4) && lc_aligned(v->dptr, 4), "%s: buffers must be 4-byte aligned", name);
-    f16_attn_split_kernel<<<dim3(num_splits, n_q), NT, 0, b->stream>>>(
-        (const __half *)q->dptr, (const __half *)k->dptr, (const __half *)v->dptr, pmax, psum, pacc, hd, kv_len,
-        current_pos, n_q, n_kv, window, num_splits, scale);
+    LC_LAUNCH_CHECKED(lc_launch(f16_attn_split_kernel, dim3(dim3(num_splits, n_q)), dim3(NT), 0, b, (const __half *)q->dptr, (const __half *)k->dptr, (const __half *)v->dptr, pmax, psum, pacc, hd, kv_len,
+        current_pos, n_q, n_kv, window, num_splits, scale));
     LC_CHECK_LAUNCH(name);
     b->dispatch_count++;
-    f16_attn_reduce_kernel<<<n_q, hd < 256 ? hd : 256, 0, b->stream>>>(pmax, psum, pacc, (__half *)output->dptr, hd,
-                                                                        num_splits);
+    LC_LAUNCH_CHECKED(lc_launch(f16_attn_reduce_kernel, dim3(n_q), dim3(hd < 256 ? hd : 256), 0, b, pmax, psum, pacc, (__half *)output->dptr, hd,
+                                                                        num_splits));
     LC_CHECK_LAUNCH(name);
     b->dispatch_count++;
     return LC_OK;

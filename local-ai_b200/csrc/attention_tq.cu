@@ -58,6 +58,8 @@ __device__ __forceinline__ void fwht_rows(float *sh, int rows) {
 
 template <int HD, int BITS, int G>
 __global__ void __launch_bounds__(NT) tq_attn_split_kernel(const TqAttnParams p) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     constexpr int DPL = HD / 32;
     constexpr int CB = HD * BITS / 8;
     constexpr int NLEV = 1 << BITS;
@@ -258,6 +260,8 @@ template <bool FUSED>
 __global__ void tq_attn_merge_kernel(const float *__restrict__ partial, const float *__restrict__ signs,
                                      float *__restrict__ out_f32, __half *__restrict__ out_f16, unsigned hd,
                                      unsigned n_splits) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[512];
     const unsigned t = threadIdx.x;
     const size_t qh = blockIdx.x;
@@ -298,7 +302,7 @@ int launch_split(lc_batch *b, const TqAttnParams &p, dim3 grid) {
         LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    kern<<<grid, NT, smem, b->stream>>>(p);
+    LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT), smem, b, p));
     LC_CHECK_LAUNCH("flash_attention_tq");
     b->dispatch_count++;
     return LC_OK;
@@ -414,11 +418,9 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     }
     if (st != LC_OK || direct) return st;
     if (fused)
-        tq_attn_merge_kernel<true><<<n_lanes * n_q, hd, 0, b->stream>>>(
-            (const float *)k->scratch, (const float *)signs->dptr, nullptr, (__half *)out->dptr, hd, n_splits);
+        LC_LAUNCH_CHECKED(lc_launch(tq_attn_merge_kernel<true>, dim3(n_lanes * n_q), dim3(hd), 0, b, (const float *)k->scratch, (const float *)signs->dptr, nullptr, (__half *)out->dptr, hd, n_splits));
     else
-        tq_attn_merge_kernel<false><<<n_lanes * n_q, hd, 0, b->stream>>>(
-            (const float *)k->scratch, nullptr, (float *)out->dptr, nullptr, hd, n_splits);
+        LC_LAUNCH_CHECKED(lc_launch(tq_attn_merge_kernel<false>, dim3(n_lanes * n_q), dim3(hd), 0, b, (const float *)k->scratch, nullptr, (float *)out->dptr, nullptr, hd, n_splits));
     LC_CHECK_LAUNCH("flash_attention_tq merge");
     b->dispatch_count++;
     return LC_OK;
@@ -607,8 +609,8 @@ extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const 
         default: st = launch_split_b<512>(b, p, grid, g, bits); break;
     }
     if (st != LC_OK) return st;
-    tq_attn_merge_kernel<true><<<num_q_heads, head_dim, 0, b->stream>>>(scratch, (const float *)signs->dptr, nullptr,
-                                                                       (__half *)attn_out->dptr, head_dim, n_splits);
+    LC_LAUNCH_CHECKED(lc_launch(tq_attn_merge_kernel<true>, dim3(num_q_heads), dim3(head_dim), 0, b, scratch, (const float *)signs->dptr, nullptr,
+                                                                       (__half *)attn_out->dptr, head_dim, n_splits));
     LC_CHECK_LAUNCH("tq_attention_noalloc merge");
     b->dispatch_count++;
     return LC_OK;

@@ -33,6 +33,8 @@ __device__ __forceinline__ float block_sum(float v, float *sh) {
 // In-place (out == in) is allowed: each thread reads its elements before writing them.
 __global__ void rms_norm_kernel(const __half *in, const __half *__restrict__ weight,
                                 const __half *__restrict__ residual, __half *out, unsigned dim, float eps) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[32];
     const size_t base = (size_t)blockIdx.x * dim;
     float s = 0.f;
@@ -53,6 +55,8 @@ __global__ void rms_norm_kernel(const __half *in, const __half *__restrict__ wei
 __global__ void rope_kernel(const __half *in, __half *out, const uint32_t *__restrict__ positions,
                             unsigned position, float theta, unsigned hd, unsigned heads, unsigned rows, float factor,
                             int copy_tail) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned half = hd / 2;
     const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * heads * half) return;
@@ -76,6 +80,8 @@ __global__ void rope_kernel(const __half *in, __half *out, const uint32_t *__res
 }
 
 __global__ void gelu_mul_kernel(const __half *a, const __half *b, __half *out, unsigned n) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = __half2float(a[i]);
@@ -87,22 +93,30 @@ __global__ void gelu_mul_kernel(const __half *a, const __half *b, __half *out, u
 }
 
 __global__ void residual_add_kernel(const __half *a, const __half *b, __half *out, unsigned n) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2half_rn(__half2float(a[i]) + __half2float(b[i]));
 }
 
 __global__ void scale_in_place_kernel(__half *data, float scalar, unsigned n) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) data[i] = __float2half_rn(__half2float(data[i]) * scalar);
 }
 
 __global__ void logit_softcap_kernel(float *data, float cap, unsigned n) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) data[i] = cap * tanhf(data[i] / cap);
 }
 
 __global__ void gather_strided_kernel(const __half *__restrict__ src, __half *__restrict__ dst, unsigned row_stride,
                                       unsigned base_off, unsigned pld, unsigned n_rows) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned gid = blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= n_rows * pld) return;
     const unsigned i = gid / pld, p = gid - i * pld;
@@ -113,6 +127,8 @@ __global__ void gather_strided_kernel(const __half *__restrict__ src, __half *__
 // Two roundings, like dequant-to-f16 followed by scale_in_place.
 __global__ void embed_rows_q4_0_kernel(const uint8_t *__restrict__ table, const uint32_t *__restrict__ tokens,
                                        __half *__restrict__ out, unsigned cols, float scale, int apply_scale) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const unsigned r = blockIdx.x;
     const size_t rb = (size_t)cols / 32 * 18;
     const uint8_t *row = table + (size_t)tokens[r] * rb;
@@ -130,6 +146,8 @@ __global__ void embed_rows_q4_0_kernel(const uint8_t *__restrict__ table, const 
 
 // First maximum of each row (strict '>' scan order => lowest index wins ties).
 __global__ void argmax_rows_kernel(const float *__restrict__ v, uint32_t *__restrict__ out, unsigned cols) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float bv_s[32];
     __shared__ unsigned bi_s[32];
     const float *row = v + (size_t)blockIdx.x * cols;
@@ -175,9 +193,9 @@ int rms_norm_common(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *
                "%s: buffers too small for %u rows of %u", name, rows, dim);
     if (rows == 0) return LC_OK;
     const unsigned threads = dim >= 1024 ? 512 : (dim >= 256 ? 256 : 64);
-    rms_norm_kernel<<<rows, threads, 0, b->stream>>>((const __half *)input->dptr, (const __half *)weight->dptr,
+    LC_LAUNCH_CHECKED(lc_launch(rms_norm_kernel, dim3(rows), dim3(threads), 0, b, (const __half *)input->dptr, (const __half *)weight->dptr,
                                                      residual ? (const __half *)residual->dptr : nullptr,
-                                                     (__half *)output->dptr, dim, eps);
+                                                     (__half *)output->dptr, dim, eps));
     LC_CHECK_LAUNCH(name);
     b->dispatch_count++;
     return LC_OK;
@@ -211,9 +229,9 @@ int lc_rope_into(lc_kernels *k, lc_batch *b, const lc_buf *input, lc_buf *output
     LC_REQUIRE(input->bytes >= n && output->bytes >= n, "rope: buffers too small");
     const unsigned total = num_heads * (head_dim / 2);
     if (total == 0) return LC_OK;
-    rope_kernel<<<cdiv(total, 256), 256, 0, b->stream>>>((const __half *)input->dptr, (__half *)output->dptr, nullptr,
+    LC_LAUNCH_CHECKED(lc_launch(rope_kernel, dim3(cdiv(total, 256)), dim3(256), 0, b, (const __half *)input->dptr, (__half *)output->dptr, nullptr,
                                                          position, theta, head_dim, num_heads, 1,
-                                                         partial_rotary_factor, 1);
+                                                         partial_rotary_factor, 1));
     LC_CHECK_LAUNCH("rope");
     b->dispatch_count++;
     return LC_OK;
@@ -227,9 +245,9 @@ int lc_rope_batch_decode_into(lc_kernels *k, lc_batch *b, lc_buf *qk, const lc_b
                "rope_batch_decode: buffers too small");
     const unsigned total = seq_len * num_heads * (head_dim / 2);
     if (total == 0) return LC_OK;
-    rope_kernel<<<cdiv(total, 256), 256, 0, b->stream>>>((const __half *)qk->dptr, (__half *)qk->dptr,
+    LC_LAUNCH_CHECKED(lc_launch(rope_kernel, dim3(cdiv(total, 256)), dim3(256), 0, b, (const __half *)qk->dptr, (__half *)qk->dptr,
                                                          (const uint32_t *)positions->dptr, 0, theta, head_dim,
-                                                         num_heads, seq_len, partial_rotary_factor, 0);
+                                                         num_heads, seq_len, partial_rotary_factor, 0));
     LC_CHECK_LAUNCH("rope_batch_decode");
     b->dispatch_count++;
     return LC_OK;
@@ -240,8 +258,8 @@ int lc_gelu_mul_into(lc_kernels *k, lc_batch *b, const lc_buf *a, const lc_buf *
     const size_t n = (size_t)count * 2;
     LC_REQUIRE(a->bytes >= n && bb->bytes >= n && out->bytes >= n, "gelu_mul: buffers too small for %u", count);
     if (count == 0) return LC_OK;
-    gelu_mul_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((const __half *)a->dptr, (const __half *)bb->dptr,
-                                                             (__half *)out->dptr, count);
+    LC_LAUNCH_CHECKED(lc_launch(gelu_mul_kernel, dim3(cdiv(count, 256)), dim3(256), 0, b, (const __half *)a->dptr, (const __half *)bb->dptr,
+                                                             (__half *)out->dptr, count));
     LC_CHECK_LAUNCH("gelu_mul");
     b->dispatch_count++;
     return LC_OK;
@@ -253,8 +271,8 @@ int lc_residual_add_into(lc_kernels *k, lc_batch *b, const lc_buf *a, const lc_b
     const size_t n = (size_t)count * 2;
     LC_REQUIRE(a->bytes >= n && bb->bytes >= n && output->bytes >= n, "residual_add: buffers too small for %u", count);
     if (count == 0) return LC_OK;
-    residual_add_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((const __half *)a->dptr, (const __half *)bb->dptr,
-                                                                 (__half *)output->dptr, count);
+    LC_LAUNCH_CHECKED(lc_launch(residual_add_kernel, dim3(cdiv(count, 256)), dim3(256), 0, b, (const __half *)a->dptr, (const __half *)bb->dptr,
+                                                                 (__half *)output->dptr, count));
     LC_CHECK_LAUNCH("residual_add");
     b->dispatch_count++;
     return LC_OK;
@@ -264,7 +282,7 @@ int lc_scale_in_place_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, float s
     if (!k || !b || !data) return lc_fail(LC_ERR_INVALID_ARGUMENT, "scale_in_place: NULL argument");
     LC_REQUIRE(data->bytes >= (size_t)count * 2, "scale_in_place: buffer too small for %u", count);
     if (count == 0) return LC_OK;
-    scale_in_place_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((__half *)data->dptr, scalar, count);
+    LC_LAUNCH_CHECKED(lc_launch(scale_in_place_kernel, dim3(cdiv(count, 256)), dim3(256), 0, b, (__half *)data->dptr, scalar, count));
     LC_CHECK_LAUNCH("scale_in_place");
     b->dispatch_count++;
     return LC_OK;
@@ -274,7 +292,7 @@ int lc_logit_softcap_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, float ca
     if (!k || !b || !data) return lc_fail(LC_ERR_INVALID_ARGUMENT, "logit_softcap: NULL argument");
     LC_REQUIRE(data->bytes >= (size_t)count * 4, "logit_softcap: buffer too small for %u", count);
     if (count == 0) return LC_OK;
-    logit_softcap_kernel<<<cdiv(count, 256), 256, 0, b->stream>>>((float *)data->dptr, cap, count);
+    LC_LAUNCH_CHECKED(lc_launch(logit_softcap_kernel, dim3(cdiv(count, 256)), dim3(256), 0, b, (float *)data->dptr, cap, count));
     LC_CHECK_LAUNCH("logit_softcap");
     b->dispatch_count++;
     return LC_OK;
@@ -287,8 +305,7 @@ int lc_gather_strided_f16_into(lc_kernels *k, lc_batch *b, const lc_buf *src, lc
     LC_REQUIRE(src->bytes >= ((size_t)(n_rows - 1) * row_stride + base_off + pld) * 2 &&
                    dst->bytes >= (size_t)n_rows * pld * 2,
                "gather_strided_f16: buffers too small");
-    gather_strided_kernel<<<cdiv(n_rows * pld, 256), 256, 0, b->stream>>>(
-        (const __half *)src->dptr, (__half *)dst->dptr, row_stride, base_off, pld, n_rows);
+    LC_LAUNCH_CHECKED(lc_launch(gather_strided_kernel, dim3(cdiv(n_rows * pld, 256)), dim3(256), 0, b, (const __half *)src->dptr, (__half *)dst->dptr, row_stride, base_off, pld, n_rows));
     LC_CHECK_LAUNCH("gather_strided_f16");
     b->dispatch_count++;
     return LC_OK;
@@ -302,8 +319,8 @@ int lc_embed_rows_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *table, con
                    output->bytes >= (size_t)n_rows * cols * 2,
                "embed_rows_q4_0: buffers too small");
     if (n_rows == 0) return LC_OK;
-    embed_rows_q4_0_kernel<<<n_rows, 256, 0, b->stream>>>((const uint8_t *)table->dptr, (const uint32_t *)tokens->dptr,
-                                                          (__half *)output->dptr, cols, scale, scale != 1.0f);
+    LC_LAUNCH_CHECKED(lc_launch(embed_rows_q4_0_kernel, dim3(n_rows), dim3(256), 0, b, (const uint8_t *)table->dptr, (const uint32_t *)tokens->dptr,
+                                                          (__half *)output->dptr, cols, scale, scale != 1.0f));
     LC_CHECK_LAUNCH("embed_rows_q4_0");
     b->dispatch_count++;
     return LC_OK;
@@ -316,7 +333,7 @@ int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc
     LC_REQUIRE(values->bytes >= (size_t)rows * cols * 4 && out_index->bytes >= (size_t)rows * 4,
                "argmax_rows_f32: buffers too small");
     if (rows == 0) return LC_OK;
-    argmax_rows_kernel<<<rows, 1024, 0, b->stream>>>((const float *)values->dptr, (uint32_t *)out_index->dptr, cols);
+    LC_LAUNCH_CHECKED(lc_launch(argmax_rows_kernel, dim3(rows), dim3(1024), 0, b, (const float *)values->dptr, (uint32_t *)out_index->dptr, cols));
     LC_CHECK_LAUNCH("argmax_rows_f32");
     b->dispatch_count++;
     return LC_OK;

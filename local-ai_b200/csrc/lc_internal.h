@@ -14,6 +14,7 @@ struct lc_ctx {
     size_t smem_optin = 0;
     size_t l2_bytes = 0;
     size_t total_mem = 0;
+    bool pdl = true;  // launch kernels with programmatic stream serialization (LOCAL_CUDA_PDL=0 disables)
 };
 
 struct lc_buf {
@@ -72,6 +73,13 @@ void lc_clear_error();
         if (!(cond)) return lc_fail(LC_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
     } while (0)
 
+#define LC_LAUNCH_CHECKED(expr)                                                        \
+    do {                                                                               \
+        cudaError_t _le = (expr);                                                      \
+        if (_le != cudaSuccess)                                                        \
+            return lc_fail(LC_ERR_CUDA, "launch: %s", cudaGetErrorString(_le));         \
+    } while (0)
+
 // After a kernel launch: surface launch-configuration errors as a status.
 #define LC_CHECK_LAUNCH(name)                                                          \
     do {                                                                               \
@@ -79,6 +87,31 @@ void lc_clear_error();
         if (_e != cudaSuccess)                                                         \
             return lc_fail(LC_ERR_CUDA, "launch %s: %s", name, cudaGetErrorString(_e)); \
     } while (0)
+
+// Every kernel of this library is launched through lc_launch so that it can start while its
+// predecessor on the stream is still draining (programmatic dependent launch): a kernel calls
+// lc_pdl_trigger() at its top — its successors may then be scheduled — and lc_pdl_wait() before it
+// first touches memory a predecessor may have written.  Work that does not depend on the predecessor
+// (streaming constant weights towards the SM) goes before the wait.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t lc_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, lc_batch *b,
+                                    Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = b->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = b->ctx->pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void lc_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void lc_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 static inline bool lc_aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 

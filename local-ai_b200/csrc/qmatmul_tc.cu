@@ -28,6 +28,7 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status
 // word, skips to the TMEM release and returns.
+#include <stdlib.h>
 #include "lc_internal.h"
 
 namespace {
@@ -135,6 +136,7 @@ struct TcParams {
     int sb;                // activation stages (6 when they fit, else 3); weight stages are fixed at 2
     int tmem_cols;         // power of two >= max(32, NB)
     int *status;
+    long long *prof;   // optional: cycle stamps of CTA (0,0,0), for tuning
 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t addr) {
@@ -170,6 +172,9 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    lc_pdl_trigger();
+    const bool prof = p.prof && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (prof && tid == 0) p.prof[0] = clock64();
     int grp = 0;
     while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
     const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * TILE_ROWS, m0 = blockIdx.y * MAX_NB;
@@ -195,6 +200,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (prof && tid == 0) p.prof[1] = clock64();
     const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
     const int nphases = (kbe - kbs + PB - 1) / PB;
     const int total_tiles = ((kbe - kbs) * BE) / KT;
@@ -226,10 +232,6 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             ok = __shfl_sync(0xffffffffu, ok, 0);
             return ok && !*abort_flag;
         };
-        for (int t = 0; t < PD; t++) {   // activation tiles 0 .. PD-1, one cp.async group each
-            if (t < total_tiles) load_b(t);
-            cp_async_commit();
-        }
         for (int ph = 0; ph < nphases && !dead; ph++) {
             const int kb0 = kbs + ph * PB, kb1 = min(kbe, kb0 + PB);
             const int seg = (kb1 - kb0) * BB;
@@ -251,8 +253,18 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                 }
             }
             cp_async_commit();
+            if (ph == 0) {
+                // The weights above do not depend on the previous kernel, so their copies are already in
+                // flight; the activations do: wait for the predecessor grid before touching them.
+                lc_pdl_wait();
+                for (int t = 0; t < PD; t++) {   // activation tiles 0 .. PD-1, one cp.async group each
+                    if (t < total_tiles) load_b(t);
+                    cp_async_commit();
+                }
+            }
             cp_async_wait<0>();
             __syncwarp();
+            if (prof && tid == 0 && ph == 0) p.prof[2] = clock64();
             const int ntiles = ((kb1 - kb0) * BE) / KT;
             // Per-thread constants of this phase: where each of its rows starts in the raw area (the row's
             // 16-byte skew differs from row to row) and whether the row exists.
@@ -331,6 +343,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                 if (lane == 0) mbar_arrive(smem_u32(&a_full[s]));
             }
         }
+        if (prof && tid == 0) p.prof[3] = clock64();
     } else {
         // ============================ MMA issue (one warp) ============================
         bool dead = false;
@@ -361,9 +374,11 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) *abort_flag = 1;
         }
+        if (prof && lane == 0) p.prof[4] = clock64();
     }
     tc_fence_before();
     __syncthreads();
+    if (prof && tid == 0) p.prof[5] = clock64();
     tc_fence_after();
     const bool failed = *abort_flag != 0;
     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
@@ -386,6 +401,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             }
         }
     }
+    if (prof && tid == 0) p.prof[6] = clock64();
     if (p.ks > 1 && !failed) {
         // Deterministic split-K: every split stores its f32 partial tile; the last CTA to arrive adds the
         // partials in split order and writes the result.
@@ -402,17 +418,35 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             __threadfence();
             OutT *out = reinterpret_cast<OutT *>(p.out[grp]);
             const float *part = p.partial + (size_t)tile_id * p.ks * (size_t)NB * TILE_ROWS;
-            for (int i = tid; i < NB * TILE_ROWS; i += NT2) {
+            // four rows per thread-step (float4 along the row index), splits summed in order, loads in
+            // independent batches of four so several L2 round trips are in flight per thread
+            const size_t pstride = (size_t)NB * TILE_ROWS;
+            for (int i4 = tid; i4 < NB * TILE_ROWS / 4; i4 += NT2) {
+                const int i = i4 * 4;
                 const int col = i / TILE_ROWS, lrow = i - col * TILE_ROWS;
-                const int gm = m0 + col, row = n0 + lrow;
-                if (gm < p.m && row < n_rows) {
-                    float acc = 0.f;
-                    for (int sp = 0; sp < p.ks; sp++) acc += __ldcg(part + (size_t)sp * NB * TILE_ROWS + i);
-                    store_c(out + (size_t)gm * n_rows + row, acc);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < p.ks; sp += 4) {
+                    float4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        v[u] = (sp + u < p.ks) ? __ldcg(reinterpret_cast<const float4 *>(part + (size_t)(sp + u) * pstride + i))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+                    }
+                }
+                const int gm = m0 + col;
+                if (gm < p.m) {
+                    const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (n0 + lrow + u < n_rows) store_c(out + (size_t)gm * n_rows + n0 + lrow + u, a4[u]);
                 }
             }
         }
     }
+    if (prof && tid == 0) p.prof[7] = clock64();
     if (failed && tid == 0) atomicExch(p.status, 1);
     tc_fence_before();
     __syncthreads();
@@ -434,7 +468,7 @@ int launch_tc(lc_kernels *k, lc_batch *b, TcParams &p, dim3 grid) {
         LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    kern<<<grid, NT2, smem, b->stream>>>(p);
+    LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT2), smem, b, p));
     LC_CHECK_LAUNCH("qgemm_tcgen05");
     b->dispatch_count++;
     return LC_OK;
@@ -471,6 +505,7 @@ int lc_qgemm_tcgen05_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, c
     p.tmem_cols = cols;
     p.sb = 3;
     p.status = k->dev_status;
+    p.prof = getenv("LOCAL_CUDA_TC_PROFILE") ? (long long *)(k->dev_status + 2) : nullptr;
     const int mtiles = (int)((m + MAX_NB - 1) / MAX_NB);
     // split-K so that small-n projections still fill the GPU: each split gets whole blocks and at least two k-tiles.
     const int min_blocks = fmt == FMT_Q4_0 ? 8 : 1;   // 8 Q4_0 blocks = 256 k = 2 k-tiles; 1 TQ2_0 block = 2 k-tiles
@@ -513,4 +548,13 @@ extern "C" int lc_kernels_device_status(lc_kernels *k, int *status) {
     LC_CUDA_TRY(cudaStreamSynchronize(k->ctx->stream));
     if (*status) return lc_fail(LC_ERR_TIMEOUT, "a device-side bounded wait expired (status %d)", *status);
     return LC_OK;
+}
+
+// Tuning aid: the eight cycle stamps the tensor-core matmul records for its first CTA when
+// LOCAL_CUDA_TC_PROFILE is set (entry, set-up done, weights landed, unpack done, MMAs drained,
+// after the CTA barrier, after the accumulator read-out, after the split-K merge).
+extern "C" __attribute__((visibility("default"))) int lc_debug_tc_profile(lc_kernels *k, long long *out8) {
+    if (!k || !out8) return LC_ERR_INVALID_ARGUMENT;
+    cudaStreamSynchronize(k->ctx->stream);
+    return cudaMemcpy(out8, k->dev_status + 2, 8 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? LC_OK : LC_ERR_CUDA;
 }

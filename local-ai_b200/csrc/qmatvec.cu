@@ -52,6 +52,8 @@ template <int FMT, int MT, typename OutT, bool XSMEM>
 __global__ void __launch_bounds__(NTHREADS)
 qgemv_kernel(const uint8_t *__restrict__ w, size_t w_bytes, const __half *__restrict__ x,
              OutT *__restrict__ out, int n, int K, int m, int rows_per_chunk, int nchunks) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     extern __shared__ __align__(16) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m0 = blockIdx.y * MT;
@@ -169,6 +171,8 @@ qgemv_kernel(const uint8_t *__restrict__ w, size_t w_bytes, const __half *__rest
 __global__ void __launch_bounds__(NTHREADS)
 matvec_tq2_0_soa_kernel(const uint8_t *__restrict__ qs, const __half *__restrict__ scales,
                         const __half *__restrict__ x, __half *__restrict__ out, int rows, int K) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * NWARPS + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -196,6 +200,8 @@ matvec_tq2_0_soa_kernel(const uint8_t *__restrict__ qs, const __half *__restrict
 // shaders/tq2_dequant.metal:4-16, over all elements.
 __global__ void tq2_dequant_kernel(const uint8_t *__restrict__ packed, const __half *__restrict__ scales,
                                    __half *__restrict__ out, uint32_t n) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const uint32_t bi = i >> 2;
@@ -222,7 +228,7 @@ int launch_qgemv(lc_kernels *k, lc_batch *b, const uint8_t *w, size_t w_bytes, c
     int gx = k->ctx->sm_count * 4;
     if (gx > nchunks) gx = nchunks;
     dim3 grid(gx, (m + MT - 1) / MT);
-    kern<<<grid, NTHREADS, smem, b->stream>>>(w, w_bytes, x, out, n, K, m, rpc, nchunks);
+    LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NTHREADS), smem, b, w, w_bytes, x, out, n, K, m, rpc, nchunks));
     LC_CHECK_LAUNCH("qgemv");
     b->dispatch_count++;
     return LC_OK;
@@ -320,9 +326,8 @@ int lc_matvec_tq2_0_soa_into(lc_kernels *k, lc_batch *b, const lc_buf *qs, const
                "matvec_tq2_0_soa: vector/output buffers too small");
     LC_REQUIRE(lc_aligned(qs->dptr, 4) && lc_aligned(vector->dptr, 4), "matvec_tq2_0_soa: buffers must be 4-byte aligned");
     if (rows == 0) return LC_OK;
-    matvec_tq2_0_soa_kernel<<<(rows + NWARPS - 1) / NWARPS, NTHREADS, 0, b->stream>>>(
-        (const uint8_t *)qs->dptr, (const __half *)scales->dptr, (const __half *)vector->dptr,
-        (__half *)output->dptr, (int)rows, (int)cols);
+    LC_LAUNCH_CHECKED(lc_launch(matvec_tq2_0_soa_kernel, dim3((rows + NWARPS - 1) / NWARPS), dim3(NTHREADS), 0, b, (const uint8_t *)qs->dptr, (const __half *)scales->dptr, (const __half *)vector->dptr,
+        (__half *)output->dptr, (int)rows, (int)cols));
     LC_CHECK_LAUNCH("matvec_tq2_0_soa");
     b->dispatch_count++;
     return LC_OK;
@@ -354,8 +359,7 @@ int lc_tq2_dequant(lc_kernels *k, lc_ctx *ctx, const lc_buf *packed, const lc_bu
                "tq2_dequant: buffers too small for %u elements", num_elements);
     if (num_elements == 0) return LC_OK;
     return lc_run_and_wait(ctx, [&](lc_batch *b) {
-        tq2_dequant_kernel<<<(num_elements + 255) / 256, 256, 0, b->stream>>>(
-            (const uint8_t *)packed->dptr, (const __half *)scales->dptr, (__half *)output->dptr, num_elements);
+        LC_LAUNCH_CHECKED(lc_launch(tq2_dequant_kernel, dim3((num_elements + 255) / 256), dim3(256), 0, b, (const uint8_t *)packed->dptr, (const __half *)scales->dptr, (__half *)output->dptr, num_elements));
         LC_CHECK_LAUNCH("tq2_dequant");
         b->dispatch_count++;
         return (int)LC_OK;

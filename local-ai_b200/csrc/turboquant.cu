@@ -51,6 +51,8 @@ __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *
                                  __half *__restrict__ norms, const uint32_t *__restrict__ positions,
                                  unsigned hd, unsigned n_kv, unsigned lane_capacity, unsigned bits,
                                  unsigned position, unsigned ring, int norm_mode) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[MAX_HD];
     __shared__ float red[MAX_HD];
     __shared__ unsigned code_sh[MAX_HD];
@@ -122,6 +124,8 @@ __global__ void dequantize_kv_kernel(const uint8_t *__restrict__ packed, const _
                                      const float *__restrict__ levels, const float *__restrict__ signs,
                                      __half *__restrict__ output, unsigned hd, unsigned n_kv, unsigned bits,
                                      unsigned group_offset, unsigned ring) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[MAX_HD];
     const unsigned t = threadIdx.x;
     const size_t g = (size_t)blockIdx.x + group_offset;
@@ -147,6 +151,8 @@ __device__ __forceinline__ void st_from_float(__half *p, float v) { *p = __float
 template <typename TIn, typename TOut>
 __global__ void hadamard_rotate_kernel(const TIn *__restrict__ input, const float *__restrict__ signs,
                                        TOut *__restrict__ output, unsigned hd, unsigned pre, unsigned post) {
+    lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
+    lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[MAX_HD];
     const unsigned t = threadIdx.x;
     const size_t base = (size_t)blockIdx.x * hd;
@@ -178,8 +184,7 @@ int rotate_into(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *inpu
     LC_REQUIRE(input->bytes >= n * sizeof(TIn) && output->bytes >= n * sizeof(TOut) && signs->bytes >= hd * 4,
                "%s: buffers too small for %u heads of %u", name, heads, hd);
     if (heads == 0) return LC_OK;
-    hadamard_rotate_kernel<TIn, TOut><<<heads, hd, 0, b->stream>>>(
-        (const TIn *)input->dptr, (const float *)signs->dptr, (TOut *)output->dptr, hd, pre, post);
+    LC_LAUNCH_CHECKED(lc_launch(hadamard_rotate_kernel<TIn, TOut>, dim3(heads), dim3(hd), 0, b, (const TIn *)input->dptr, (const float *)signs->dptr, (TOut *)output->dptr, hd, pre, post));
     LC_CHECK_LAUNCH(name);
     b->dispatch_count++;
     return LC_OK;
@@ -288,10 +293,9 @@ int lc_encode_kv_turboquant_into(lc_kernels *k, lc_batch *b, const lc_buf *input
     LC_REQUIRE(packed->bytes >= rows * n_kv_heads * cb && norms->bytes >= rows * n_kv_heads * 2,
                "encode_kv_turboquant: cache buffers hold fewer than %zu rows", rows);
     if (groups == 0) return LC_OK;
-    encode_kv_kernel<false><<<(unsigned)groups, head_dim, 0, b->stream>>>(
-        (const __half *)input->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
+    LC_LAUNCH_CHECKED(lc_launch(encode_kv_kernel<false>, dim3((unsigned)groups), dim3(head_dim), 0, b, (const __half *)input->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
         (uint8_t *)packed->dptr, (__half *)norms->dptr, nullptr, head_dim, n_kv_heads, 0, bits, position,
-        ring_capacity, k->kv_norm_mode);
+        ring_capacity, k->kv_norm_mode));
     LC_CHECK_LAUNCH("encode_kv_turboquant");
     b->dispatch_count++;
     return LC_OK;
@@ -329,10 +333,9 @@ int lc_encode_kv_turboquant_batched_into(lc_kernels *k, lc_batch *b, const lc_bu
     LC_REQUIRE(packed->bytes >= rows * n_kv_heads * cb && norms->bytes >= rows * n_kv_heads * 2,
                "encode_kv_turboquant_batched: pool buffers hold fewer than %zu rows", rows);
     if (groups == 0) return LC_OK;
-    encode_kv_kernel<true><<<(unsigned)groups, head_dim, 0, b->stream>>>(
-        (const __half *)input->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
+    LC_LAUNCH_CHECKED(lc_launch(encode_kv_kernel<true>, dim3((unsigned)groups), dim3(head_dim), 0, b, (const __half *)input->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
         (uint8_t *)packed->dptr, (__half *)norms->dptr, (const uint32_t *)positions->dptr, head_dim, n_kv_heads,
-        lane_capacity, bits, 0, ring_capacity, k->kv_norm_mode);
+        lane_capacity, bits, 0, ring_capacity, k->kv_norm_mode));
     LC_CHECK_LAUNCH("encode_kv_turboquant_batched");
     b->dispatch_count++;
     return LC_OK;
@@ -357,10 +360,9 @@ int lc_dequantize_kv_turboquant_into(lc_kernels *k, lc_batch *b, const lc_buf *p
     LC_REQUIRE(levels->bytes >= (4u << bits) && signs->bytes >= head_dim * 4u,
                "dequantize_kv_turboquant: codec buffers too small");
     const unsigned groups = n_kv_heads * (num_tokens - token_start);
-    dequantize_kv_kernel<<<groups, head_dim, 0, b->stream>>>(
-        (const uint8_t *)packed->dptr, (const __half *)norms->dptr, (const float *)levels->dptr,
+    LC_LAUNCH_CHECKED(lc_launch(dequantize_kv_kernel, dim3(groups), dim3(head_dim), 0, b, (const uint8_t *)packed->dptr, (const __half *)norms->dptr, (const float *)levels->dptr,
         (const float *)signs->dptr, (__half *)output->dptr, head_dim, n_kv_heads, bits,
-        token_start * n_kv_heads, ring_capacity);
+        token_start * n_kv_heads, ring_capacity));
     LC_CHECK_LAUNCH("dequantize_kv_turboquant");
     b->dispatch_count++;
     return LC_OK;
