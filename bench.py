@@ -316,41 +316,83 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
+def _load_module(name: str, path: Path):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def run_reference(args, rank: int, world: int) -> None:
-    """The reference's CPU path for this workload on the host cores (rank 0 only)."""
+    """The reference's CPU path for this workload on the host cores (rank 0 only): the reference is Rust +
+    Metal and cannot be built or run here, so this arm times the oracle's restatement of what the reference
+    computes on a CPU, with all host threads, on a bounded sample of the same workload."""
     if rank != 0:
         return
     orc = entry.load_oracle()
-    import importlib.util
-    spec = importlib.util.spec_from_file_location("la_synth", ROOT / "local-ai_b200" / "synth.py")
-    synth = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(synth)
+    synth = _load_module("la_synth", ROOT / "local-ai_b200" / "synth.py")
     name = args.workload
-    shapes = {"matvec_tq2_0": ("tq2_0", 8192, 1536, 1), "matvec_q4_0": ("q4_0", 6144, 1536, 1),
-              "matmul_tq2_0_m16": ("tq2_0", 8192, 1536, 16), "matmul_tq2_0_m64": ("tq2_0", 8192, 1536, 64),
-              "matvec_vocab_q4_0": ("q4_0", 262144, 1536, 1)}
-    fmt, rows, cols, m = shapes[name]
-    w = (synth.q4_0_weights if fmt == "q4_0" else synth.tq2_0_weights)(rows, cols, seed=1)
-    x = synth.normal_f16((m, cols), seed=2)
-    f = orc.Q4_0 if fmt == "q4_0" else orc.TQ2_0
-    alg = w.size + m * cols * 2 + m * rows * 2
     threads = orc.num_threads()
-    for _ in range(args.warmup):
-        orc.baseline_matmul_nt(f, x, w, m, cols, rows, 0)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        orc.baseline_matmul_nt(f, x, w, m, cols, rows, 0)
-    dt = (time.perf_counter() - t0) / args.steps
-    val = alg / dt / 1e9
-    sample = f"each step = one {rows}x{cols} {fmt} matrix (dequant to f16 + naive f32 dot), {threads} OpenMP threads"
+    note = ("CPU restatement of the reference's arithmetic (oracle/); the reference's Metal path is unavailable on "
+            "this box and its Rust toolchain is absent")
+    if name.startswith("decode"):
+        import ctypes as C
+
+        class Cfg:  # the lc_model_config field names the oracle model reads
+            pass
+
+        lanes_full, context, n_layers, vocab = {"decode_b64": (64, 8192, 35, 262144), "decode_b1": (1, 8192, 35, 262144),
+                                                "decode_b64_small": (64, 2048, 5, 32768)}[name]
+        cfg = Cfg()
+        cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.inter = 1536, 8, 1, 256, 6144
+        cfg.vocab, cfg.n_layers, cfg.kv_bits = vocab, n_layers, 2
+        sample_lanes = min(lanes_full, 2)
+        cfg.max_lanes, cfg.max_context = sample_lanes, context + 512
+        cfg.rms_eps, cfg.rope_theta, cfg.softmax_scale = 1e-6, 1e6, 1.0 / 16.0
+        cfg.embed_scale = float(np.sqrt(np.float32(1536)))
+        model = _load_module("la_model_shapes", ROOT / "oracle" / "synth_model.py")
+        layers, emb, fnorm, geo = model.build(synth, cfg, context)
+        om = orc.OracleModel(cfg, layers, emb, fnorm, geo)
+        tok = (synth.splitmix64(7, sample_lanes) % np.uint64(vocab)).astype(np.uint32)
+        pos = np.full(sample_lanes, context, np.uint32)
+        for _ in range(min(args.warmup, 1)):
+            om.decode_batch_step(tok, pos)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            om.decode_batch_step(tok, pos)
+        dt = (time.perf_counter() - t0) / args.steps
+        val = sample_lanes / dt
+        metric, unit = f"decode_tok_s_batch{lanes_full}", "tok/s"
+        sample = (f"each step = {sample_lanes} of the {lanes_full} lanes, one token each at context {context}, all {n_layers} "
+                  f"layers + vocabulary projection, {threads} OpenMP threads")
+        wl_name = f"decode step, E2B-like dense decoder {n_layers} layers, batch {lanes_full}, context {context}"
+    else:
+        shapes = {"matvec_tq2_0": ("tq2_0", 8192, 1536, 1), "matvec_q4_0": ("q4_0", 6144, 1536, 1),
+                  "matmul_tq2_0_m16": ("tq2_0", 8192, 1536, 16), "matmul_tq2_0_m64": ("tq2_0", 8192, 1536, 64),
+                  "matvec_vocab_q4_0": ("q4_0", 262144, 1536, 1)}
+        fmt, rows, cols, m = shapes[name]
+        w = (synth.q4_0_weights if fmt == "q4_0" else synth.tq2_0_weights)(rows, cols, seed=1)
+        x = synth.normal_f16((m, cols), seed=2)
+        f = orc.Q4_0 if fmt == "q4_0" else orc.TQ2_0
+        alg = w.size + m * cols * 2 + m * rows * 2
+        for _ in range(args.warmup):
+            orc.baseline_matmul_nt(f, x, w, m, cols, rows, 0)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            orc.baseline_matmul_nt(f, x, w, m, cols, rows, 0)
+        dt = (time.perf_counter() - t0) / args.steps
+        val = alg / dt / 1e9
+        metric, unit = "fused_quant_matvec_hbm_gbs", "GB/s"
+        sample = f"each step = one {rows}x{cols} {fmt} matrix (dequant to f16 + naive f32 dot), {threads} OpenMP threads"
+        wl_name = name
     print(json.dumps({
-        "impl": "reference", "metric": "fused_quant_matvec_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "note": "CPU restatement of the reference's qat_recover dequant + test-checker dot; "
-                   "the reference's Metal path is unavailable on this box"},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": wl_name, "note": note},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
