@@ -343,6 +343,26 @@ LC_API int lc_logit_softcap_gpu_into(lc_kernels *k, lc_batch *b, lc_buf *data, f
 LC_API int lc_gather_strided_f16_into(lc_kernels *k, lc_batch *b, const lc_buf *src, lc_buf *dst,
                                       uint32_t row_stride, uint32_t base_off, uint32_t pld,
                                       uint32_t n_rows);                             /* kernels.rs:2801 */
+/* Fused forms of dispatch pairs the forward pass always issues back to back; each keeps the f16
+ * rounding points of the unfused sequence.
+ *  - qk_norm + rope_batch_decode in place (the reference's own fusion: qk_norm_rope_into, kernels.rs:2302);
+ *  - rms_norm_add followed by rms_norm of its result (layer.rs:808-822, 843-853): two outputs;
+ *  - the KV write of a decode step: k_norm, V rms_norm with unit weights, RoPE on K, TurboQuant encode of
+ *    both rows into the per-lane pools (layer.rs:773-790 + kv_cache/quant_unified_pool.rs:138-181). */
+LC_API int lc_qk_norm_rope_batch_decode_into(lc_kernels *k, lc_batch *b, lc_buf *qk, const lc_buf *weight,
+                                             const lc_buf *positions, float theta, uint32_t head_dim,
+                                             uint32_t num_heads, uint32_t seq_len, float eps,
+                                             float partial_rotary_factor);
+LC_API int lc_rms_norm_add_norm_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                                     const lc_buf *residual, lc_buf *out_residual, const lc_buf *weight2,
+                                     lc_buf *out_normed, uint32_t dim, uint32_t rows, float eps);
+LC_API int lc_kv_write_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *k_in, const lc_buf *v_in,
+                                    const lc_buf *k_norm_weight, const lc_buf *positions, const lc_buf *levels,
+                                    const lc_buf *signs, lc_buf *k_packed, lc_buf *k_norms, lc_buf *v_packed,
+                                    lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
+                                    uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes,
+                                    uint32_t ring_capacity, float eps, float rope_theta,
+                                    float partial_rotary_factor);
 /* Device-side stand-ins for two CPU steps the reference performs through unified
  * memory: the embedding-row gather (QuantWeight::dequant_row, local-engine/src/layer.rs:255-281,
  * followed by scale_in_place) and greedy first-max argmax (sampler.rs:148-158). */

@@ -8,6 +8,9 @@
 //              -> KV encode into the per-lane pool -> attention over codes (rotate, attend, rotate back)
 //              -> O -> rms_norm_add -> rms_norm -> gate, up -> gelu_mul -> down -> rms_norm_add
 //   final rms_norm -> vocabulary projection (all lanes in one pass) -> optional greedy argmax
+// Launch count is cut by issuing Q/K/V and gate/up as grouped matmuls and by the fused forms of
+// q_norm+rope, the KV write, and rms_norm_add+rms_norm; the arithmetic and its f16 rounding points
+// are those of the unfused sequence.
 //
 // Everything between ops is f16, as the reference's scratch buffers are
 // (layer.rs:873-1036).  The model object owns the KV pools (QuantizedUnifiedKvPool,
@@ -18,6 +21,9 @@
 #include <vector>
 
 #include "lc_internal.h"
+
+int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
+                               lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk);
 
 struct lc_model_layer {
     const lc_buf *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr,
@@ -208,34 +214,40 @@ int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *toke
 #define STEP(call) do { if ((st = (call)) != LC_OK) return st; } while (0)
     STEP(lc_embed_rows_q4_0_into(k, b, m->embed, tokens, m->x, n, H, c.vocab, c.embed_scale));
     lc_buf *x = m->x, *xn = m->x2;
-    for (lc_model_layer &L : m->layers) {
-        STEP(lc_rms_norm_into(k, b, x, L.attn_norm, m->normed, H, n, c.rms_eps));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wq, m->q, n, H, qd));
-        STEP(lc_qk_norm_gpu_into(k, b, m->q, L.q_norm, HD, n * NQ, c.rms_eps));
-        STEP(lc_rope_batch_decode_into(k, b, m->q, positions, c.rope_theta, HD, NQ, n, 1.0f));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wk, m->kbuf, n, H, kd));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wv, m->vbuf, n, H, kd));
-        STEP(lc_qk_norm_gpu_into(k, b, m->kbuf, L.k_norm, HD, n * NKV, c.rms_eps));
-        STEP(lc_rms_norm_into(k, b, m->vbuf, m->ones, m->vbuf, HD, n * NKV, c.rms_eps));
-        STEP(lc_rope_batch_decode_into(k, b, m->kbuf, positions, c.rope_theta, HD, NKV, n, 1.0f));
-        STEP(lc_encode_kv_turboquant_batched_into(k, b, m->kbuf, m->levels, m->signs, L.k_codes, L.k_norms, positions,
-                                                  HD, NKV, L.lane_rows, c.kv_bits, n, L.ring));
-        STEP(lc_encode_kv_turboquant_batched_into(k, b, m->vbuf, m->levels, m->signs, L.v_codes, L.v_norms, positions,
-                                                  HD, NKV, L.lane_rows, c.kv_bits, n, L.ring));
+    const size_t nl = m->layers.size();
+    STEP(lc_rms_norm_into(k, b, x, m->layers[0].attn_norm, m->normed, H, n, c.rms_eps));
+    for (size_t li = 0; li < nl; li++) {
+        lc_model_layer &L = m->layers[li];
+        // Q, K, V in one grouped launch (same activations); q_norm + RoPE fused; the KV write fused
+        {
+            const lc_buf *ws[3] = {L.wq, L.wk, L.wv};
+            lc_buf *os[3] = {m->q, m->kbuf, m->vbuf};
+            const uint32_t ns[3] = {qd, kd, kd};
+            STEP(lc_matmul_nt_tq2_0_grouped(k, b, m->normed, 3, ws, os, ns, n, H));
+        }
+        STEP(lc_qk_norm_rope_batch_decode_into(k, b, m->q, L.q_norm, positions, c.rope_theta, HD, NQ, n, c.rms_eps, 1.0f));
+        STEP(lc_kv_write_batched_into(k, b, m->kbuf, m->vbuf, L.k_norm, positions, m->levels, m->signs, L.k_codes,
+                                      L.k_norms, L.v_codes, L.v_norms, HD, NKV, L.lane_rows, c.kv_bits, n, L.ring,
+                                      c.rms_eps, c.rope_theta, 1.0f));
         STEP(lc_tq_attention_batched_into(k, b, m->q, L.k_codes, L.k_norms, L.v_codes, L.v_norms, m->levels, m->signs,
                                           m->attn, positions, HD, L.lane_rows, NQ, NKV, L.window, c.kv_bits, n, L.ring,
                                           c.softmax_scale));
         STEP(lc_matmul_nt_tq2_0_into(k, b, m->attn, L.wo, m->ffn, n, qd, H));
-        STEP(lc_rms_norm_add_into(k, b, m->ffn, L.post_attn_norm, x, m->resid, H, n, c.rms_eps));
-        STEP(lc_rms_norm_into(k, b, m->resid, L.ffn_norm, m->normed, H, n, c.rms_eps));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wgate, m->gate, n, H, I));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->normed, L.wup, m->up, n, H, I));
+        // resid = rms_norm(ffn, post_attn) + x ; normed = rms_norm(resid, ffn_norm)
+        STEP(lc_rms_norm_add_norm_into(k, b, m->ffn, L.post_attn_norm, x, m->resid, L.ffn_norm, m->normed, H, n, c.rms_eps));
+        {
+            const lc_buf *ws[2] = {L.wgate, L.wup};
+            lc_buf *os[2] = {m->gate, m->up};
+            const uint32_t ns[2] = {I, I};
+            STEP(lc_matmul_nt_tq2_0_grouped(k, b, m->normed, 2, ws, os, ns, n, H));
+        }
         STEP(lc_gelu_mul_into(k, b, m->gate, m->up, m->gate, n * I));
         STEP(lc_matmul_nt_tq2_0_into(k, b, m->gate, L.wdown, m->ffn, n, I, H));
-        STEP(lc_rms_norm_add_into(k, b, m->ffn, L.post_ffn_norm, m->resid, xn, H, n, c.rms_eps));
+        // x' = rms_norm(ffn, post_ffn) + resid ; normed = rms_norm(x', next layer's attention norm | final norm)
+        const lc_buf *next_norm = li + 1 < nl ? m->layers[li + 1].attn_norm : m->final_norm;
+        STEP(lc_rms_norm_add_norm_into(k, b, m->ffn, L.post_ffn_norm, m->resid, xn, next_norm, m->normed, H, n, c.rms_eps));
         lc_buf *t = x; x = xn; xn = t;
     }
-    STEP(lc_rms_norm_into(k, b, x, m->final_norm, m->normed, H, n, c.rms_eps));
     if (want_logits || next_tokens) {
         STEP(lc_matmul_nt_q4_0_f32out_into(k, b, m->normed, m->embed, m->logits, n, H, c.vocab));
         if (next_tokens) STEP(lc_argmax_rows_f32_into(k, b, m->logits, next_tokens, n, c.vocab));

@@ -181,6 +181,70 @@ __global__ void argmax_rows_kernel(const float *__restrict__ v, uint32_t *__rest
     }
 }
 
+// Fused per-head RMSNorm + NEOX RoPE in place (shaders/qk_norm.metal:70-144 qk_norm_rope): identical to
+// qk_norm followed by rope_batch_decode, including the f16 rounding between the two.
+// grid = rows * heads, block = head_dim / 2; thread i owns the pair (i, i + head_dim/2).
+__global__ void qk_norm_rope_kernel(__half *qk, const __half *__restrict__ weight, const uint32_t *__restrict__ positions,
+                                    float theta, unsigned hd, unsigned heads, float eps, float factor) {
+    lc_pdl_trigger();
+    lc_pdl_wait();
+    __shared__ float sh[32];
+    const unsigned half = hd / 2, i = threadIdx.x;
+    const unsigned rh = blockIdx.x, row = rh / heads;
+    __half *p = qk + (size_t)rh * hd;
+    const float a = __half2float(p[i]), c = __half2float(p[i + half]);
+    const float ss = block_sum(fmaf(a, a, c * c), sh);
+    const float rms = rsqrtf(ss / (float)hd + eps);
+    const float n0 = __half2float(__float2half_rn(a * rms * __half2float(weight[i])));
+    const float n1 = __half2float(__float2half_rn(c * rms * __half2float(weight[i + half])));
+    const unsigned angles = (unsigned)((float)hd * factor) / 2;
+    if (i >= angles) {
+        p[i] = __float2half_rn(n0);
+        p[i + half] = __float2half_rn(n1);
+        return;
+    }
+    const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)hd);
+    const float ang = (float)positions[row] * freq;
+    const float cs = cosf(ang), sn = sinf(ang);
+    p[i] = __float2half_rn(n0 * cs - n1 * sn);
+    p[i + half] = __float2half_rn(n0 * sn + n1 * cs);
+}
+
+// Two dependent norms in one pass over a row (the pair every decoder layer issues back to back,
+// local-engine/src/layer.rs:808-822, 843-853 + the next layer's attention norm):
+//   resid  = f16(rms_norm(in, w1) + residual)           (rms_norm_add)
+//   normed = f16(rms_norm(resid, w2))                   (rms_norm)
+// The f16 `resid` row is kept in shared memory between the two.  grid = rows, dynamic smem = dim * 2 bytes.
+__global__ void rms_norm_add_norm_kernel(const __half *in, const __half *__restrict__ w1, const __half *residual,
+                                         __half *out_resid, const __half *__restrict__ w2, __half *out_normed,
+                                         unsigned dim, float eps) {
+    lc_pdl_trigger();
+    lc_pdl_wait();
+    extern __shared__ __align__(16) __half row_s[];
+    __shared__ float sh[32];
+    const size_t base = (size_t)blockIdx.x * dim;
+    float s = 0.f;
+    for (unsigned i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = __half2float(in[base + i]);
+        s = fmaf(v, v, s);
+    }
+    s = block_sum(s, sh);
+    const float rms1 = rsqrtf(s / (float)dim + eps);
+    float s2 = 0.f;
+    for (unsigned i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = __half2float(in[base + i]) * rms1 * __half2float(w1[i]) + __half2float(residual[base + i]);
+        const __half h = __float2half_rn(v);
+        row_s[i] = h;
+        out_resid[base + i] = h;
+        const float hv = __half2float(h);
+        s2 = fmaf(hv, hv, s2);
+    }
+    s2 = block_sum(s2, sh);
+    const float rms2 = rsqrtf(s2 / (float)dim + eps);
+    for (unsigned i = threadIdx.x; i < dim; i += blockDim.x)
+        out_normed[base + i] = __float2half_rn(__half2float(row_s[i]) * rms2 * __half2float(w2[i]));
+}
+
 inline unsigned cdiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
 
 int rms_norm_common(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
@@ -335,6 +399,50 @@ int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc
     if (rows == 0) return LC_OK;
     LC_LAUNCH_CHECKED(lc_launch(argmax_rows_kernel, dim3(rows), dim3(1024), 0, b, (const float *)values->dptr, (uint32_t *)out_index->dptr, cols));
     LC_CHECK_LAUNCH("argmax_rows_f32");
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+
+int lc_qk_norm_rope_batch_decode_into(lc_kernels *k, lc_batch *b, lc_buf *qk, const lc_buf *weight, const lc_buf *positions,
+                                      float theta, uint32_t head_dim, uint32_t num_heads, uint32_t seq_len, float eps,
+                                      float partial_rotary_factor) {
+    if (!k || !b || !qk || !weight || !positions) return lc_fail(LC_ERR_INVALID_ARGUMENT, "qk_norm_rope: NULL argument");
+    LC_REQUIRE(head_dim >= 2 && head_dim % 2 == 0 && head_dim <= 2048, "qk_norm_rope: head_dim %u must be even and <= 2048", head_dim);
+    LC_REQUIRE(qk->bytes >= (size_t)seq_len * num_heads * head_dim * 2 && positions->bytes >= (size_t)seq_len * 4 &&
+                   weight->bytes >= head_dim * 2u,
+               "qk_norm_rope: buffers too small");
+    if (seq_len * num_heads == 0) return LC_OK;
+    LC_LAUNCH_CHECKED(lc_launch(qk_norm_rope_kernel, dim3(seq_len * num_heads), dim3(head_dim / 2), 0, b, (__half *)qk->dptr,
+                                (const __half *)weight->dptr, (const uint32_t *)positions->dptr, theta, head_dim, num_heads,
+                                eps, partial_rotary_factor));
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+int lc_rms_norm_add_norm_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight, const lc_buf *residual,
+                              lc_buf *out_residual, const lc_buf *weight2, lc_buf *out_normed, uint32_t dim, uint32_t rows,
+                              float eps) {
+    if (!k || !b || !input || !weight || !residual || !out_residual || !weight2 || !out_normed)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "rms_norm_add_norm: NULL argument");
+    LC_REQUIRE(dim >= 1 && dim <= 32768, "rms_norm_add_norm: dim %u out of range", dim);
+    const size_t n = (size_t)dim * rows * 2;
+    LC_REQUIRE(input->bytes >= n && residual->bytes >= n && out_residual->bytes >= n && out_normed->bytes >= n &&
+                   weight->bytes >= (size_t)dim * 2 && weight2->bytes >= (size_t)dim * 2,
+               "rms_norm_add_norm: buffers too small for %u rows of %u", rows, dim);
+    if (rows == 0) return LC_OK;
+    const unsigned threads = dim >= 1024 ? 512 : (dim >= 256 ? 256 : 64);
+    const size_t smem = (size_t)dim * 2;
+    if (smem > 48 * 1024) {
+        static size_t configured = 0;
+        if (smem > configured) {
+            LC_CUDA_TRY(cudaFuncSetAttribute(rms_norm_add_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured = smem;
+        }
+    }
+    LC_LAUNCH_CHECKED(lc_launch(rms_norm_add_norm_kernel, dim3(rows), dim3(threads), smem, b, (const __half *)input->dptr,
+                                (const __half *)weight->dptr, (const __half *)residual->dptr, (__half *)out_residual->dptr,
+                                (const __half *)weight2->dptr, (__half *)out_normed->dptr, dim, eps));
     b->dispatch_count++;
     return LC_OK;
 }

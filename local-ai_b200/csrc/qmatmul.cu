@@ -29,6 +29,29 @@ static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch
     return lc_qgemm_cuda_core(fmt, f32out, k, b, input, weight, output, m, kk, n);
 }
 
+int lc_qgemm_tcgen05_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
+                             const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
+                             uint32_t kk);
+
+// Several TQ2_0 projections of the same activations (Q/K/V; gate/up) as one launch when the tensor-core
+// path applies, else one after the other.
+int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
+                               lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk) {
+    for (int g = 0; g < ng; g++) {
+        int st = lc_check_qargs(1, "matmul_nt_tq2_0", k, b, weights[g], input, outputs[g], m, kk, ns[g], 2);
+        if (st != LC_OK) return st;
+    }
+    if (k->mma && m > 8) {
+        int st = lc_qgemm_tcgen05_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
+        if (st >= 0) return st;
+    }
+    for (int g = 0; g < ng; g++) {
+        int st = lc_qgemm_cuda_core(1, false, k, b, input, weights[g], outputs[g], m, kk, ns[g]);
+        if (st != LC_OK) return st;
+    }
+    return LC_OK;
+}
+
 extern "C" {
 
 int lc_matmul_nt_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,

@@ -45,6 +45,62 @@ __device__ __forceinline__ void fwht_block(float *sh, unsigned d, unsigned t) {
 //     ring ? ((position + tok) % ring) * n_kv + head : (position + tok) * n_kv + head
 //   slot rule, per lane (BATCHED == true), dequantize_kv.metal:349-351:
 //     (lane * lane_capacity + (ring ? pos % ring : pos)) * n_kv + head
+// Encode one row held one element per thread (xv) into `packed_row` / `*norm_out`.
+// sh/red/code_sh are MAX_HD-sized shared arrays, norm_sh one shared float.  Block = hd threads.
+__device__ __forceinline__ void encode_row(float xv, unsigned t, unsigned hd, unsigned bits,
+                                           const float *__restrict__ levels, const float *__restrict__ signs,
+                                           int norm_mode, uint8_t *__restrict__ packed_row, __half *__restrict__ norm_out,
+                                           float *sh, float *red, unsigned *code_sh, float *norm_sh) {
+    const unsigned code_bytes = (hd * bits + 7) >> 3;
+    red[t] = __fmul_rn(xv, xv);
+    __syncthreads();
+    if (norm_mode == 0) {
+        if (t == 0) {
+            float s = 0.f;
+            for (unsigned i = 0; i < hd; i++) s = __fadd_rn(s, red[i]);
+            *norm_sh = __fsqrt_rn(s);
+        }
+    } else {
+        for (unsigned stride = hd >> 1; stride > 0; stride >>= 1) {
+            if (t < stride) red[t] = __fadd_rn(red[t], red[t + stride]);
+            __syncthreads();
+        }
+        if (t == 0) *norm_sh = __fsqrt_rn(red[0]);
+    }
+    __syncthreads();
+    const float norm = *norm_sh;
+    float v = xv;
+    if (norm > 0.f) v = __fmul_rn(xv, __fdiv_rn(1.0f, norm));
+    else if (norm_mode == 1) v = __fmul_rn(xv, 0.f);
+    sh[t] = __fmul_rn(v, signs[t]);
+    fwht_block(sh, hd, t);
+    const float inv_sqrt_d = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    const float y = __fmul_rn(sh[t], inv_sqrt_d);
+
+    const unsigned k = 1u << bits;
+    unsigned best = 0;
+    float bd = INFINITY;
+    for (unsigned i = 0; i < k; i++) {
+        const float dd = fabsf(__fsub_rn(y, levels[i]));
+        if (dd < bd) { bd = dd; best = i; }
+    }
+    code_sh[t] = best;
+    if (t == 0) *norm_out = __float2half_rn(norm);
+    __syncthreads();
+    // LSB-first packing, one thread per output byte.
+    if (t < code_bytes) {
+        unsigned byte_val = 0;
+        for (unsigned bp = 0; bp < 8; bp++) {
+            const unsigned gb = t * 8 + bp;
+            const unsigned ci = gb / bits;
+            if (ci >= hd) break;
+            byte_val |= ((code_sh[ci] >> (gb - ci * bits)) & 1u) << bp;
+        }
+        packed_row[t] = (uint8_t)byte_val;
+    }
+    __syncthreads();
+}
+
 template <bool BATCHED>
 __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *__restrict__ levels,
                                  const float *__restrict__ signs, uint8_t *__restrict__ packed,
@@ -69,54 +125,70 @@ __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *
         slot = (size_t)(ring ? logical % ring : logical) * n_kv + head;
     }
     const unsigned code_bytes = (hd * bits + 7) >> 3;
-
     const float xv = __half2float(input[(size_t)g_in * hd + t]);
-    red[t] = __fmul_rn(xv, xv);
-    __syncthreads();
-    if (norm_mode == 0) {
-        if (t == 0) {
-            float s = 0.f;
-            for (unsigned i = 0; i < hd; i++) s = __fadd_rn(s, red[i]);
-            norm_sh = __fsqrt_rn(s);
-        }
-    } else {
-        for (unsigned stride = hd >> 1; stride > 0; stride >>= 1) {
-            if (t < stride) red[t] = __fadd_rn(red[t], red[t + stride]);
-            __syncthreads();
-        }
-        if (t == 0) norm_sh = __fsqrt_rn(red[0]);
-    }
-    __syncthreads();
-    const float norm = norm_sh;
-    float v = xv;
-    if (norm > 0.f) v = __fmul_rn(xv, __fdiv_rn(1.0f, norm));
-    else if (norm_mode == 1) v = __fmul_rn(xv, 0.f);
-    sh[t] = __fmul_rn(v, signs[t]);
-    fwht_block(sh, hd, t);
-    const float inv_sqrt_d = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-    const float y = __fmul_rn(sh[t], inv_sqrt_d);
+    encode_row(xv, t, hd, bits, levels, signs, norm_mode, packed + slot * code_bytes, norms + slot, sh, red, code_sh,
+               &norm_sh);
+}
 
-    const unsigned k = 1u << bits;
-    unsigned best = 0;
-    float bd = INFINITY;
-    for (unsigned i = 0; i < k; i++) {
-        const float dd = fabsf(__fsub_rn(y, levels[i]));
-        if (dd < bd) { bd = dd; best = i; }
-    }
-    code_sh[t] = best;
-    if (t == 0) norms[slot] = __float2half_rn(norm);
+// The KV write of one decode step in one launch: k_norm (learned weights), V rms_norm (unit weights),
+// NEOX RoPE on K, TurboQuant encode of both rows into the per-lane pools.  Same arithmetic and the same
+// f16 rounding points as the five separate dispatches of layer.rs:773-790 + quant_unified_pool.rs:138-181.
+// grid = n_lanes * n_kv, block = head_dim.
+__global__ void kv_write_kernel(const __half *__restrict__ kin, const __half *__restrict__ vin,
+                                const __half *__restrict__ k_norm_w, const uint32_t *__restrict__ positions,
+                                const float *__restrict__ levels, const float *__restrict__ signs,
+                                uint8_t *__restrict__ k_packed, __half *__restrict__ k_norms,
+                                uint8_t *__restrict__ v_packed, __half *__restrict__ v_norms, unsigned hd, unsigned n_kv,
+                                unsigned lane_capacity, unsigned bits, unsigned ring, float eps, float theta,
+                                float rotary_factor, int norm_mode) {
+    lc_pdl_trigger();
+    lc_pdl_wait();
+    __shared__ float sh[MAX_HD];
+    __shared__ float red[MAX_HD];
+    __shared__ unsigned code_sh[MAX_HD];
+    __shared__ float norm_sh;
+    __shared__ float red2[32];
+    const unsigned t = threadIdx.x, g_in = blockIdx.x;
+    const unsigned row = g_in / n_kv, head = g_in - row * n_kv;
+    const unsigned pos = positions[row];
+    const size_t slot = ((size_t)row * lane_capacity + (ring ? pos % ring : pos)) * n_kv + head;
+    const unsigned code_bytes = (hd * bits + 7) >> 3;
+    auto block_sumsq = [&](float v) {
+        float s = v * v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if ((t & 31) == 0) red2[t >> 5] = s;
+        __syncthreads();
+        float tot = 0.f;
+        for (unsigned w = 0; w < (hd + 31) / 32; w++) tot += red2[w];
+        __syncthreads();
+        return tot;
+    };
+    // K: per-head RMSNorm with weights -> f16, RoPE -> f16
+    const float kx = __half2float(kin[(size_t)g_in * hd + t]);
+    const float krms = rsqrtf(block_sumsq(kx) / (float)hd + eps);
+    const float kn = __half2float(__float2half_rn(kx * krms * __half2float(k_norm_w[t])));
+    sh[t] = kn;
     __syncthreads();
-    // LSB-first packing, one thread per output byte.
-    if (t < code_bytes) {
-        unsigned byte_val = 0;
-        for (unsigned bp = 0; bp < 8; bp++) {
-            const unsigned gb = t * 8 + bp;
-            const unsigned ci = gb / bits;
-            if (ci >= hd) break;
-            byte_val |= ((code_sh[ci] >> (gb - ci * bits)) & 1u) << bp;
-        }
-        packed[slot * code_bytes + t] = (uint8_t)byte_val;
+    const unsigned half = hd / 2, i = t < half ? t : t - half;
+    const unsigned angles = (unsigned)((float)hd * rotary_factor) / 2;
+    float kr = kn;
+    if (i < angles) {
+        const float x0 = sh[i], x1 = sh[i + half];
+        const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)hd);
+        const float ang = (float)pos * freq;
+        const float c = cosf(ang), sn = sinf(ang);
+        kr = __half2float(__float2half_rn(t < half ? x0 * c - x1 * sn : x0 * sn + x1 * c));
     }
+    __syncthreads();
+    encode_row(kr, t, hd, bits, levels, signs, norm_mode, k_packed + slot * code_bytes, k_norms + slot, sh, red, code_sh,
+               &norm_sh);
+    // V: RMSNorm with unit weights -> f16
+    const float vx = __half2float(vin[(size_t)g_in * hd + t]);
+    const float vrms = rsqrtf(block_sumsq(vx) / (float)hd + eps);
+    const float vn = __half2float(__float2half_rn(vx * vrms * 1.0f));
+    encode_row(vn, t, hd, bits, levels, signs, norm_mode, v_packed + slot * code_bytes, v_norms + slot, sh, red, code_sh,
+               &norm_sh);
 }
 
 // dequantize_kv.metal:132-189. grid = n_kv * (num_tokens - token_start).
@@ -393,6 +465,40 @@ int lc_hadamard_rotate_fh_into(lc_kernels *k, lc_batch *b, const lc_buf *input, 
                                lc_buf *output, uint32_t head_dim, uint32_t num_heads, uint32_t pre_sign,
                                uint32_t post_sign) {
     return rotate_into<float, __half>("hadamard_rotate_fh", k, b, input, signs, output, head_dim, num_heads, pre_sign, post_sign);
+}
+
+
+int lc_kv_write_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *k_in, const lc_buf *v_in, const lc_buf *k_norm_weight,
+                             const lc_buf *positions, const lc_buf *levels, const lc_buf *signs, lc_buf *k_packed,
+                             lc_buf *k_norms, lc_buf *v_packed, lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
+                             uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes, uint32_t ring_capacity, float eps,
+                             float rope_theta, float partial_rotary_factor) {
+    if (!k || !b || !k_in || !v_in || !k_norm_weight || !positions || !levels || !signs || !k_packed || !k_norms ||
+        !v_packed || !v_norms)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "kv_write_batched: NULL argument");
+    int st = check_codec("kv_write_batched", head_dim, bits);
+    if (st != LC_OK) return st;
+    LC_REQUIRE(n_kv_heads >= 1, "kv_write_batched: n_kv_heads must be >= 1");
+    const size_t groups = (size_t)n_kv_heads * n_lanes, cb = lc_tq_code_bytes(head_dim, bits);
+    LC_REQUIRE(k_in->bytes >= groups * head_dim * 2 && v_in->bytes >= groups * head_dim * 2 &&
+                   positions->bytes >= (size_t)n_lanes * 4 && k_norm_weight->bytes >= head_dim * 2u,
+               "kv_write_batched: input buffers too small");
+    LC_REQUIRE(levels->bytes >= (4u << bits) && signs->bytes >= head_dim * 4u, "kv_write_batched: codec buffers too small");
+    LC_REQUIRE(ring_capacity <= lane_capacity, "kv_write_batched: ring %u exceeds lane capacity %u", ring_capacity,
+               lane_capacity);
+    const size_t rows = (size_t)n_lanes * lane_capacity * n_kv_heads;
+    LC_REQUIRE(k_packed->bytes >= rows * cb && v_packed->bytes >= rows * cb && k_norms->bytes >= rows * 2 &&
+                   v_norms->bytes >= rows * 2,
+               "kv_write_batched: pool buffers hold fewer than %zu rows", rows);
+    if (groups == 0) return LC_OK;
+    LC_LAUNCH_CHECKED(lc_launch(kv_write_kernel, dim3((unsigned)groups), dim3(head_dim), 0, b, (const __half *)k_in->dptr,
+                                (const __half *)v_in->dptr, (const __half *)k_norm_weight->dptr,
+                                (const uint32_t *)positions->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
+                                (uint8_t *)k_packed->dptr, (__half *)k_norms->dptr, (uint8_t *)v_packed->dptr,
+                                (__half *)v_norms->dptr, head_dim, n_kv_heads, lane_capacity, bits, ring_capacity, eps,
+                                rope_theta, partial_rotary_factor, k->kv_norm_mode));
+    b->dispatch_count++;
+    return LC_OK;
 }
 
 }  // extern "C"
