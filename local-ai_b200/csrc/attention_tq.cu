@@ -13,8 +13,10 @@
 //    rotation + f16 store in the merge kernel, removing two launches and the
 //    f32 round trips through rq / vacc.
 #include <math.h>
+#include <stdlib.h>
 
 #include "lc_internal.h"
+#include "attention_tq.h"
 
 namespace {
 
@@ -22,21 +24,6 @@ constexpr int NT = 256;
 constexpr int NW = NT / 32;
 constexpr int TILE = 32;  // keys per warp step: one key per lane in the QK phase
 
-struct TqAttnParams {
-    const float *rq;      // rotated query f32 [lanes, n_q, HD]   (fused_q == 0)
-    const __half *q;      // query f16 [lanes, n_q, HD]            (fused_q == 1)
-    const float *signs;   // [HD]
-    const uint8_t *kc, *vc;
-    const __half *kn, *vn;
-    const float *levels;  // [1 << BITS]
-    float *out;           // f32 [lanes, n_q, HD], written when n_splits == 1 and !fused
-    float *partial;       // [lanes * n_q * n_splits] x (2 + HD) floats
-    const uint32_t *positions;  // per-lane positions, or NULL for the single-sequence form
-    uint32_t kv_len, current_pos;
-    uint32_t lane_capacity, n_q, n_kv, window, ring, n_splits, group;  // group = n_q / n_kv
-    uint32_t fused_q, direct_out;
-    float scale;
-};
 
 // In-place unnormalised FWHT on `rows` rows of HD floats in shared memory,
 // cooperatively by the whole CTA.  Ends with a barrier.
@@ -370,6 +357,11 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
 
     const uint32_t group = n_q / n_kv;
     int g = group >= 8 ? 8 : (group > 4 ? 8 : (group > 2 ? 4 : (group > 1 ? 2 : 1)));
+    // tq2 at head_dim 256 runs on the tensor-core kernel (8 heads per CTA); LOCAL_CUDA_ATTN_MMA=0 keeps the
+    // CUDA-core kernel, which also serves every other head size and bit width.
+    static const bool mma_allowed = []() { const char *e = getenv("LOCAL_CUDA_ATTN_MMA"); return !(e && e[0] == '0'); }();
+    const bool use_mma = mma_allowed && hd == 256 && bits == 2;
+    if (use_mma) g = 8;
     const uint32_t gchunks = (group + g - 1) / g;
     const uint32_t base = n_lanes * n_kv * gchunks;
     uint32_t want = (2u * (uint32_t)k->ctx->sm_count + base - 1) / base;
@@ -410,11 +402,15 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     p.scale = scale;
     dim3 grid(n_splits, n_kv * gchunks, n_lanes);
     int st;
-    switch (hd) {
-        case 64: st = launch_split_b<64>(b, p, grid, g, bits); break;
-        case 128: st = launch_split_b<128>(b, p, grid, g, bits); break;
-        case 256: st = launch_split_b<256>(b, p, grid, g, bits); break;
-        default: st = launch_split_b<512>(b, p, grid, g, bits); break;
+    if (use_mma) {
+        st = lc_tq2_attn_mma_launch(b, p, grid);
+    } else {
+        switch (hd) {
+            case 64: st = launch_split_b<64>(b, p, grid, g, bits); break;
+            case 128: st = launch_split_b<128>(b, p, grid, g, bits); break;
+            case 256: st = launch_split_b<256>(b, p, grid, g, bits); break;
+            default: st = launch_split_b<512>(b, p, grid, g, bits); break;
+        }
     }
     if (st != LC_OK || direct) return st;
     if (fused)

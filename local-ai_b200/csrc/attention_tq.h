@@ -1,0 +1,23 @@
+// Parameters shared by the code-space attention kernels (CUDA-core and tensor-core variants).
+#pragma once
+#include "lc_internal.h"
+
+struct TqAttnParams {
+    const float *rq;      // rotated query f32 [lanes, n_q, HD]   (fused_q == 0)
+    const __half *q;      // query f16 [lanes, n_q, HD]            (fused_q == 1)
+    const float *signs;   // [HD]
+    const uint8_t *kc, *vc;
+    const __half *kn, *vn;
+    const float *levels;  // [1 << BITS]
+    float *out;           // f32 [lanes, n_q, HD], written when n_splits == 1 and !fused
+    float *partial;       // [lanes * n_q * n_splits] x (2 + HD) floats
+    const uint32_t *positions;  // per-lane positions, or NULL for the single-sequence form
+    uint32_t kv_len, current_pos;
+    uint32_t lane_capacity, n_q, n_kv, window, ring, n_splits, group;  // group = n_q / n_kv
+    uint32_t fused_q, direct_out;
+    float scale;
+};
+
+// Tensor-core variant for tq2 / head_dim 256 (attention_tq_mma.cu). Same grid and partial layout as the
+// CUDA-core split kernel: grid = (n_splits, n_kv * gchunks, n_lanes) with 8 q-heads per chunk.
+int lc_tq2_attn_mma_launch(lc_batch *b, const TqAttnParams &p, dim3 grid);
