@@ -24,4 +24,5 @@ from .kernels import (  # noqa: F401
 )
 from . import synth  # noqa: F401
 from . import model  # noqa: F401
+from . import sharding  # noqa: F401
 from .model import DecodeModel, ModelConfig, e2b_like_config  # noqa: F401

@@ -73,8 +73,8 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     uint2 *lut = reinterpret_cast<uint2 *>(smem);                       // [256 bytes][32 lanes] x 4 f16
     float *rq_s = reinterpret_cast<float *>(smem + LUT_BYTES);          // [G][HD] rotated, scaled query
     __shared__ float gamma_s;
-    __shared__ float cand_err[NT];
-    __shared__ int cand_idx[NT];
+    __shared__ float cand_err[NW];
+    __shared__ int cand_idx[NW];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -118,13 +118,18 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
             }
             if (e < best) { best = e; besti = j; }
         }
-        cand_err[threadIdx.x] = best;
-        cand_idx[threadIdx.x] = besti;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {   // arg-min inside the warp, lowest index on ties
+            const float oe = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, off);
+            if (oe < best || (oe == best && oi < besti)) { best = oe; besti = oi; }
+        }
+        if (lane == 0) { cand_err[warp] = best; cand_idx[warp] = besti; }
         __syncthreads();
         if (threadIdx.x == 0) {
             float b = cand_err[0];
             int bi = cand_idx[0];
-            for (int i = 1; i < NT; i++)
+            for (int i = 1; i < NW; i++)
                 if (cand_err[i] < b || (cand_err[i] == b && cand_idx[i] < bi)) { b = cand_err[i]; bi = cand_idx[i]; }
             gamma_s = ref > 0.f ? ref / (1.0f + (float)bi * (1.0f / 1024.0f)) : 1.0f;
         }
@@ -186,18 +191,31 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     for (int s = 0; s < 16; s++) o[s][0] = o[s][1] = o[s][2] = o[s][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // heads 2t, 2t+1 (l: this thread's keys only)
 
-    for (uint32_t t0 = k_begin + warp * KT; t0 < k_end; t0 += NW * KT) {
+    // One tile of codes is always in flight ahead of the one being consumed.
+    struct Tile { uint4 kqa, kqb, vqa, vqb; float kna, knb, vna, vnb; };
+    auto fetch = [&](uint32_t t0, Tile &tl) {
         const uint32_t ka = t0 + g, kb = t0 + g + 8;
-        const bool va = ka < k_end, vb = kb < k_end;
-        const uint32_t kca = va ? ka : t0, kcb = vb ? kb : t0;   // t0 is always a valid key
+        const uint32_t kca = ka < k_end ? ka : t0, kcb = kb < k_end ? kb : t0;   // t0 is always a valid key
         const size_t slot_a = (lane_base + (p.ring ? kca % p.ring : kca)) * p.n_kv + kv_head;
         const size_t slot_b = (lane_base + (p.ring ? kcb % p.ring : kcb)) * p.n_kv + kv_head;
-        const uint4 kqa = __ldg(reinterpret_cast<const uint4 *>(p.kc + slot_a * CB) + t);
-        const uint4 kqb = __ldg(reinterpret_cast<const uint4 *>(p.kc + slot_b * CB) + t);
-        const uint4 vqa = __ldg(reinterpret_cast<const uint4 *>(p.vc + slot_a * CB) + t);
-        const uint4 vqb = __ldg(reinterpret_cast<const uint4 *>(p.vc + slot_b * CB) + t);
-        const float kna = __half2float(p.kn[slot_a]) * gamma, knb = __half2float(p.kn[slot_b]) * gamma;
-        const float vna = __half2float(p.vn[slot_a]) * gamma, vnb = __half2float(p.vn[slot_b]) * gamma;
+        tl.kqa = __ldg(reinterpret_cast<const uint4 *>(p.kc + slot_a * CB) + t);
+        tl.kqb = __ldg(reinterpret_cast<const uint4 *>(p.kc + slot_b * CB) + t);
+        tl.vqa = __ldg(reinterpret_cast<const uint4 *>(p.vc + slot_a * CB) + t);
+        tl.vqb = __ldg(reinterpret_cast<const uint4 *>(p.vc + slot_b * CB) + t);
+        tl.kna = __half2float(p.kn[slot_a]);
+        tl.knb = __half2float(p.kn[slot_b]);
+        tl.vna = __half2float(p.vn[slot_a]);
+        tl.vnb = __half2float(p.vn[slot_b]);
+    };
+    Tile nxt;
+    const uint32_t t_first = k_begin + warp * KT;
+    if (t_first < k_end) fetch(t_first, nxt);
+    for (uint32_t t0 = t_first; t0 < k_end; t0 += NW * KT) {
+        const Tile cur = nxt;
+        if (t0 + NW * KT < k_end) fetch(t0 + NW * KT, nxt);
+        const bool va = t0 + g < k_end, vb = t0 + g + 8 < k_end;
+        const uint4 kqa = cur.kqa, kqb = cur.kqb, vqa = cur.vqa, vqb = cur.vqb;
+        const float kna = cur.kna * gamma, knb = cur.knb * gamma, vna = cur.vna * gamma, vnb = cur.vnb * gamma;
 
         // S^T[16 keys x 8 heads]
         float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -225,9 +243,11 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
             l_part[h] = l_part[h] * resc[h] + pa[h] + pb[h];
             m_run[h] = m_new;
         }
+        if (__any_sync(0xffffffffu, resc[0] != 1.0f || resc[1] != 1.0f)) {   // the running max moved for some head
 #pragma unroll
-        for (int s = 0; s < 16; s++) {
-            o[s][0] *= resc[0]; o[s][1] *= resc[1]; o[s][2] *= resc[0]; o[s][3] *= resc[1];
+            for (int s = 0; s < 16; s++) {
+                o[s][0] *= resc[0]; o[s][1] *= resc[1]; o[s][2] *= resc[0]; o[s][3] *= resc[1];
+            }
         }
         // P (times the value norms) into the B operand: (key g | g+8; heads 2t, 2t+1) -> transposed
         uint32_t bp[2];
