@@ -299,6 +299,175 @@ class DecodeStep:
         return dt, lanes / dt, f"1 step of {lanes} lanes at context {self.context} (f64-accumulating oracle, all host threads)"
 
 
+class RaggedDecode(DecodeStep):
+    """Config 5: 512 concurrent sequences of the config-4 model with lognormal context lengths (median 2048,
+    sigma 1.0, clipped to [16, 131072]; seed fixed), sharded by request across the ranks (balanced by context
+    sum), weights replicated, each lane's KV on its owner GPU.  Vocabulary projection:
+      replicated  every rank projects its own lanes against the whole table; no collective (default);
+      allgather   the table is row-split; hidden rows are all-gathered (1.5 MB), every rank projects its rows for
+                  all 512 lanes and the f32 logit slices are all-gathered over NCCL (537 MB per step), as the
+                  configuration states; greedy tokens are then taken on every rank.
+    One step = one token for every one of the 512 sequences; value = 512 / step time (strong scaling)."""
+
+    def __init__(self, la, ctx, kernels, rank: int, world: int, vocab_mode: str = "replicated", total: int = 512,
+                 n_layers: int = 35, vocab: int = 262144, max_ctx: int = 131072):
+        self.la, self.ctx, self.k = la, ctx, kernels
+        self.rank, self.world, self.vocab_mode, self.total = rank, world, vocab_mode, total
+        ctxs = la.synth.lognormal_contexts(total, seed=55, hi=max_ctx)
+        self.shards = la.sharding.shard_lanes(ctxs, world)
+        self.my = self.shards[rank]
+        self.lanes = len(self.my)
+        self.context = int(ctxs[self.my].max())
+        cfg = la.e2b_like_config(max_lanes=self.lanes, max_context=self.context + 260, n_layers=n_layers, vocab=vocab)
+        self.cfg = cfg
+        self.model = la.DecodeModel(ctx, kernels, cfg)
+        self.host_layers = []
+        for i in range(n_layers):
+            t = la.model.synth_layer(cfg, i, seed=4)
+            self.model.set_layer(i, t)
+        self.emb, self.fnorm = la.model.synth_embedding(cfg, seed=4)
+        self.emb_buf = la.CudaBuffer.from_slice(ctx, self.emb)
+        self.model.set_embedding(self.emb_buf, self.fnorm)
+        self.emb = None
+        cb = la.tq_code_bytes(cfg.head_dim, cfg.kv_bits)
+        self.kv_bytes = 0
+        my_ctx = ctxs[self.my].astype(np.int64)
+        for i in range(n_layers):
+            kv = self.model.kv_buffers(i)
+            for name in ("k_codes", "v_codes"):
+                kv[name].fill(0x9C)          # codes 0,3,1,2 repeating: every level occurs
+            for name in ("k_norms", "v_norms"):
+                kv[name].fill(0x4C)          # f16 0x4C4C = 17.2, about |N(0, I_256)|
+            eff = np.minimum(my_ctx + 1, kv["window"]) if kv["window"] else my_ctx + 1
+            self.kv_bytes += int(eff.sum()) * cfg.n_kv_heads * (2 * cb + 4)
+        tq = lambda r, c: r * (c // 256) * 66
+        qd, kd = cfg.n_q_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+        per_layer = (tq(qd, cfg.hidden) + 2 * tq(kd, cfg.hidden) + tq(cfg.hidden, qd) + 2 * tq(cfg.inter, cfg.hidden) +
+                     tq(cfg.hidden, cfg.inter))
+        vocab_rows = vocab if vocab_mode == "replicated" else (la.sharding.vocab_rows(vocab, world, rank)[1] -
+                                                                la.sharding.vocab_rows(vocab, world, rank)[0])
+        self.weight_bytes = n_layers * per_layer + vocab_rows * (cfg.hidden // 32) * 18
+        self.alg_bytes_per_step = self.weight_bytes + self.kv_bytes
+        self.tokens_host = (la.synth.splitmix64(7, total) % np.uint64(vocab)).astype(np.uint32)[self.my]
+        self.positions_host = ctxs[self.my].astype(np.uint32)
+        self.tokens = la.CudaBuffer.from_slice(ctx, self.tokens_host)
+        self.positions = la.CudaBuffer.from_slice(ctx, self.positions_host)
+        self.next_tokens = la.CudaBuffer.empty(ctx, max(self.lanes, total) * 4)
+        self.name = (f"ragged decode, {total} sequences (lognormal contexts, median 2048) of the E2B-like decoder sharded by "
+                     f"request over {world} GPU(s), vocabulary {vocab_mode}")
+        self.copies, self.wbytes, self.graph, self.launches_per_step = 1, self.weight_bytes, None, None
+        self.geo, self.n_layers_, self.vocab_ = [], n_layers, vocab
+
+    def prepare(self):
+        import torch
+        import torch.distributed as dist
+        la, ctx, cfg = self.la, self.ctx, self.cfg
+        local_vocab = self.vocab_mode == "replicated"
+        b = la.CommandBatch.new(ctx)
+        self.model.decode_batch_step_into(b, self.tokens, self.positions, self.lanes, False,
+                                          self.next_tokens if local_vocab else None)
+        self.launches_per_step = b.dispatch_count()
+        b.commit_and_wait()
+        b = la.CommandBatch.capture(ctx)
+        self.model.decode_batch_step_into(b, self.tokens, self.positions, self.lanes, False,
+                                          self.next_tokens if local_vocab else None)
+        self.graph = b.end_capture()
+        if not local_vocab:
+            assert self.total % self.world == 0, "the all-gather variant needs equal shards"
+            dev = torch.device("cuda", ctx.device)
+            self.t_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+            lo, hi = la.sharding.vocab_rows(self.vocab_, self.world, self.rank)
+            self.rows = hi - lo
+            rb = cfg.hidden // 32 * 18
+            self.table_slice = la.CudaBuffer.wrap(ctx, self.emb_buf.device_ptr + lo * rb, self.rows * rb)
+            self.t_hidden_all = torch.empty(self.total, cfg.hidden, dtype=torch.float16, device=dev)
+            self.t_logits_slice = torch.empty(self.total, self.rows, dtype=torch.float32, device=dev)
+            self.t_logits_all = torch.empty(self.world, self.total, self.rows, dtype=torch.float32, device=dev)
+            self.hidden_all = la.CudaBuffer.wrap(ctx, self.t_hidden_all.data_ptr(), self.t_hidden_all.numel() * 2)
+            self.logits_slice = la.CudaBuffer.wrap(ctx, self.t_logits_slice.data_ptr(), self.t_logits_slice.numel() * 4)
+            self.hidden_local = self.model.hidden_buffer()
+            self.dist = dist
+            self.launches_per_step += 1
+
+    def step(self):
+        self.graph.launch()
+        if self.vocab_mode == "replicated":
+            return
+        import torch
+        la, ctx, cfg = self.la, self.ctx, self.cfg
+        n = self.lanes
+        for p in getattr(self, "_pend", []):   # the previous step's batches (long finished): release their events
+            p.wait()
+        with torch.cuda.stream(self.t_stream):
+            b = la.CommandBatch.new(ctx)
+            b.blit_buffer_copy(self.hidden_local, 0, self.hidden_all, self.rank * n * cfg.hidden * 2, n * cfg.hidden * 2)
+            pend = [b.commit_async()]   # enqueued on the context's stream; the collective below orders itself after it
+            mine = self.t_hidden_all[self.rank * n:(self.rank + 1) * n]
+            if self.world > 1:
+                self.dist.all_gather_into_tensor(self.t_hidden_all, mine.clone())
+            b = la.CommandBatch.new(ctx)
+            self.k.matmul_nt_q4_0_f32out_into(b, self.hidden_all, self.table_slice, self.logits_slice, self.total,
+                                              cfg.hidden, self.rows)
+            pend.append(b.commit_async())
+            if self.world > 1:
+                self.dist.all_gather_into_tensor(self.t_logits_all, self.t_logits_slice)
+            else:
+                self.t_logits_all[0].copy_(self.t_logits_slice)
+            vals, idx = self.t_logits_all.max(dim=2)            # [world, total]
+            best = vals.max(dim=0).values
+            shard = (vals == best).to(torch.int32).argmax(dim=0)  # first shard holding the maximum = lowest rows
+            self.t_next = idx.gather(0, shard[None])[0] + shard * self.rows
+        self._pend = pend
+
+    def l2_note(self):
+        return (f"inputs larger than L2: {self.weight_bytes / 1e6:.0f} MB of weights + {self.kv_bytes / 1e6:.0f} MB of KV "
+                "read per step on this rank")
+
+    def check(self, orc):
+        if self.vocab_mode == "replicated":
+            nt = self.next_tokens.as_slice(np.uint32, self.lanes)
+            assert np.all(nt < self.cfg.vocab), "argmax out of range"
+        else:
+            assert int(self.t_next.max()) < self.cfg.vocab
+
+    def prepare_e2e(self):
+        self.h_in = self.la.PinnedHost(2 * self.lanes * 4, dtype=np.uint32)
+        self.h_out = self.la.PinnedHost(self.lanes * 4, dtype=np.uint32)
+        self.h_in.array[: self.lanes] = self.tokens_host
+        self.h_in.array[self.lanes:] = self.positions_host
+        self.e2e_pos0 = self.positions_host.copy()
+        self.e2e_steps = 0
+        self.h2d, self.d2h = 2 * self.lanes * 4, self.lanes * 4
+
+    def step_e2e(self):
+        b = self.la.CommandBatch.new(self.ctx)
+        b.upload(self.tokens, 0, self.h_in.ptr, self.lanes * 4)
+        b.upload(self.positions, 0, self.h_in.ptr + self.lanes * 4, self.lanes * 4)
+        b.commit_and_wait()
+        self.step()
+        if self.vocab_mode == "replicated":
+            b = self.la.CommandBatch.new(self.ctx)
+            b.download(self.next_tokens, 0, self.h_out.ptr, self.lanes * 4)
+            b.commit_and_wait()
+            self.h_in.array[: self.lanes] = self.h_out.array
+        else:
+            self.ctx.synchronize()
+            import torch
+            torch.cuda.synchronize()
+            self.h_in.array[: self.lanes] = self.t_next[self.rank * self.lanes:(self.rank + 1) * self.lanes].cpu().numpy().astype(np.uint32)
+        self.e2e_steps += 1
+        self.h_in.array[self.lanes:] = self.e2e_pos0 + (self.e2e_steps % 200)
+
+    def metric(self):
+        return f"decode_tok_s_ragged{self.total}", "tok/s"
+
+    def value(self, ms_per_step: float) -> float:
+        return self.total / self.world / (ms_per_step * 1e-3)   # main() multiplies by world
+
+    def cpu_sample(self, orc, threads: int):
+        return 0.0, 0.0, "not timed for the ragged workload (see the batch-64 workload)"
+
+
 WORKLOADS = {
     "matvec_tq2_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 1),
     "matvec_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 6144, 1536, 1),
@@ -308,6 +477,7 @@ WORKLOADS = {
     "decode_b64": lambda la, ctx, k: DecodeStep(la, ctx, k, 64, 8192),
     "decode_b1": lambda la, ctx, k: DecodeStep(la, ctx, k, 1, 8192),
     "decode_b64_small": lambda la, ctx, k: DecodeStep(la, ctx, k, 64, 2048, n_layers=5, vocab=32768),
+    "ragged512": None, "ragged512_allgather": None, "ragged64_small": None, "ragged64_small_allgather": None,
 }
 DEFAULT_WORKLOAD = "decode_b64"
 
@@ -421,7 +591,14 @@ def main() -> None:
     la = entry.load_package()
     ctx = la.CudaContext.new(local_rank)
     kernels = la.Kernels.new(ctx)
-    wl = WORKLOADS[args.workload](la, ctx, kernels)
+    if args.workload.startswith("ragged"):
+        mode = "allgather" if args.workload.endswith("allgather") else "replicated"
+        if "small" in args.workload:
+            wl = RaggedDecode(la, ctx, kernels, rank, world, mode, total=64, n_layers=5, vocab=32768, max_ctx=8192)
+        else:
+            wl = RaggedDecode(la, ctx, kernels, rank, world, mode)
+    else:
+        wl = WORKLOADS[args.workload](la, ctx, kernels)
     wl.prepare()
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
 
@@ -468,7 +645,8 @@ def main() -> None:
     value = wl.value(ms) * world
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if args.workload.startswith("ragged") else "weak",
+        "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": wl.name, "l2_policy": wl.l2_note(), "launch": "one CUDA graph per step",
                    "replicas": world},

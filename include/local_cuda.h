@@ -90,6 +90,8 @@ LC_API int lc_buf_upload(lc_buf *buf, size_t offset, const void *src, size_t byt
 LC_API int lc_buf_download(const lc_buf *buf, size_t offset, void *dst, size_t bytes);
 /* Zero a byte range (the containers' reset paths, kv_cache/quant_cache.rs:364-380). */
 LC_API int lc_buf_zero(lc_buf *buf, size_t offset, size_t bytes);
+/* Set every byte of a range to `value` (synthetic pool contents for benchmarks). */
+LC_API int lc_buf_fill(lc_buf *buf, size_t offset, size_t bytes, int value);
 
 /* --------------------------------------------------------------- batch -- */
 LC_API int lc_batch_begin(lc_ctx *ctx, lc_batch **out);           /* CommandBatch::new batch.rs:160-172 */

@@ -209,6 +209,14 @@ int lc_buf_zero(lc_buf *buf, size_t offset, size_t bytes) {
     return LC_OK;
 }
 
+int lc_buf_fill(lc_buf *buf, size_t offset, size_t bytes, int value) {
+    int st = range_ok(buf, offset, bytes, "lc_buf_fill");
+    if (st != LC_OK) return st;
+    if (!bytes) return LC_OK;
+    LC_CUDA_TRY(cudaMemsetAsync((char *)buf->dptr + offset, value & 0xFF, bytes, buf->ctx->stream));
+    return LC_OK;
+}
+
 // ------------------------------------------------------------------ batch --
 int lc_batch_begin(lc_ctx *ctx, lc_batch **out) {
     if (!ctx || !out) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_batch_begin: NULL argument");

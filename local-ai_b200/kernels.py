@@ -128,6 +128,9 @@ class CudaBuffer:
     def zero(self, offset: int = 0, nbytes: int | None = None) -> None:
         _check(self._lib.lc_buf_zero(self._h, offset, self.nbytes - offset if nbytes is None else nbytes))
 
+    def fill(self, value: int, offset: int = 0, nbytes: int | None = None) -> None:
+        _check(self._lib.lc_buf_fill(self._h, offset, self.nbytes - offset if nbytes is None else nbytes, value))
+
     def free(self) -> None:
         if self._h:
             self._lib.lc_buf_free(self._h)
