@@ -370,6 +370,20 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     uint32_t n_splits = want < by_len ? want : by_len;
     if (n_splits < 1) n_splits = 1;
     if (n_splits > 64) n_splits = 64;
+    if (use_mma) {
+        // One CTA per SM (registers), so the launch runs in whole waves; every CTA pays a fixed prologue worth
+        // about 320 keys.  Pick the split count that minimises waves x (prologue + keys per split).
+        const uint32_t sms = (uint32_t)k->ctx->sm_count;
+        uint32_t max_s = len_max / 256u;   // at least two 16-key tiles for each of the 8 warps
+        if (max_s < 1) max_s = 1;
+        if (max_s > 64) max_s = 64;
+        uint64_t best_cost = ~0ull;
+        for (uint32_t s = 1; s <= max_s; s++) {
+            const uint64_t waves = ((uint64_t)base * s + sms - 1) / sms;
+            const uint64_t cost = waves * (320u + (len_max + s - 1) / s);
+            if (cost < best_cost) { best_cost = cost; n_splits = s; }
+        }
+    }
     const bool direct = (n_splits == 1 && !fused);
 
     if (!direct) {

@@ -29,6 +29,7 @@ constexpr int NW = NT / 32;
 constexpr int G = 8;             // q-heads per CTA (MMA N)
 constexpr int KT = 16;           // keys per warp step (MMA M for QK, MMA K for PV)
 constexpr int LUT_BYTES = 256 * 32 * 8;
+static_assert(NW == G && NT == 256, "the prologue maps warps to heads and threads to code bytes");
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile(
@@ -50,20 +51,10 @@ __device__ __forceinline__ uint32_t byte_of(const uint4 &q, int s) {
     return (w >> (8 * (s & 3))) & 0xFFu;
 }
 
-template <int HDIM>
-__device__ __forceinline__ void fwht_rows_cta(float *sh, int rows) {
-    const int pairs = rows * (HDIM / 2);
-    for (int len = 1; len < HDIM; len <<= 1) {
-        __syncthreads();
-        for (int p = threadIdx.x; p < pairs; p += NT) {
-            const int i = p & (len - 1);
-            const int idx = ((p - i) << 1) + i;
-            const float a = sh[idx], b = sh[idx + len];
-            sh[idx] = a + b;
-            sh[idx + len] = a - b;
-        }
-    }
-    __syncthreads();
+// rq_s index of (head h, dim d): the order in which thread (g, t) = lane 4g + t reads its B fragments,
+// so that fragment loads are one conflict-free float4 per (s, lane).  d = 64t + 4s + e.
+__device__ __forceinline__ int rq_index(int h, int d) {
+    return (((d & 63) >> 2) * 32 + h * 4 + (d >> 6)) * 4 + (d & 3);
 }
 
 __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) {
@@ -71,7 +62,8 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     lc_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem[];
     uint2 *lut = reinterpret_cast<uint2 *>(smem);                       // [256 bytes][32 lanes] x 4 f16
-    float *rq_s = reinterpret_cast<float *>(smem + LUT_BYTES);          // [G][HD] rotated, scaled query
+    float *rq_s = reinterpret_cast<float *>(smem + LUT_BYTES);          // [16 s][32 lanes][4] rotated, scaled query
+    uint2 *ent_s = reinterpret_cast<uint2 *>(smem + LUT_BYTES + G * HD * sizeof(float));   // [256] one table copy
     __shared__ float gamma_s;
     __shared__ float cand_err[NW];
     __shared__ int cand_idx[NW];
@@ -101,97 +93,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     const uint32_t k_end = min(seq_len, k_begin + per);
     const size_t lane_base = (size_t)lane_idx * p.lane_capacity;
 
-    // ---- prologue 1: gamma such that every level / gamma is (almost) exactly an f16 ----
-    const float lv0 = p.levels[0], lv1 = p.levels[1], lv2 = p.levels[2], lv3 = p.levels[3];
-    {
-        const float ref = fmaxf(fmaxf(fabsf(lv0), fabsf(lv1)), fmaxf(fabsf(lv2), fabsf(lv3)));
-        float best = INFINITY;
-        int besti = 0;
-        for (int j = threadIdx.x; j < 1024; j += NT) {
-            const float gm = ref > 0.f ? ref / (1.0f + (float)j * (1.0f / 1024.0f)) : 1.0f;  // largest level -> [1, 2)
-            float e = 0.f;
-            const float ls[4] = {lv0, lv1, lv2, lv3};
-#pragma unroll
-            for (int l = 0; l < 4; l++) {
-                const float back = __half2float(__float2half_rn(ls[l] / gm)) * gm;
-                e = fmaxf(e, ls[l] != 0.f ? fabsf(back - ls[l]) / fabsf(ls[l]) : 0.f);
-            }
-            if (e < best) { best = e; besti = j; }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {   // arg-min inside the warp, lowest index on ties
-            const float oe = __shfl_xor_sync(0xffffffffu, best, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, besti, off);
-            if (oe < best || (oe == best && oi < besti)) { best = oe; besti = oi; }
-        }
-        if (lane == 0) { cand_err[warp] = best; cand_idx[warp] = besti; }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float b = cand_err[0];
-            int bi = cand_idx[0];
-            for (int i = 1; i < NW; i++)
-                if (cand_err[i] < b || (cand_err[i] == b && cand_idx[i] < bi)) { b = cand_err[i]; bi = cand_idx[i]; }
-            gamma_s = ref > 0.f ? ref / (1.0f + (float)bi * (1.0f / 1024.0f)) : 1.0f;
-        }
-        __syncthreads();
-    }
-    const float gamma = gamma_s;
-    // ---- prologue 2: byte -> four f16 levels table, one copy per lane ----
-    {
-        const float ls[4] = {lv0 / gamma, lv1 / gamma, lv2 / gamma, lv3 / gamma};
-        for (int e = threadIdx.x; e < 256 * 32; e += NT) {
-            const int byte = e >> 5;
-            uint2 v;
-            v.x = pack_h2(ls[byte & 3], ls[(byte >> 2) & 3]);
-            v.y = pack_h2(ls[(byte >> 4) & 3], ls[(byte >> 6) & 3]);
-            lut[e] = v;
-        }
-    }
-    // ---- prologue 3: rotated, scaled query rq_s[g][d] ----
-    if (p.fused_q) {
-        for (int i = threadIdx.x; i < G * HD; i += NT) {
-            const int h = i / HD, d = i - h * HD;
-            float v = 0.f;
-            if (h < gvalid) v = __half2float(p.q[((size_t)lane_idx * p.n_q + qh0 + h) * HD + d]) * p.signs[d];
-            rq_s[i] = v;
-        }
-        fwht_rows_cta<HD>(rq_s, G);
-        const float f = p.scale / sqrtf((float)HD);
-        for (int i = threadIdx.x; i < G * HD; i += NT) rq_s[i] *= f;
-    } else {
-        for (int i = threadIdx.x; i < G * HD; i += NT) {
-            const int h = i / HD, d = i - h * HD;
-            rq_s[i] = h < gvalid ? p.rq[((size_t)lane_idx * p.n_q + qh0 + h) * HD + d] * p.scale : 0.f;
-        }
-    }
-    __syncthreads();
-    // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15
-    // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
-    // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
-    uint32_t bq[16][2], bql[16][2];
-#pragma unroll
-    for (int s = 0; s < 16; s++) {
-        const float *r = rq_s + g * HD + 64 * t + 4 * s;
-        float hi[4], lo[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            hi[e] = __half2float(__float2half_rn(r[e]));
-            lo[e] = r[e] - hi[e];
-        }
-        bq[s][0] = pack_h2(hi[0], hi[1]);
-        bq[s][1] = pack_h2(hi[2], hi[3]);
-        bql[s][0] = pack_h2(lo[0], lo[1]);
-        bql[s][1] = pack_h2(lo[2], lo[3]);
-    }
-    const uint2 *lut_lane = lut + lane;
-
-    // ---- main loop: each warp takes every 8th 16-key tile of this split ----
-    float o[16][4];
-#pragma unroll
-    for (int s = 0; s < 16; s++) o[s][0] = o[s][1] = o[s][2] = o[s][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // heads 2t, 2t+1 (l: this thread's keys only)
-
-    // One tile of codes is always in flight ahead of the one being consumed.
+    // One tile of codes is always in flight ahead of the one being consumed; the first leaves before the prologue.
     struct Tile { uint4 kqa, kqb, vqa, vqb; float kna, knb, vna, vnb; };
     auto fetch = [&](uint32_t t0, Tile &tl) {
         const uint32_t ka = t0 + g, kb = t0 + g + 8;
@@ -210,6 +112,145 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     Tile nxt;
     const uint32_t t_first = k_begin + warp * KT;
     if (t_first < k_end) fetch(t_first, nxt);
+
+    // ---- prologue 1: gamma such that every level / gamma is (almost) exactly an f16 ----
+    const float lv0 = p.levels[0], lv1 = p.levels[1], lv2 = p.levels[2], lv3 = p.levels[3];
+    const float ref = fmaxf(fmaxf(fabsf(lv0), fabsf(lv1)), fmaxf(fabsf(lv2), fabsf(lv3)));
+    {
+        const float ia0 = lv0 != 0.f ? 1.0f / fabsf(lv0) : 0.f, ia1 = lv1 != 0.f ? 1.0f / fabsf(lv1) : 0.f;
+        const float ia2 = lv2 != 0.f ? 1.0f / fabsf(lv2) : 0.f, ia3 = lv3 != 0.f ? 1.0f / fabsf(lv3) : 0.f;
+        float best = INFINITY;
+        int besti = 0;
+#pragma unroll
+        for (int it = 0; it < 1024 / NT; it++) {
+            const int j = threadIdx.x + it * NT;
+            const float gm = ref > 0.f ? ref / (1.0f + (float)j * (1.0f / 1024.0f)) : 1.0f;  // largest level -> [1, 2)
+            const float inv = __frcp_rn(gm);
+            float e = fabsf(__half2float(__float2half_rn(lv0 * inv)) * gm - lv0) * ia0;
+            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv1 * inv)) * gm - lv1) * ia1);
+            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv2 * inv)) * gm - lv2) * ia2);
+            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv3 * inv)) * gm - lv3) * ia3);
+            if (e < best) { best = e; besti = j; }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {   // arg-min inside the warp, lowest index on ties
+            const float oe = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, off);
+            if (oe < best || (oe == best && oi < besti)) { best = oe; besti = oi; }
+        }
+        if (lane == 0) { cand_err[warp] = best; cand_idx[warp] = besti; }
+    }
+    // ---- prologue 2 (independent of gamma): rotated, scaled query; warp w owns head w ----
+    {
+        const int h = warp;   // NW == G
+        float x[8];
+        if (h < gvalid) {
+            const size_t row = ((size_t)lane_idx * p.n_q + qh0 + h) * HD + 8 * lane;
+            if (p.fused_q) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(p.q + row);
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
+                const float4 s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
+                const float4 s1 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane + 4);
+                const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(hp[e]);
+                    x[2 * e] = f.x * sg[2 * e];
+                    x[2 * e + 1] = f.y * sg[2 * e + 1];
+                }
+                // 256-point Walsh-Hadamard butterflies: strides 1, 2, 4 inside the thread, 8..128 across lanes
+#pragma unroll
+                for (int len = 1; len < 8; len <<= 1) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        if (!(i & len)) {
+                            const float a = x[i], b2 = x[i + len];
+                            x[i] = a + b2;
+                            x[i + len] = a - b2;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int m = 1; m < 32; m <<= 1) {
+                    const bool upper = lane & m;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float o2 = __shfl_xor_sync(0xffffffffu, x[i], m);
+                        x[i] = upper ? o2 - x[i] : x[i] + o2;
+                    }
+                }
+                const float f = p.scale / sqrtf((float)HD);
+#pragma unroll
+                for (int i = 0; i < 8; i++) x[i] *= f;
+            } else {
+                const float4 r0 = *reinterpret_cast<const float4 *>(p.rq + row);
+                const float4 r1 = *reinterpret_cast<const float4 *>(p.rq + row + 4);
+                x[0] = r0.x * p.scale; x[1] = r0.y * p.scale; x[2] = r0.z * p.scale; x[3] = r0.w * p.scale;
+                x[4] = r1.x * p.scale; x[5] = r1.y * p.scale; x[6] = r1.z * p.scale; x[7] = r1.w * p.scale;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) x[i] = 0.f;
+        }
+        *reinterpret_cast<float4 *>(rq_s + rq_index(h, 8 * lane)) = make_float4(x[0], x[1], x[2], x[3]);
+        *reinterpret_cast<float4 *>(rq_s + rq_index(h, 8 * lane + 4)) = make_float4(x[4], x[5], x[6], x[7]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b2 = cand_err[0];
+        int bi = cand_idx[0];
+        for (int i = 1; i < NW; i++)
+            if (cand_err[i] < b2 || (cand_err[i] == b2 && cand_idx[i] < bi)) { b2 = cand_err[i]; bi = cand_idx[i]; }
+        gamma_s = ref > 0.f ? ref / (1.0f + (float)bi * (1.0f / 1024.0f)) : 1.0f;
+    }
+    // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15
+    // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
+    // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
+    uint32_t bq[16][2], bql[16][2];
+#pragma unroll
+    for (int s = 0; s < 16; s++) {
+        const float4 r4 = *reinterpret_cast<const float4 *>(rq_s + (s * 32 + lane) * 4);
+        const float r[4] = {r4.x, r4.y, r4.z, r4.w};
+        float hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            hi[e] = __half2float(__float2half_rn(r[e]));
+            lo[e] = r[e] - hi[e];
+        }
+        bq[s][0] = pack_h2(hi[0], hi[1]);
+        bq[s][1] = pack_h2(hi[2], hi[3]);
+        bql[s][0] = pack_h2(lo[0], lo[1]);
+        bql[s][1] = pack_h2(lo[2], lo[3]);
+    }
+    __syncthreads();
+    const float gamma = gamma_s;
+    // ---- prologue 3: byte -> four f16 levels table; one copy first, then one copy per lane ----
+    {
+        const int byte = threadIdx.x;   // NT == 256
+        const float inv_levels[4] = {lv0 / gamma, lv1 / gamma, lv2 / gamma, lv3 / gamma};
+        float e4[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int c = (byte >> (2 * q)) & 3;
+            e4[q] = c == 0 ? inv_levels[0] : (c == 1 ? inv_levels[1] : (c == 2 ? inv_levels[2] : inv_levels[3]));
+        }
+        uint2 v;
+        v.x = pack_h2(e4[0], e4[1]);
+        v.y = pack_h2(e4[2], e4[3]);
+        ent_s[byte] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int e = threadIdx.x; e < 256 * 32; e += NT) lut[e] = ent_s[e >> 5];
+    __syncthreads();
+    const uint2 *lut_lane = lut + lane;
+
+    // ---- main loop: each warp takes every 8th 16-key tile of this split ----
+    float o[16][4];
+#pragma unroll
+    for (int s = 0; s < 16; s++) o[s][0] = o[s][1] = o[s][2] = o[s][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // heads 2t, 2t+1 (l: this thread's keys only)
+
     for (uint32_t t0 = t_first; t0 < k_end; t0 += NW * KT) {
         const Tile cur = nxt;
         if (t0 + NW * KT < k_end) fetch(t0 + NW * KT, nxt);
@@ -218,14 +259,22 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         const float kna = cur.kna * gamma, knb = cur.knb * gamma, vna = cur.vna * gamma, vnb = cur.vnb * gamma;
 
         // S^T[16 keys x 8 heads]
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        // four independent accumulation chains (even / odd k-steps, high / low query parts)
+        float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f},
+              c3[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int s = 0; s < 16; s++) {
+        for (int s = 0; s < 16; s += 2) {
             const uint2 la = lut_lane[byte_of(kqa, s) * 32], lb = lut_lane[byte_of(kqb, s) * 32];
+            const uint2 ma = lut_lane[byte_of(kqa, s + 1) * 32], mb = lut_lane[byte_of(kqb, s + 1) * 32];
             const uint32_t a[4] = {la.x, lb.x, la.y, lb.y};
+            const uint32_t a2[4] = {ma.x, mb.x, ma.y, mb.y};
             mma16816(c, a, bq[s]);
-            mma16816(c, a, bql[s]);
+            mma16816(c1, a, bql[s]);
+            mma16816(c2, a2, bq[s + 1]);
+            mma16816(c3, a2, bql[s + 1]);
         }
+#pragma unroll
+        for (int e = 0; e < 4; e++) c[e] = (c[e] + c2[e]) + (c1[e] + c3[e]);
         // logits of keys g (c0, c1) and g+8 (c2, c3) for heads 2t, 2t+1
         float sA[2] = {va ? c[0] * kna : -INFINITY, va ? c[1] * kna : -INFINITY};
         float sB[2] = {vb ? c[2] * knb : -INFINITY, vb ? c[3] * knb : -INFINITY};
@@ -283,48 +332,67 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         l_s[warp * G + 2 * t] = l_part[0];
         l_s[warp * G + 2 * t + 1] = l_part[1];
     }
-    // row g of tile s is dim 64*(g>>1) + 4s + (g&1); row g+8 is two dims further
-    const int d_lo = 64 * (g >> 1) + (g & 1);
+    // Accumulators go to shared memory in fragment order [warp][s][j][lane] (conflict-free both ways).
 #pragma unroll
     for (int s = 0; s < 16; s++) {
-        float *base = acc_s + (size_t)(warp * G) * HD + d_lo + 4 * s;
-        base[(2 * t) * HD] = o[s][0];
-        base[(2 * t + 1) * HD] = o[s][1];
-        base[(2 * t) * HD + 2] = o[s][2];
-        base[(2 * t + 1) * HD + 2] = o[s][3];
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc_s[((warp * 16 + s) * 4 + j) * 32 + lane] = o[s][j];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < gvalid * HD; i += NT) {
-        const int h = i / HD, d = i - h * HD;
+    // Per (warp, head) weights exp(m_w - max) and the merged (max, sum); thread h < G does head h.
+    float *f_s = l_s + NW * G;       // [NW][G]
+    float *ml_s = f_s + NW * G;      // [G][2]
+    if (threadIdx.x < G) {
+        const int h = threadIdx.x;
         float gmax = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NW; w++) gmax = fmaxf(gmax, m_s[w * G + h]);
-        float gsum = 0.f, acc = 0.f;
+        float gsum = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; w++) {
             const float mw = m_s[w * G + h];
             const float f = (mw == -INFINITY) ? 0.f : __expf(mw - gmax);
+            f_s[w * G + h] = f;
             gsum += f * l_s[w * G + h];
-            acc += f * acc_s[(size_t)(w * G + h) * HD + d];
         }
-        const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
-        if (p.direct_out) {
-            p.out[qh * HD + d] = gsum > 0.f ? acc / gsum : 0.f;
-        } else {
-            float *pp = p.partial + (qh * p.n_splits + split) * (size_t)(HD + 2);
-            if (d == 0) {
-                pp[0] = gmax;
-                pp[1] = gsum;
+        ml_s[2 * h] = gmax;
+        ml_s[2 * h + 1] = gsum;
+    }
+    __syncthreads();
+    // Thread (warp, lane) merges fragment position `lane` of tiles s = 2 warp, 2 warp + 1: element j of tile s is
+    // head 2t + (j & 1), dim 64 (g >> 1) + 4 s + (g & 1) + 2 (j >> 1).
+#pragma unroll
+    for (int ss = 0; ss < 2; ss++) {
+        const int s = 2 * warp + ss;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int h = 2 * t + (j & 1);
+            const int d = 64 * (g >> 1) + 4 * s + (g & 1) + 2 * (j >> 1);
+            float acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; w++) acc += f_s[w * G + h] * acc_s[((w * 16 + s) * 4 + j) * 32 + lane];
+            if (h < gvalid) {
+                const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
+                if (p.direct_out) {
+                    const float gsum = ml_s[2 * h + 1];
+                    p.out[qh * HD + d] = gsum > 0.f ? acc / gsum : 0.f;
+                } else {
+                    p.partial[(qh * p.n_splits + split) * (size_t)(HD + 2) + 2 + d] = acc;
+                }
             }
-            pp[2 + d] = acc;
         }
+    }
+    if (!p.direct_out && threadIdx.x < 2 * gvalid) {
+        const int h = threadIdx.x >> 1;
+        const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
+        p.partial[(qh * p.n_splits + split) * (size_t)(HD + 2) + (threadIdx.x & 1)] = ml_s[threadIdx.x];
     }
 }
 
 }  // namespace
 
 int lc_tq2_attn_mma_launch(lc_batch *b, const TqAttnParams &p, dim3 grid) {
-    const size_t smem = (size_t)LUT_BYTES + (size_t)G * HD * sizeof(float);
+    const size_t smem = (size_t)LUT_BYTES + (size_t)G * HD * sizeof(float) + 256 * sizeof(uint2);
     static bool configured = false;
     if (!configured) {
         LC_CUDA_TRY(cudaFuncSetAttribute(tq2_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
