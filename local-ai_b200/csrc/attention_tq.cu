@@ -360,7 +360,10 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     // tq2 at head_dim 256 runs on the tensor-core kernel (8 heads per CTA); LOCAL_CUDA_ATTN_MMA=0 keeps the
     // CUDA-core kernel, which also serves every other head size and bit width.
     static const bool mma_allowed = []() { const char *e = getenv("LOCAL_CUDA_ATTN_MMA"); return !(e && e[0] == '0'); }();
-    const bool use_mma = mma_allowed && hd == 256 && bits == 2;
+    // (the tensor-core kernel copies norms as aligned 4-byte words)
+    const size_t norm_words = ((rows * n_kv + 1) & ~(size_t)1) * 2;
+    const bool use_mma = mma_allowed && hd == 256 && bits == 2 && lc_aligned(kn->dptr, 4) && lc_aligned(vn->dptr, 4) &&
+                         kn->bytes >= norm_words && vn->bytes >= norm_words && (ring == 0 || ring >= 16);
     if (use_mma) g = 8;
     const uint32_t gchunks = (group + g - 1) / g;
     const uint32_t base = n_lanes * n_kv * gchunks;

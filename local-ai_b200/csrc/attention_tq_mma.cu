@@ -7,12 +7,14 @@
 // 132 bytes of KV, which binds long before HBM does.  Here both contractions run on tensor cores, with
 // operands built directly in registers:
 //   * a shared-memory table maps one code byte (four 2-bit codes) to four f16 levels with a single
-//     8-byte load; the table is replicated per lane so lookups never collide on a bank;
+//     8-byte load; the table is replicated 16 times so the lookups of a half-warp never collide on a bank;
 //   * S^T[16 keys x 8 heads] = K[16 x 256] . RQ^T: the contraction index (dims) is free to permute, so
 //     thread (g, t) of a warp feeds the MMA with the 64 dims held in its own 16 code bytes of keys g, g+8;
-//   * O^T[256 dims x 8 heads] += V^T[256 x 16 keys] . P: the V bytes decode to (key, dim-pair) tiles,
-//     which movmatrix transposes into the (dim, key-pair) layout the A operand wants; P reaches the B
-//     operand the same way.
+//   * O^T[256 dims x 8 heads] += V^T[256 x 16 keys] . P: the A operand wants (dim; two adjacent keys) per
+//     register, so thread (g, t) decodes bytes 8g..8g+7 of keys 2t, 2t+1, 2t+8, 2t+9 itself and pairs the
+//     table entries of adjacent keys with byte permutes (no cross-lane traffic); P reaches the B operand
+//     through one movmatrix transpose per 8 keys;
+//   * codes and norms stream through a per-warp cp.async ring in shared memory (five tiles in flight).
 // f16 levels: the table stores levels / gamma, with gamma searched (1024 mantissas) so that all levels
 // are f16-representable to ~1e-6 relative; gamma is folded into the row norms in f32.  Logits, softmax
 // and accumulation stay f32.
@@ -28,7 +30,13 @@ constexpr int NT = 256;
 constexpr int NW = NT / 32;
 constexpr int G = 8;             // q-heads per CTA (MMA N)
 constexpr int KT = 16;           // keys per warp step (MMA M for QK, MMA K for PV)
-constexpr int LUT_BYTES = 256 * 32 * 8;
+constexpr int LUT_COPIES = 16;   // an 8-byte shared load is served per half-warp, so 16 copies are conflict-free
+constexpr int LUT_BYTES = 256 * LUT_COPIES * 8;
+constexpr int ACC_BYTES = NW * 16 * 4 * 32 * 4;   // merge staging, reuses the front of shared memory
+constexpr int DEPTH = 6;         // ring slots per warp (DEPTH - 1 tiles in flight)
+constexpr int RING_OFF = LUT_BYTES + G * HD * 4 + 256 * 8;
+constexpr int SMEM_BYTES = RING_OFF + NW * DEPTH * (4 * 32 * 16 + 32 * 4);
+static_assert(SMEM_BYTES >= ACC_BYTES + 4 * NW * G * 4, "merge staging must fit");
 static_assert(NW == G && NT == 256, "the prologue maps warps to heads and threads to code bytes");
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -37,6 +45,18 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
@@ -61,7 +81,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     lc_pdl_trigger();
     lc_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem[];
-    uint2 *lut = reinterpret_cast<uint2 *>(smem);                       // [256 bytes][32 lanes] x 4 f16
+    uint2 *lut = reinterpret_cast<uint2 *>(smem);                       // [256 bytes][16 copies] x 4 f16
     float *rq_s = reinterpret_cast<float *>(smem + LUT_BYTES);          // [16 s][32 lanes][4] rotated, scaled query
     uint2 *ent_s = reinterpret_cast<uint2 *>(smem + LUT_BYTES + G * HD * sizeof(float));   // [256] one table copy
     __shared__ float gamma_s;
@@ -77,6 +97,21 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     const int gvalid = min((int)G, (int)(p.group - gchunk * G));
     const uint32_t qh0 = kv_head * p.group + gchunk * G;
 
+    // Every global load of the prologue leaves first, so their latencies overlap.
+    const float lv0 = p.levels[0], lv1 = p.levels[1], lv2 = p.levels[2], lv3 = p.levels[3];
+    const size_t q_row = ((size_t)lane_idx * p.n_q + qh0 + warp) * HD + 8 * lane;   // warp w owns head w
+    uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
+    float4 q_s0 = make_float4(0.f, 0.f, 0.f, 0.f), q_s1 = q_s0;
+    if (warp < gvalid) {
+        if (p.fused_q) {
+            q_raw = *reinterpret_cast<const uint4 *>(p.q + q_row);
+            q_s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
+            q_s1 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane + 4);
+        } else {
+            q_s0 = *reinterpret_cast<const float4 *>(p.rq + q_row);
+            q_s1 = *reinterpret_cast<const float4 *>(p.rq + q_row + 4);
+        }
+    }
     uint32_t pos, seq_len;
     if (p.positions) {
         pos = p.positions[lane_idx];
@@ -93,28 +128,45 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     const uint32_t k_end = min(seq_len, k_begin + per);
     const size_t lane_base = (size_t)lane_idx * p.lane_capacity;
 
-    // One tile of codes is always in flight ahead of the one being consumed; the first leaves before the prologue.
-    struct Tile { uint4 kqa, kqb, vqa, vqb; float kna, knb, vna, vnb; };
-    auto fetch = [&](uint32_t t0, Tile &tl) {
-        const uint32_t ka = t0 + g, kb = t0 + g + 8;
-        const uint32_t kca = ka < k_end ? ka : t0, kcb = kb < k_end ? kb : t0;   // t0 is always a valid key
-        const size_t slot_a = (lane_base + (p.ring ? kca % p.ring : kca)) * p.n_kv + kv_head;
-        const size_t slot_b = (lane_base + (p.ring ? kcb % p.ring : kcb)) * p.n_kv + kv_head;
-        tl.kqa = __ldg(reinterpret_cast<const uint4 *>(p.kc + slot_a * CB) + t);
-        tl.kqb = __ldg(reinterpret_cast<const uint4 *>(p.kc + slot_b * CB) + t);
-        tl.vqa = __ldg(reinterpret_cast<const uint4 *>(p.vc + slot_a * CB) + t);
-        tl.vqb = __ldg(reinterpret_cast<const uint4 *>(p.vc + slot_b * CB) + t);
-        tl.kna = __half2float(p.kn[slot_a]);
-        tl.knb = __half2float(p.kn[slot_b]);
-        tl.vna = __half2float(p.vn[slot_a]);
-        tl.vnb = __half2float(p.vn[slot_b]);
+    // Each warp keeps DEPTH - 1 tiles of codes and norms in flight.  Every thread copies, with cp.async, exactly the
+    // bytes it will consume into its own slots of a shared-memory ring, so no cross-thread synchronisation is needed:
+    //   K codes: keys g and g + 8, bytes 16 t .. 16 t + 15 (the thread's 64 dims of the QK contraction);
+    //   V codes: keys 2t, 2t + 1, 2t + 8, 2t + 9, bytes 8 g .. 8 g + 7 (the thread's 32 output dims of PV);
+    //   one 4-byte word holding one norm (lanes 0-15: key norm of key `lane`; 16-31: value norm of key `lane - 16`).
+    uint4 *ring_c = reinterpret_cast<uint4 *>(smem + RING_OFF) + warp * (DEPTH * 4 * 32);
+    uint32_t *ring_n = reinterpret_cast<uint32_t *>(smem + RING_OFF + NW * DEPTH * 4 * 32 * 16) + warp * (DEPTH * 32);
+    uint32_t parity = 0;   // bit `stage`: which half of the copied word is this lane's norm
+    auto issue = [&](uint32_t t0, int stage) {
+        const uint32_t r0 = p.ring ? t0 % p.ring : t0;   // ring slot of the tile's first key (ring >= 16)
+        auto slot_of = [&](uint32_t off) -> size_t {
+            uint32_t r = t0 + off < k_end ? r0 + off : r0;   // t0 is always a valid key
+            if (p.ring && r >= p.ring) r -= p.ring;
+            return (lane_base + r) * p.n_kv + kv_head;
+        };
+        const size_t slot_n = slot_of(lane & 15);
+        uint4 *dst = ring_c + stage * 4 * 32 + lane;
+        cp_async16(dst, p.kc + slot_of(g) * CB + 16 * t);
+        cp_async16(dst + 32, p.kc + slot_of(g + 8) * CB + 16 * t);
+        uint2 *dv = reinterpret_cast<uint2 *>(dst + 64);
+        cp_async8(dv, p.vc + slot_of(2 * t) * CB + 8 * g);
+        cp_async8(dv + 1, p.vc + slot_of(2 * t + 1) * CB + 8 * g);
+        dv = reinterpret_cast<uint2 *>(dst + 96);
+        cp_async8(dv, p.vc + slot_of(2 * t + 8) * CB + 8 * g);
+        cp_async8(dv + 1, p.vc + slot_of(2 * t + 9) * CB + 8 * g);
+        const __half *nsrc = (lane < 16 ? p.kn : p.vn) + (slot_n & ~(size_t)1);
+        cp_async4(ring_n + stage * 32 + lane, nsrc);
+        parity = (parity & ~(1u << stage)) | ((uint32_t)(slot_n & 1) << stage);
     };
-    Tile nxt;
     const uint32_t t_first = k_begin + warp * KT;
-    if (t_first < k_end) fetch(t_first, nxt);
+    uint32_t t_issue = t_first;
+#pragma unroll
+    for (int i = 0; i < DEPTH - 1; i++) {
+        if (t_issue < k_end) issue(t_issue, i);
+        cp_async_commit();
+        t_issue += NW * KT;
+    }
 
     // ---- prologue 1: gamma such that every level / gamma is (almost) exactly an f16 ----
-    const float lv0 = p.levels[0], lv1 = p.levels[1], lv2 = p.levels[2], lv3 = p.levels[3];
     const float ref = fmaxf(fmaxf(fabsf(lv0), fabsf(lv1)), fmaxf(fabsf(lv2), fabsf(lv3)));
     {
         const float ia0 = lv0 != 0.f ? 1.0f / fabsf(lv0) : 0.f, ia1 = lv1 != 0.f ? 1.0f / fabsf(lv1) : 0.f;
@@ -145,13 +197,9 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         const int h = warp;   // NW == G
         float x[8];
         if (h < gvalid) {
-            const size_t row = ((size_t)lane_idx * p.n_q + qh0 + h) * HD + 8 * lane;
             if (p.fused_q) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(p.q + row);
-                const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
-                const float4 s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
-                const float4 s1 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane + 4);
-                const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&q_raw);
+                const float sg[8] = {q_s0.x, q_s0.y, q_s0.z, q_s0.w, q_s1.x, q_s1.y, q_s1.z, q_s1.w};
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const float2 f = __half22float2(hp[e]);
@@ -183,8 +231,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
 #pragma unroll
                 for (int i = 0; i < 8; i++) x[i] *= f;
             } else {
-                const float4 r0 = *reinterpret_cast<const float4 *>(p.rq + row);
-                const float4 r1 = *reinterpret_cast<const float4 *>(p.rq + row + 4);
+                const float4 r0 = q_s0, r1 = q_s1;
                 x[0] = r0.x * p.scale; x[1] = r0.y * p.scale; x[2] = r0.z * p.scale; x[3] = r0.w * p.scale;
                 x[4] = r1.x * p.scale; x[5] = r1.y * p.scale; x[6] = r1.z * p.scale; x[7] = r1.w * p.scale;
             }
@@ -241,9 +288,9 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     }
     __syncthreads();
 #pragma unroll 8
-    for (int e = threadIdx.x; e < 256 * 32; e += NT) lut[e] = ent_s[e >> 5];
+    for (int e = threadIdx.x; e < 256 * LUT_COPIES; e += NT) lut[e] = ent_s[e / LUT_COPIES];
     __syncthreads();
-    const uint2 *lut_lane = lut + lane;
+    const uint2 *lut_lane = lut + (lane & (LUT_COPIES - 1));
 
     // ---- main loop: each warp takes every 8th 16-key tile of this split ----
     float o[16][4];
@@ -251,30 +298,42 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     for (int s = 0; s < 16; s++) o[s][0] = o[s][1] = o[s][2] = o[s][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // heads 2t, 2t+1 (l: this thread's keys only)
 
+    int stage = 0;
     for (uint32_t t0 = t_first; t0 < k_end; t0 += NW * KT) {
-        const Tile cur = nxt;
-        if (t0 + NW * KT < k_end) fetch(t0 + NW * KT, nxt);
+        // tile t0 is the oldest group in flight; DEPTH - 2 newer ones may still be pending
+        cp_async_wait<DEPTH - 2>();
+        const uint4 *src = ring_c + stage * 4 * 32 + lane;
+        const uint4 kqa = src[0], kqb = src[32], vqa = src[64], vqb = src[96];
+        const uint32_t nw = ring_n[stage * 32 + lane];
+        const float n_own = __half2float(__ushort_as_half((unsigned short)((parity >> stage) & 1u ? nw >> 16 : nw & 0xFFFFu))) * gamma;
+        const float kna = __shfl_sync(0xffffffffu, n_own, g), knb = __shfl_sync(0xffffffffu, n_own, g + 8);
+        const float vna = __shfl_sync(0xffffffffu, n_own, 16 + g), vnb = __shfl_sync(0xffffffffu, n_own, 24 + g);
+        // refill: the slot of the tile consumed in the previous iteration is free (its values were used by then)
+        {
+            const int st_fill = stage == 0 ? DEPTH - 1 : stage - 1;
+            if (t_issue < k_end) issue(t_issue, st_fill);
+            cp_async_commit();
+            t_issue += NW * KT;
+        }
+        stage = stage + 1 == DEPTH ? 0 : stage + 1;
         const bool va = t0 + g < k_end, vb = t0 + g + 8 < k_end;
-        const uint4 kqa = cur.kqa, kqb = cur.kqb, vqa = cur.vqa, vqb = cur.vqb;
-        const float kna = cur.kna * gamma, knb = cur.knb * gamma, vna = cur.vna * gamma, vnb = cur.vnb * gamma;
 
         // S^T[16 keys x 8 heads]
-        // four independent accumulation chains (even / odd k-steps, high / low query parts)
-        float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f},
-              c3[4] = {0.f, 0.f, 0.f, 0.f};
+        // eight independent accumulation chains (k-step mod 4, high / low query parts)
+        float c8[8][4];
 #pragma unroll
-        for (int s = 0; s < 16; s += 2) {
-            const uint2 la = lut_lane[byte_of(kqa, s) * 32], lb = lut_lane[byte_of(kqb, s) * 32];
-            const uint2 ma = lut_lane[byte_of(kqa, s + 1) * 32], mb = lut_lane[byte_of(kqb, s + 1) * 32];
+        for (int i = 0; i < 8; i++) c8[i][0] = c8[i][1] = c8[i][2] = c8[i][3] = 0.f;
+#pragma unroll
+        for (int s = 0; s < 16; s++) {
+            const uint2 la = lut_lane[byte_of(kqa, s) * LUT_COPIES], lb = lut_lane[byte_of(kqb, s) * LUT_COPIES];
             const uint32_t a[4] = {la.x, lb.x, la.y, lb.y};
-            const uint32_t a2[4] = {ma.x, mb.x, ma.y, mb.y};
-            mma16816(c, a, bq[s]);
-            mma16816(c1, a, bql[s]);
-            mma16816(c2, a2, bq[s + 1]);
-            mma16816(c3, a2, bql[s + 1]);
+            mma16816(c8[2 * (s & 3)], a, bq[s]);
+            mma16816(c8[2 * (s & 3) + 1], a, bql[s]);
         }
+        float c[4];
 #pragma unroll
-        for (int e = 0; e < 4; e++) c[e] = (c[e] + c2[e]) + (c1[e] + c3[e]);
+        for (int e = 0; e < 4; e++)
+            c[e] = ((c8[0][e] + c8[2][e]) + (c8[4][e] + c8[6][e])) + ((c8[1][e] + c8[3][e]) + (c8[5][e] + c8[7][e]));
         // logits of keys g (c0, c1) and g+8 (c2, c3) for heads 2t, 2t+1
         float sA[2] = {va ? c[0] * kna : -INFINITY, va ? c[1] * kna : -INFINITY};
         float sB[2] = {vb ? c[2] * knb : -INFINITY, vb ? c[3] * knb : -INFINITY};
@@ -298,20 +357,28 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
                 o[s][0] *= resc[0]; o[s][1] *= resc[1]; o[s][2] *= resc[0]; o[s][3] *= resc[1];
             }
         }
-        // P (times the value norms) into the B operand: (key g | g+8; heads 2t, 2t+1) -> transposed
+        // P (times the value norms) into the B operand: (key g | g+8; heads 2t, 2t+1) -> (keys 2t, 2t+1 | +8; head g)
         uint32_t bp[2];
         bp[0] = movmatrix_trans(pack_h2(pa[0] * vna, pa[1] * vna));
         bp[1] = movmatrix_trans(pack_h2(pb[0] * vnb, pb[1] * vnb));
-        // O^T[256 dims x 8 heads] += V^T . P, one 16-dim tile per code byte index s
+        // O^T[256 dims x 8 heads] += V^T . P.  Code byte u of this thread's 8 (dims 32 g + 4 u .. + 3) of its four keys
+        // feeds two MMAs: tile 2u has rows (g, g + 8) = dims (32 g + 4 u, + 1), tile 2u + 1 the next two dims.  The
+        // A fragment wants (dim; two adjacent keys) per register: a byte permute of two table entries.
 #pragma unroll
-        for (int s = 0; s < 16; s++) {
-            const uint2 la = lut_lane[byte_of(vqa, s) * 32], lb = lut_lane[byte_of(vqb, s) * 32];
+        for (int u = 0; u < 8; u++) {
+            const uint2 e0 = lut_lane[byte_of(vqa, u) * LUT_COPIES], e1 = lut_lane[byte_of(vqa, 8 + u) * LUT_COPIES];   // keys 2t, 2t+1
+            const uint2 e2 = lut_lane[byte_of(vqb, u) * LUT_COPIES], e3 = lut_lane[byte_of(vqb, 8 + u) * LUT_COPIES];   // keys 2t+8, 2t+9
             uint32_t a[4];
-            a[0] = movmatrix_trans(la.x);   // dims rows 0-7,  keys 0-7
-            a[1] = movmatrix_trans(la.y);   // dims rows 8-15, keys 0-7
-            a[2] = movmatrix_trans(lb.x);   // dims rows 0-7,  keys 8-15
-            a[3] = movmatrix_trans(lb.y);   // dims rows 8-15, keys 8-15
-            mma16816(o[s], a, bp);
+            a[0] = __byte_perm(e0.x, e1.x, 0x5410);
+            a[1] = __byte_perm(e0.x, e1.x, 0x7632);
+            a[2] = __byte_perm(e2.x, e3.x, 0x5410);
+            a[3] = __byte_perm(e2.x, e3.x, 0x7632);
+            mma16816(o[2 * u], a, bp);
+            a[0] = __byte_perm(e0.y, e1.y, 0x5410);
+            a[1] = __byte_perm(e0.y, e1.y, 0x7632);
+            a[2] = __byte_perm(e2.y, e3.y, 0x5410);
+            a[3] = __byte_perm(e2.y, e3.y, 0x7632);
+            mma16816(o[2 * u + 1], a, bp);
         }
     }
 
@@ -324,7 +391,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     l_part[1] += __shfl_xor_sync(0xffffffffu, l_part[1], 16);
     __syncthreads();   // every warp is done with the table
     float *acc_s = reinterpret_cast<float *>(smem);   // [NW][G][HD]
-    float *m_s = reinterpret_cast<float *>(smem + LUT_BYTES);   // [NW][G]  (rq_s is dead too)
+    float *m_s = reinterpret_cast<float *>(smem + ACC_BYTES);   // [NW][G]  (query, table and ring are all dead)
     float *l_s = m_s + NW * G;
     if (g == 0) {
         m_s[warp * G + 2 * t] = m_run[0];
@@ -360,14 +427,14 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     }
     __syncthreads();
     // Thread (warp, lane) merges fragment position `lane` of tiles s = 2 warp, 2 warp + 1: element j of tile s is
-    // head 2t + (j & 1), dim 64 (g >> 1) + 4 s + (g & 1) + 2 (j >> 1).
+    // head 2t + (j & 1), dim 32 g + 2 s + (j >> 1).
 #pragma unroll
     for (int ss = 0; ss < 2; ss++) {
         const int s = 2 * warp + ss;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int h = 2 * t + (j & 1);
-            const int d = 64 * (g >> 1) + 4 * s + (g & 1) + 2 * (j >> 1);
+            const int d = 32 * g + 2 * s + (j >> 1);
             float acc = 0.f;
 #pragma unroll
             for (int w = 0; w < NW; w++) acc += f_s[w * G + h] * acc_s[((w * 16 + s) * 4 + j) * 32 + lane];
@@ -392,7 +459,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
 }  // namespace
 
 int lc_tq2_attn_mma_launch(lc_batch *b, const TqAttnParams &p, dim3 grid) {
-    const size_t smem = (size_t)LUT_BYTES + (size_t)G * HD * sizeof(float) + 256 * sizeof(uint2);
+    const size_t smem = SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
         LC_CUDA_TRY(cudaFuncSetAttribute(tq2_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
