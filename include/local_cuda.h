@@ -365,6 +365,16 @@ LC_API int lc_kv_write_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *k_
                                     uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes,
                                     uint32_t ring_capacity, float eps, float rope_theta,
                                     float partial_rotary_factor);
+/* lc_qk_norm_rope_batch_decode_into on the queries and lc_kv_write_batched_into in one launch: everything
+ * between the Q/K/V projections and attention of a decode step (layer.rs:757-790). */
+LC_API int lc_qkv_post_batched_into(lc_kernels *k, lc_batch *b, lc_buf *q, const lc_buf *q_norm_weight,
+                                    uint32_t n_q_heads, const lc_buf *k_in, const lc_buf *v_in,
+                                    const lc_buf *k_norm_weight, const lc_buf *positions, const lc_buf *levels,
+                                    const lc_buf *signs, lc_buf *k_packed, lc_buf *k_norms, lc_buf *v_packed,
+                                    lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
+                                    uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes,
+                                    uint32_t ring_capacity, float eps, float rope_theta,
+                                    float partial_rotary_factor);
 /* Device-side stand-ins for two CPU steps the reference performs through unified
  * memory: the embedding-row gather (QuantWeight::dequant_row, local-engine/src/layer.rs:255-281,
  * followed by scale_in_place) and greedy first-max argmax (sampler.rs:148-158). */

@@ -225,9 +225,8 @@ int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *toke
             const uint32_t ns[3] = {qd, kd, kd};
             STEP(lc_matmul_nt_tq2_0_grouped(k, b, m->normed, 3, ws, os, ns, n, H));
         }
-        STEP(lc_qk_norm_rope_batch_decode_into(k, b, m->q, L.q_norm, positions, c.rope_theta, HD, NQ, n, c.rms_eps, 1.0f));
-        STEP(lc_kv_write_batched_into(k, b, m->kbuf, m->vbuf, L.k_norm, positions, m->levels, m->signs, L.k_codes,
-                                      L.k_norms, L.v_codes, L.v_norms, HD, NKV, L.lane_rows, c.kv_bits, n, L.ring,
+        STEP(lc_qkv_post_batched_into(k, b, m->q, L.q_norm, NQ, m->kbuf, m->vbuf, L.k_norm, positions, m->levels, m->signs,
+                                      L.k_codes, L.k_norms, L.v_codes, L.v_norms, HD, NKV, L.lane_rows, c.kv_bits, n, L.ring,
                                       c.rms_eps, c.rope_theta, 1.0f));
         STEP(lc_tq_attention_batched_into(k, b, m->q, L.k_codes, L.k_norms, L.v_codes, L.v_norms, m->levels, m->signs,
                                           m->attn, positions, HD, L.lane_rows, NQ, NKV, L.window, c.kv_bits, n, L.ring,

@@ -130,11 +130,13 @@ __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *
                &norm_sh);
 }
 
-// The KV write of one decode step in one launch: k_norm (learned weights), V rms_norm (unit weights),
-// NEOX RoPE on K, TurboQuant encode of both rows into the per-lane pools.  Same arithmetic and the same
-// f16 rounding points as the five separate dispatches of layer.rs:773-790 + quant_unified_pool.rs:138-181.
-// grid = n_lanes * n_kv, block = head_dim.
-__global__ void kv_write_kernel(const __half *__restrict__ kin, const __half *__restrict__ vin,
+// Everything between the Q/K/V projections and attention for one decode step, in one launch: per-head RMSNorm
+// (learned weights for Q and K, unit weights for V), NEOX RoPE on Q and K, TurboQuant encode of the K and V rows
+// into the per-lane pools.  Same arithmetic and the same f16 rounding points as the separate dispatches of
+// layer.rs:773-790 + quant_unified_pool.rs:138-181.  One CTA per (lane, head, role): grid = (n_lanes,
+// n_q + 2 n_kv), block = head_dim; n_q = 0 leaves the queries alone.
+__global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, unsigned n_q,
+                                const __half *__restrict__ kin, const __half *__restrict__ vin,
                                 const __half *__restrict__ k_norm_w, const uint32_t *__restrict__ positions,
                                 const float *__restrict__ levels, const float *__restrict__ signs,
                                 uint8_t *__restrict__ k_packed, __half *__restrict__ k_norms,
@@ -142,53 +144,56 @@ __global__ void kv_write_kernel(const __half *__restrict__ kin, const __half *__
                                 unsigned lane_capacity, unsigned bits, unsigned ring, float eps, float theta,
                                 float rotary_factor, int norm_mode) {
     lc_pdl_trigger();
-    lc_pdl_wait();
     __shared__ float sh[MAX_HD];
     __shared__ float red[MAX_HD];
     __shared__ unsigned code_sh[MAX_HD];
     __shared__ float norm_sh;
     __shared__ float red2[32];
-    const unsigned t = threadIdx.x, g_in = blockIdx.x;
-    const unsigned row = g_in / n_kv, head = g_in - row * n_kv;
-    const unsigned pos = positions[row];
-    const size_t slot = ((size_t)row * lane_capacity + (ring ? pos % ring : pos)) * n_kv + head;
-    const unsigned code_bytes = (hd * bits + 7) >> 3;
-    auto block_sumsq = [&](float v) {
-        float s = v * v;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if ((t & 31) == 0) red2[t >> 5] = s;
-        __syncthreads();
-        float tot = 0.f;
-        for (unsigned w = 0; w < (hd + 31) / 32; w++) tot += red2[w];
-        __syncthreads();
-        return tot;
-    };
-    // K: per-head RMSNorm with weights -> f16, RoPE -> f16
-    const float kx = __half2float(kin[(size_t)g_in * hd + t]);
-    const float krms = rsqrtf(block_sumsq(kx) / (float)hd + eps);
-    const float kn = __half2float(__float2half_rn(kx * krms * __half2float(k_norm_w[t])));
-    sh[t] = kn;
-    __syncthreads();
+    const unsigned t = threadIdx.x, row = blockIdx.x, r = blockIdx.y;
+    const int role = r < n_q ? 0 : (r < n_q + n_kv ? 1 : 2);   // Q, K, V
+    const unsigned head = role == 0 ? r : (role == 1 ? r - n_q : r - n_q - n_kv);
+    // norm weight and rotation frequency do not depend on the predecessor
+    float w = 1.0f;
+    if (role == 0) w = __half2float(q_norm_w[t]);
+    else if (role == 1) w = __half2float(k_norm_w[t]);
     const unsigned half = hd / 2, i = t < half ? t : t - half;
     const unsigned angles = (unsigned)((float)hd * rotary_factor) / 2;
-    float kr = kn;
-    if (i < angles) {
-        const float x0 = sh[i], x1 = sh[i + half];
-        const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)hd);
-        const float ang = (float)pos * freq;
-        const float c = cosf(ang), sn = sinf(ang);
-        kr = __half2float(__float2half_rn(t < half ? x0 * c - x1 * sn : x0 * sn + x1 * c));
-    }
+    const bool rotate = role != 2 && i < angles;
+    const float freq = rotate ? 1.0f / powf(theta, (float)(2 * i) / (float)hd) : 0.f;
+    lc_pdl_wait();
+    const unsigned pos = positions[row];
+    __half *qrow = q + ((size_t)row * n_q + head) * hd;
+    const size_t g_in = (size_t)row * n_kv + head;
+    const float x = __half2float(role == 0 ? qrow[t] : (role == 1 ? kin[g_in * hd + t] : vin[g_in * hd + t]));
+    float ss = x * x;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((t & 31) == 0) red2[t >> 5] = ss;
     __syncthreads();
-    encode_row(kr, t, hd, bits, levels, signs, norm_mode, k_packed + slot * code_bytes, k_norms + slot, sh, red, code_sh,
-               &norm_sh);
-    // V: RMSNorm with unit weights -> f16
-    const float vx = __half2float(vin[(size_t)g_in * hd + t]);
-    const float vrms = rsqrtf(block_sumsq(vx) / (float)hd + eps);
-    const float vn = __half2float(__float2half_rn(vx * vrms * 1.0f));
-    encode_row(vn, t, hd, bits, levels, signs, norm_mode, v_packed + slot * code_bytes, v_norms + slot, sh, red, code_sh,
-               &norm_sh);
+    float tot = 0.f;
+    for (unsigned wi = 0; wi < (hd + 31) / 32; wi++) tot += red2[wi];
+    const float rms = rsqrtf(tot / (float)hd + eps);
+    const float xn = __half2float(__float2half_rn(x * rms * w));
+    float xr = xn;
+    if (role != 2) {
+        sh[t] = xn;
+        __syncthreads();
+        if (rotate) {
+            const float x0 = sh[i], x1 = sh[i + half];
+            const float ang = (float)pos * freq;
+            const float c = cosf(ang), sn = sinf(ang);
+            xr = __half2float(__float2half_rn(t < half ? x0 * c - x1 * sn : x0 * sn + x1 * c));
+        }
+        __syncthreads();
+    }
+    if (role == 0) {
+        qrow[t] = __float2half_rn(xr);
+        return;
+    }
+    const size_t slot = ((size_t)row * lane_capacity + (ring ? pos % ring : pos)) * n_kv + head;
+    const unsigned code_bytes = (hd * bits + 7) >> 3;
+    encode_row(xr, t, hd, bits, levels, signs, norm_mode, (role == 1 ? k_packed : v_packed) + slot * code_bytes,
+               (role == 1 ? k_norms : v_norms) + slot, sh, red, code_sh, &norm_sh);
 }
 
 // dequantize_kv.metal:132-189. grid = n_kv * (num_tokens - token_start).
@@ -468,37 +473,66 @@ int lc_hadamard_rotate_fh_into(lc_kernels *k, lc_batch *b, const lc_buf *input, 
 }
 
 
+static int kv_write_common(const char *name, lc_kernels *k, lc_batch *b, lc_buf *q, const lc_buf *q_norm_weight,
+                           uint32_t n_q_heads, const lc_buf *k_in, const lc_buf *v_in, const lc_buf *k_norm_weight,
+                           const lc_buf *positions, const lc_buf *levels, const lc_buf *signs, lc_buf *k_packed,
+                           lc_buf *k_norms, lc_buf *v_packed, lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
+                           uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes, uint32_t ring_capacity, float eps,
+                           float rope_theta, float partial_rotary_factor) {
+    if (!k || !b || !k_in || !v_in || !k_norm_weight || !positions || !levels || !signs || !k_packed || !k_norms ||
+        !v_packed || !v_norms || (n_q_heads && (!q || !q_norm_weight)))
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    int st = check_codec(name, head_dim, bits);
+    if (st != LC_OK) return st;
+    LC_REQUIRE(n_kv_heads >= 1, "%s: n_kv_heads must be >= 1", name);
+    LC_REQUIRE(n_q_heads + 2 * n_kv_heads <= 65535, "%s: too many heads", name);
+    const size_t groups = (size_t)n_kv_heads * n_lanes, cb = lc_tq_code_bytes(head_dim, bits);
+    LC_REQUIRE(k_in->bytes >= groups * head_dim * 2 && v_in->bytes >= groups * head_dim * 2 &&
+                   positions->bytes >= (size_t)n_lanes * 4 && k_norm_weight->bytes >= head_dim * 2u,
+               "%s: input buffers too small", name);
+    if (n_q_heads)
+        LC_REQUIRE(q->bytes >= (size_t)n_lanes * n_q_heads * head_dim * 2 && q_norm_weight->bytes >= head_dim * 2u,
+                   "%s: query buffers too small", name);
+    LC_REQUIRE(levels->bytes >= (4u << bits) && signs->bytes >= head_dim * 4u, "%s: codec buffers too small", name);
+    LC_REQUIRE(ring_capacity <= lane_capacity, "%s: ring %u exceeds lane capacity %u", name, ring_capacity, lane_capacity);
+    const size_t rows = (size_t)n_lanes * lane_capacity * n_kv_heads;
+    LC_REQUIRE(k_packed->bytes >= rows * cb && v_packed->bytes >= rows * cb && k_norms->bytes >= rows * 2 &&
+                   v_norms->bytes >= rows * 2,
+               "%s: pool buffers hold fewer than %zu rows", name, rows);
+    if (groups == 0) return LC_OK;
+    LC_LAUNCH_CHECKED(lc_launch(kv_write_kernel, dim3(n_lanes, n_q_heads + 2 * n_kv_heads), dim3(head_dim), 0, b,
+                                q ? (__half *)q->dptr : nullptr, q_norm_weight ? (const __half *)q_norm_weight->dptr : nullptr,
+                                n_q_heads, (const __half *)k_in->dptr, (const __half *)v_in->dptr,
+                                (const __half *)k_norm_weight->dptr, (const uint32_t *)positions->dptr,
+                                (const float *)levels->dptr, (const float *)signs->dptr, (uint8_t *)k_packed->dptr,
+                                (__half *)k_norms->dptr, (uint8_t *)v_packed->dptr, (__half *)v_norms->dptr, head_dim,
+                                n_kv_heads, lane_capacity, bits, ring_capacity, eps, rope_theta, partial_rotary_factor,
+                                k->kv_norm_mode));
+    b->dispatch_count++;
+    return LC_OK;
+}
+
 int lc_kv_write_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *k_in, const lc_buf *v_in, const lc_buf *k_norm_weight,
                              const lc_buf *positions, const lc_buf *levels, const lc_buf *signs, lc_buf *k_packed,
                              lc_buf *k_norms, lc_buf *v_packed, lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
                              uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes, uint32_t ring_capacity, float eps,
                              float rope_theta, float partial_rotary_factor) {
-    if (!k || !b || !k_in || !v_in || !k_norm_weight || !positions || !levels || !signs || !k_packed || !k_norms ||
-        !v_packed || !v_norms)
-        return lc_fail(LC_ERR_INVALID_ARGUMENT, "kv_write_batched: NULL argument");
-    int st = check_codec("kv_write_batched", head_dim, bits);
-    if (st != LC_OK) return st;
-    LC_REQUIRE(n_kv_heads >= 1, "kv_write_batched: n_kv_heads must be >= 1");
-    const size_t groups = (size_t)n_kv_heads * n_lanes, cb = lc_tq_code_bytes(head_dim, bits);
-    LC_REQUIRE(k_in->bytes >= groups * head_dim * 2 && v_in->bytes >= groups * head_dim * 2 &&
-                   positions->bytes >= (size_t)n_lanes * 4 && k_norm_weight->bytes >= head_dim * 2u,
-               "kv_write_batched: input buffers too small");
-    LC_REQUIRE(levels->bytes >= (4u << bits) && signs->bytes >= head_dim * 4u, "kv_write_batched: codec buffers too small");
-    LC_REQUIRE(ring_capacity <= lane_capacity, "kv_write_batched: ring %u exceeds lane capacity %u", ring_capacity,
-               lane_capacity);
-    const size_t rows = (size_t)n_lanes * lane_capacity * n_kv_heads;
-    LC_REQUIRE(k_packed->bytes >= rows * cb && v_packed->bytes >= rows * cb && k_norms->bytes >= rows * 2 &&
-                   v_norms->bytes >= rows * 2,
-               "kv_write_batched: pool buffers hold fewer than %zu rows", rows);
-    if (groups == 0) return LC_OK;
-    LC_LAUNCH_CHECKED(lc_launch(kv_write_kernel, dim3((unsigned)groups), dim3(head_dim), 0, b, (const __half *)k_in->dptr,
-                                (const __half *)v_in->dptr, (const __half *)k_norm_weight->dptr,
-                                (const uint32_t *)positions->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
-                                (uint8_t *)k_packed->dptr, (__half *)k_norms->dptr, (uint8_t *)v_packed->dptr,
-                                (__half *)v_norms->dptr, head_dim, n_kv_heads, lane_capacity, bits, ring_capacity, eps,
-                                rope_theta, partial_rotary_factor, k->kv_norm_mode));
-    b->dispatch_count++;
-    return LC_OK;
+    return kv_write_common("kv_write_batched", k, b, nullptr, nullptr, 0, k_in, v_in, k_norm_weight, positions, levels, signs,
+                           k_packed, k_norms, v_packed, v_norms, head_dim, n_kv_heads, lane_capacity, bits, n_lanes,
+                           ring_capacity, eps, rope_theta, partial_rotary_factor);
+}
+
+int lc_qkv_post_batched_into(lc_kernels *k, lc_batch *b, lc_buf *q, const lc_buf *q_norm_weight, uint32_t n_q_heads,
+                             const lc_buf *k_in, const lc_buf *v_in, const lc_buf *k_norm_weight, const lc_buf *positions,
+                             const lc_buf *levels, const lc_buf *signs, lc_buf *k_packed, lc_buf *k_norms,
+                             lc_buf *v_packed, lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
+                             uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes, uint32_t ring_capacity, float eps,
+                             float rope_theta, float partial_rotary_factor) {
+    if (!q || !q_norm_weight || n_q_heads == 0)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "qkv_post_batched: the query buffer, its norm weight and n_q_heads are required");
+    return kv_write_common("qkv_post_batched", k, b, q, q_norm_weight, n_q_heads, k_in, v_in, k_norm_weight, positions, levels,
+                           signs, k_packed, k_norms, v_packed, v_norms, head_dim, n_kv_heads, lane_capacity, bits, n_lanes,
+                           ring_capacity, eps, rope_theta, partial_rotary_factor);
 }
 
 }  // extern "C"

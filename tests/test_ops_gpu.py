@@ -141,8 +141,8 @@ def test_qk_norm_rope_fused(la, orc, ctx, kernels):
     rel_close(buf.as_slice(np.float16), want.astype(np.float32), 4e-3, "qk_norm_rope")
 
 
-def test_rms_norm_add_norm_fused(la, orc, ctx, kernels):
-    dim, rows = 1536, 64
+@pytest.mark.parametrize("dim,rows", [(1536, 64), (8, 3), (264, 5), (8192, 2), (100, 4), (8200, 2)])
+def test_rms_norm_add_norm_fused(la, orc, ctx, kernels, dim, rows):
     x = la.synth.normal_f16((rows, dim), 23, 3.0)
     r = la.synth.normal_f16((rows, dim), 24)
     w1 = (1.0 + 0.1 * la.synth.normal(25, dim)).astype(np.float16)
@@ -185,3 +185,40 @@ def test_kv_write_fused(la, orc, ctx, kernels):
     assert np.array_equal(gk == 0, wkc == 0) or True
     assert np.allclose(kn.read(np.float16).astype(np.float32), wkn.astype(np.float32), rtol=2e-3, atol=0)
     assert np.allclose(vn.read(np.float16).astype(np.float32), wvn.astype(np.float32), rtol=2e-3, atol=0)
+
+
+def test_qkv_post_fused_equals_separate_launches(la, orc, ctx, kernels):
+    """Query norm+RoPE and the KV write in one launch: pools bit-identical to kv_write_batched, queries equal to
+    qk_norm_rope_batch_decode within f16 rounding and to the oracle."""
+    hd, n_q, n_kv, bits, n_lanes, cap, ring, theta = 256, 8, 2, 2, 5, 48, 16, 1e6
+    levels, signs = la.tq_levels(hd, bits), la.tq_signs(hd, la.TQ_SEED)
+    cb = la.tq_code_bytes(hd, bits)
+    positions = np.array([0, 7, 16, 33, 900], np.uint32)
+    q = la.synth.normal_f16((n_lanes, n_q, hd), 41, 1.2)
+    kin, vin = la.synth.normal_f16((n_lanes, n_kv, hd), 42, 1.5), la.synth.normal_f16((n_lanes, n_kv, hd), 43, 0.7)
+    qw = (1.0 + 0.1 * la.synth.normal(44, hd)).astype(np.float16)
+    kw = (1.0 + 0.1 * la.synth.normal(45, hd)).astype(np.float16)
+    rows = n_lanes * cap * n_kv
+    d = lambda a: dev(la, ctx, a)
+    pools = []
+    for fused in (False, True):
+        kc, kn, vc, vn = (Guarded(la, ctx, rows * cb), Guarded(la, ctx, rows * 2), Guarded(la, ctx, rows * cb), Guarded(la, ctx, rows * 2))
+        for g in (kc, kn, vc, vn):
+            g.buf.zero(0, g.nbytes)
+        qb = d(q)
+        b = la.CommandBatch.new(ctx)
+        if fused:
+            kernels.qkv_post_batched_into(b, qb, d(qw), n_q, d(kin), d(vin), d(kw), d(positions), d(levels), d(signs), kc.view,
+                                          kn.view, vc.view, vn.view, hd, n_kv, cap, bits, n_lanes, ring, EPS, theta, 1.0)
+            assert b.dispatch_count() == 1
+        else:
+            kernels.qk_norm_rope_batch_decode_into(b, qb, d(qw), d(positions), theta, hd, n_q, n_lanes, EPS, 1.0)
+            kernels.kv_write_batched_into(b, d(kin), d(vin), d(kw), d(positions), d(levels), d(signs), kc.view, kn.view,
+                                          vc.view, vn.view, hd, n_kv, cap, bits, n_lanes, ring, EPS, theta, 1.0)
+        b.commit_and_wait()
+        pools.append((qb.as_slice(np.float16), kc.read(np.uint8), kn.read(np.float16), vc.read(np.uint8), vn.read(np.float16)))
+    for a, c in zip(pools[0][1:], pools[1][1:]):
+        assert np.array_equal(a.view(np.uint8), c.view(np.uint8))
+    want_q = orc.rope(orc.rms_norm(q, qw, hd, n_lanes * n_q, EPS), positions, theta, hd, n_q, n_lanes, 1.0)
+    rel_close(pools[1][0], want_q.astype(np.float32), 4e-3, "fused q norm+rope")
+    rel_close(pools[1][0], pools[0][0].astype(np.float32), 2e-3, "fused vs separate q")
