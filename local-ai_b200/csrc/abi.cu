@@ -384,6 +384,7 @@ int lc_kernels_create(lc_ctx *ctx, lc_kernels **out) {
     k->batchm = env_enabled("LOCAL_AI_BATCHM");
     k->smallm = env_enabled("LOCAL_AI_SMALLM");
     k->mma = env_enabled("LOCAL_AI_MMA");
+    k->decode_mma = env_enabled("LOCAL_CUDA_DECODE_MMA");
     const char *nm = getenv("LOCAL_CUDA_TQ_NORM");
     k->kv_norm_mode = (nm && strcmp(nm, "tree") == 0) ? 1 : 0;
     cudaError_t e = cudaMalloc((void **)&k->dev_status, 128);  // status word + tuning stamps

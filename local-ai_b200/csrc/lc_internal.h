@@ -48,6 +48,7 @@ struct lc_kernels {
     bool batchm = true;  // LOCAL_AI_BATCHM: register-resident small-M path
     bool smallm = true;  // LOCAL_AI_SMALLM
     bool mma = true;     // LOCAL_AI_MMA: tensor-core path for larger M
+    bool decode_mma = true;  // LOCAL_CUDA_DECODE_MMA: register-direct mma.sync path for 8 < M <= 64 (0: tcgen05 there too)
     int kv_norm_mode = 0;  // LOCAL_CUDA_TQ_NORM: 0 sequential (Rust codec order), 1 tree (Metal order)
     // Library-owned scratch for split-K partials (grown outside graph capture).
     void *scratch = nullptr;

@@ -2,10 +2,13 @@
 // stand-in for Kernels::matmul_nt_q4_0_into / matmul_nt_tq2_0_into
 // (local-metal/src/kernels.rs:6459-6563).  The reference picks between four
 // Metal kernels by m (batchm <= 4, smallm <= 8, simdgroup MMA, scalar tile);
-// here the choice is between two: the register-resident CUDA-core path that
-// streams the weights once for up to 16 rows (qmatvec.cu) and the tcgen05
+// here the choice is between three: the register-resident CUDA-core path that
+// streams the weights once for up to 16 rows (qmatvec.cu, m <= 8), the
+// register-direct mma.sync path for decode batches (qmatmul_mma.cu, 8 < m <= 64,
+// where launch latency rather than tensor throughput decides) and the tcgen05
 // tensor-core path for larger m (qmatmul_tc.cu).  LOCAL_AI_MMA=0 forces the
-// CUDA-core path for every m, as it forces the non-MMA kernels in the reference.
+// CUDA-core path for every m, as it forces the non-MMA kernels in the reference;
+// LOCAL_CUDA_DECODE_MMA=0 sends 8 < m <= 64 to the tcgen05 path as well.
 #include "lc_internal.h"
 
 int lc_qgemm_cuda_core(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
@@ -17,12 +20,24 @@ int lc_check_qargs(int fmt, const char *name, lc_kernels *k, lc_batch *b, const 
 int lc_qgemm_tcgen05(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
                      const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n);
 
+// qmatmul_mma.cu: same contract as lc_qgemm_tcgen05_grouped, for 8 < m <= 64.
+int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
+                         const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
+                         uint32_t kk);
+
 static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch *b, const lc_buf *input,
                  const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
     int st = lc_check_qargs(fmt, name, k, b, weight, input, output, m, kk, n, f32out ? 4 : 2);
     if (st != LC_OK) return st;
     if (n == 0) return LC_OK;
     if (k->mma && m > 8) {
+        if (k->decode_mma && m <= 64) {
+            const lc_buf *ws[1] = {weight};
+            lc_buf *os[1] = {output};
+            const uint32_t ns[1] = {n};
+            st = lc_qgemm_mma_grouped(fmt, f32out, k, b, input, 1, ws, os, ns, m, kk);
+            if (st >= 0) return st;
+        }
         st = lc_qgemm_tcgen05(fmt, f32out, k, b, input, weight, output, m, kk, n);
         if (st >= 0) return st;
     }
@@ -42,7 +57,9 @@ int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, 
         if (st != LC_OK) return st;
     }
     if (k->mma && m > 8) {
-        int st = lc_qgemm_tcgen05_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
+        int st = -1;
+        if (k->decode_mma && m <= 64) st = lc_qgemm_mma_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
+        if (st < 0) st = lc_qgemm_tcgen05_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
         if (st >= 0) return st;
     }
     for (int g = 0; g < ng; g++) {

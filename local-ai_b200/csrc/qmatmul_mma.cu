@@ -1,0 +1,376 @@
+// Register-direct tensor-core path of the quantized batched matmul for 8 < m <= 64 (decode batches):
+//   C[m, n] = A[m, K] (f16) x W[n, K]^T,  W in GGUF TQ2_0 / Q4_0 blocks.
+// Stands in, for these m, for the reference's simdgroup-matrix kernels matmul_nt_{q4_0,tq2_0}_mma
+// (shaders/matvec_quant.metal:447-577).
+//
+// At these batch sizes a projection of a decoder layer is a few microseconds of HBM traffic, so what matters
+// is the length of the dependent chain inside a launch and how much of it can run before the previous kernel
+// has finished.  The kernel therefore has no cross-warp pipeline, no TMEM and no operand staging of weights:
+//   * before the dependency wait, every warp copies the raw quantized blocks of its own 16 weight rows (this
+//     CTA's K range) into shared memory with 16-byte cp.async (rows are only 2-byte aligned: the enclosing
+//     16-byte ranges are copied);
+//   * after the wait, the activations [m, K range] stream through two shared-memory buffers of 256 k with
+//     cp.async;
+//   * each warp walks its rows' blocks: 2-byte pieces of code bytes -> f16 weights in registers, directly in the
+//     layout of the m16n8k16 A fragment (thread t of a quad owns bytes 2t, 2t+1 of every 8-byte group, which are
+//     the k values 2t, 2t+1 the fragment wants), B fragments by ldmatrix, f32 accumulators in registers.
+// Weights take the MMA's M dimension, the batch its N dimension.  When K is split (grid.z > 1) the CTAs of a
+// tile form a thread-block cluster: each stages its partial tile in its own shared memory and, after a cluster
+// barrier, every CTA adds one slice of the tile over all splits in split order through distributed shared
+// memory and stores it -- deterministic, with no round trip through global memory.
+//
+// Numerics: identical to the tcgen05 path.  TQ2_0 weights d (q - 1) are exact in f16; Q4_0 weights d (q - 8)
+// are rounded once to f16; accumulation is f32.
+#include "lc_internal.h"
+
+namespace {
+
+constexpr int FMT_Q4_0 = 0;
+constexpr int FMT_TQ2_0 = 1;
+constexpr int NW = 8;              // warps per CTA
+constexpr int NT = NW * 32;
+constexpr int WROWS = 16;          // weight rows per warp (one MMA tile)
+constexpr int CTA_ROWS = NW * WROWS;
+constexpr int CHUNK_K = 256;       // k per activation buffer
+constexpr int XS = CHUNK_K * 2 + 16;   // bytes per activation row in a buffer (+16: ldmatrix rows spread over banks)
+constexpr int MAX_GROUPS = 3;
+constexpr int MAX_KS = 8;          // portable cluster size
+
+struct MmaParams {
+    const uint8_t *w[MAX_GROUPS];
+    void *out[MAX_GROUPS];
+    int n[MAX_GROUPS], tile_end[MAX_GROUPS];
+    int ngroups;
+    const __half *x;
+    int m, K, nb;          // nb = blocks per weight row
+    int ks, bps;           // split-K: grid.z = cluster size = ks, bps = blocks per split
+    int raw_rs;            // bytes reserved per row of raw blocks
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes = 16u) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t b0, const uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_addr, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(local_addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra));
+    return v;
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
+__device__ __forceinline__ uint32_t lds_u16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
+
+template <int FMT> struct Fmt;
+template <> struct Fmt<FMT_Q4_0> { static constexpr int bytes = 18, elems = 32, chunk_blocks = CHUNK_K / 32; };
+template <> struct Fmt<FMT_TQ2_0> { static constexpr int bytes = 66, elems = 256, chunk_blocks = 1; };
+
+// NBT: 8-row batch tiles (m <= 8 NBT).
+template <int FMT, int NBT, typename OutT>
+__global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int BB = Fmt<FMT>::bytes, BE = Fmt<FMT>::elems, CHB = Fmt<FMT>::chunk_blocks;
+    constexpr int XBUF = 8 * NBT * XS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    lc_pdl_trigger();
+    int grp = 0;
+    while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
+    const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * CTA_ROWS;
+    const int n_rows = p.n[grp];
+    const uint8_t *wmat = p.w[grp];
+    const size_t rb = (size_t)p.nb * BB, w_bytes = rb * (size_t)n_rows;
+    const int kbs = (int)blockIdx.z * p.bps, kbe = min(p.nb, kbs + p.bps), nblk = max(kbe - kbs, 0);
+    const int seg = nblk * BB;
+    uint8_t *x_s = smem;                                   // [2][8 NBT][XS]; reused for the split-K exchange
+    uint8_t *raw = smem + 2 * XBUF;                        // [128][raw_rs]
+
+    // ---- 1. this warp's raw weight rows -> shared memory (does not depend on the previous kernel) ----
+    for (int rr = 0; rr < WROWS && nblk > 0; rr++) {
+        const int r = warp * WROWS + rr, row = n0 + r;
+        if (row >= n_rows) break;
+        const size_t g0 = (size_t)row * rb + (size_t)kbs * BB, a0 = g0 & ~(size_t)15;
+        const int npieces = (int)((g0 + seg - a0 + 15) >> 4);
+        for (int pc = lane; pc < npieces; pc += 32) {
+            const size_t ga = a0 + ((size_t)pc << 4);
+            uint8_t *dst = raw + r * p.raw_rs + (pc << 4);
+            if (ga + 16 <= w_bytes) {
+                cp_async16(smem_u32(dst), wmat + ga);
+            } else {
+                for (int b = 0; b < 16; b++) dst[b] = (ga + b < w_bytes) ? wmat[ga + b] : 0;
+            }
+        }
+    }
+    cp_async_commit();
+    lc_pdl_wait();
+
+    // ---- 2. activation chunks: [8 NBT rows][256 k] per buffer, 16-byte pieces, rows beyond m zero-filled ----
+    const int nchunks = (nblk + CHB - 1) / CHB;
+    auto load_chunk = [&](int ch) {
+        const int cb0 = ch * CHB, cblk = min(CHB, nblk - cb0);
+        const int ppr = cblk * BE / 8;                      // 16-byte pieces per row
+        const __half *src0 = p.x + (size_t)(kbs + cb0) * BE;
+        uint8_t *buf = x_s + (ch & 1) * XBUF;
+        for (int it = tid; it < 8 * NBT * ppr; it += NT) {
+            const int r = it / ppr, pc = it - r * ppr;
+            const bool ok = r < p.m;
+            cp_async16(smem_u32(buf + r * XS + pc * 16), ok ? (const void *)(src0 + (size_t)r * p.K + pc * 8) : (const void *)p.x,
+                       ok ? 16u : 0u);
+        }
+    };
+    if (nchunks > 0) load_chunk(0);
+    cp_async_commit();
+    if (nchunks > 1) load_chunk(1);
+    cp_async_commit();
+
+    // ---- 3. main loop: 16 weight rows x (8 NBT) batch rows per warp ----
+    float c[NBT][4];
+#pragma unroll
+    for (int j = 0; j < NBT; j++) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+    // the two rows this thread dequantizes: warp rows g and g + 8
+    const uint8_t *rbase[2];
+    bool rvalid[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int r = warp * WROWS + g + 8 * i, row = n0 + r;
+        const size_t g0 = (size_t)row * rb + (size_t)kbs * BB;
+        rbase[i] = raw + r * p.raw_rs + (int)(g0 & 15);
+        rvalid[i] = row < n_rows;
+    }
+    // ldmatrix lane address: matrix mi = lane >> 3 is (batch tile j + (mi >> 1), k half mi & 1 of the 16-k step)
+    const uint32_t xl = (uint32_t)((8 * (lane >> 4) + (lane & 7)) * XS + ((lane >> 3) & 1) * 16);
+
+    for (int ch = 0; ch < nchunks; ch++) {
+        cp_async_wait<1>();          // chunk ch (and the raw rows) have landed for this thread
+        __syncthreads();             // ... and for every thread
+        const uint32_t xb = smem_u32(x_s + (ch & 1) * XBUF) + xl;
+        const int cb0 = ch * CHB, cblk = min(CHB, nblk - cb0);
+        if (FMT == FMT_TQ2_0) {
+            // one block: element 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j
+            const __half2 c1025 = __float2half2_rn(1025.0f);
+            __half2 d2[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const __half d = *reinterpret_cast<const __half *>(rbase[i] + cb0 * BB + 64);
+                d2[i] = __half2half2(rvalid[i] ? d : __float2half(0.0f));
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                // pieces: bytes 8 q + 2 t, + 1 of the half (q = 0..3), packed two per word
+                uint32_t wq[2][2];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const uint8_t *hp = rbase[i] + cb0 * BB + h * 32 + 2 * t;
+                    wq[i][0] = lds_u16(hp) | (lds_u16(hp + 8) << 16);
+                    wq[i][1] = lds_u16(hp + 16) | (lds_u16(hp + 24) << 16);
+                }
+#pragma unroll
+                for (int l = 0; l < 4; l++) {
+#pragma unroll
+                    for (int qp = 0; qp < 2; qp++) {
+                        uint32_t a[4];
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            const uint32_t codes = (wq[i][qp] >> (2 * l)) & 0x03030303u;
+                            a[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1025), d2[i]));
+                            a[i + 2] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1025), d2[i]));
+                        }
+                        const uint32_t xk = xb + (uint32_t)((128 * h + 32 * l + 16 * qp) * 2);
+#pragma unroll
+                        for (int j = 0; j < NBT; j += 2) {
+                            uint32_t b[4];
+                            ldmatrix_x4(b, xk + (uint32_t)(8 * j * XS));
+                            mma16816(c[j], a, b[0], b[1]);
+                            mma16816(c[j + 1], a, b[2], b[3]);
+                        }
+                    }
+                }
+            }
+        } else {
+            // up to 8 blocks of 32 k: f16 scale, then byte i holds k = i (low nibble) and k = i + 16 (high nibble)
+            const __half2 c1032 = __float2half2_rn(1032.0f);
+            for (int bi = 0; bi < cblk; bi++) {
+                __half2 d2[2];
+                uint32_t wq[2];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const uint8_t *bp = rbase[i] + (cb0 + bi) * BB;
+                    const __half d = *reinterpret_cast<const __half *>(bp);
+                    d2[i] = __half2half2(rvalid[i] ? d : __float2half(0.0f));
+                    wq[i] = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
+                }
+#pragma unroll
+                for (int part = 0; part < 2; part++) {
+                    uint32_t a[4];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const uint32_t codes = (wq[i] >> (4 * part)) & 0x0F0F0F0Fu;
+                        a[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032), d2[i]));
+                        a[i + 2] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032), d2[i]));
+                    }
+                    const uint32_t xk = xb + (uint32_t)((32 * bi + 16 * part) * 2);
+#pragma unroll
+                    for (int j = 0; j < NBT; j += 2) {
+                        uint32_t b[4];
+                        ldmatrix_x4(b, xk + (uint32_t)(8 * j * XS));
+                        mma16816(c[j], a, b[0], b[1]);
+                        mma16816(c[j + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();             // every warp is done with buffer ch & 1
+        if (ch + 2 < nchunks) load_chunk(ch + 2);
+        cp_async_commit();
+    }
+
+    // ---- 4. results.  c[j][e]: weight row 16 warp + g + 8 (e >> 1), batch row 8 j + 2 t + (e & 1) ----
+    OutT *out = reinterpret_cast<OutT *>(p.out[grp]);
+    auto store_tile = [&](const float4 v, int w, int ln, int j) {
+        const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int row = n0 + w * WROWS + (ln >> 2) + 8 * (e >> 1), col = 8 * j + 2 * (ln & 3) + (e & 1);
+            if (row < n_rows && col < p.m) store_c(out + (size_t)col * n_rows + row, e4[e]);
+        }
+    };
+    if (p.ks == 1) {
+#pragma unroll
+        for (int j = 0; j < NBT; j++) store_tile(make_float4(c[j][0], c[j][1], c[j][2], c[j][3]), warp, lane, j);
+        return;
+    }
+    // Split K: the ks CTAs of this tile are one cluster.  Partial tiles are exchanged through shared memory.
+    cp_async_wait<0>();
+    float4 *red = reinterpret_cast<float4 *>(x_s);           // [NBT][NT]
+#pragma unroll
+    for (int j = 0; j < NBT; j++) red[j * NT + tid] = make_float4(c[j][0], c[j][1], c[j][2], c[j][3]);
+    cluster_sync();
+    // items (j, source warp) are dealt round-robin to the CTAs of the cluster; a warp adds the ks partials of an
+    // item in split order and stores it
+    const int rank = (int)blockIdx.z;
+    for (int item = rank + p.ks * warp; item < NBT * NW; item += p.ks * NW) {
+        const int j = item / NW, w = item - j * NW;
+        const uint32_t la = smem_u32(red + j * NT + w * 32 + lane);
+        float4 v[MAX_KS];
+#pragma unroll
+        for (int sp = 0; sp < MAX_KS; sp++) v[sp] = sp < p.ks ? ld_dsmem_f4(la, (uint32_t)sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int sp = 0; sp < MAX_KS; sp++) {
+            acc.x += v[sp].x; acc.y += v[sp].y; acc.z += v[sp].z; acc.w += v[sp].w;
+        }
+        store_tile(acc, w, lane, j);
+    }
+    cluster_sync();   // no CTA leaves while a peer may still read its shared memory
+}
+
+template <int FMT, int NBT, typename OutT>
+int launch_mma(lc_batch *b, const MmaParams &p, dim3 grid, size_t smem) {
+    auto kern = qgemm_mma_kernel<FMT, NBT, OutT>;
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = b->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (b->ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (p.ks > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = (unsigned)p.ks;
+        na++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    LC_LAUNCH_CHECKED(cudaLaunchKernelEx(&cfg, kern, p));
+    b->dispatch_count++;
+    return LC_OK;
+}
+
+template <int FMT, typename OutT>
+int launch_mma_nbt(lc_batch *b, const MmaParams &p, dim3 grid, size_t smem, int nbt) {
+    switch (nbt) {
+        case 2: return launch_mma<FMT, 2, OutT>(b, p, grid, smem);
+        case 4: return launch_mma<FMT, 4, OutT>(b, p, grid, smem);
+        default: return launch_mma<FMT, 8, OutT>(b, p, grid, smem);
+    }
+}
+
+}  // namespace
+
+// Grouped launch: `ng` weight matrices [ns[g], kk] sharing the activations `input` [m, kk], 8 < m <= 64.
+// Returns LC_OK after a launch, a positive status on error, or -1 when the shape is outside what this kernel
+// covers (the caller then uses another path).
+int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
+                         const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
+                         uint32_t kk) {
+    const int be = fmt == FMT_Q4_0 ? 32 : 256, bb = fmt == FMT_Q4_0 ? 18 : 66;
+    if (m > 64 || ng < 1 || ng > MAX_GROUPS || kk % be != 0 || !lc_aligned(input->dptr, 16)) return -1;
+    MmaParams p;
+    p.x = (const __half *)input->dptr;
+    p.m = (int)m;
+    p.K = (int)kk;
+    p.nb = (int)(kk / be);
+    p.ngroups = ng;
+    int tiles = 0;
+    for (int g = 0; g < MAX_GROUPS; g++) {
+        const int gi = g < ng ? g : ng - 1;
+        p.w[g] = (const uint8_t *)weights[gi]->dptr;
+        p.out[g] = outputs[gi]->dptr;
+        p.n[g] = (int)ns[gi];
+        if (g < ng) tiles += ((int)ns[g] + CTA_ROWS - 1) / CTA_ROWS;
+        p.tile_end[g] = tiles;
+    }
+    const int nbt = m <= 16 ? 2 : (m <= 32 ? 4 : 8);
+    // Split K (at most 8 ways: one cluster per tile) until there are about two CTAs per SM; whole 256-k chunks per
+    // split, and no more raw bytes per CTA than fit beside the activation buffers.
+    const int chb = CHUNK_K / be;                       // blocks per 256 k
+    const int nchunk = (p.nb + chb - 1) / chb;
+    int ks = (2 * k->ctx->sm_count + tiles - 1) / tiles;
+    if (ks > MAX_KS) ks = MAX_KS;
+    if (ks > nchunk) ks = nchunk;
+    if (ks < 1) ks = 1;
+    int cps = (nchunk + ks - 1) / ks;                   // chunks per split
+    ks = (nchunk + cps - 1) / cps;
+    p.ks = ks;
+    p.bps = cps * chb;
+    p.raw_rs = ((p.bps * bb + 15 + 15) / 16) * 16;
+    if ((p.raw_rs / 16) % 2 == 0) p.raw_rs += 16;      // odd multiple of 16 bytes: rows spread over the banks
+    const size_t smem = (size_t)2 * 8 * nbt * XS + (size_t)CTA_ROWS * p.raw_rs;
+    if (smem > k->ctx->smem_optin) return -1;           // K range too long for one CTA's raw rows (tcgen05 path instead)
+    dim3 grid(tiles, 1, ks);
+    if (fmt == FMT_Q4_0)
+        return f32out ? launch_mma_nbt<FMT_Q4_0, float>(b, p, grid, smem, nbt) : launch_mma_nbt<FMT_Q4_0, __half>(b, p, grid, smem, nbt);
+    return f32out ? launch_mma_nbt<FMT_TQ2_0, float>(b, p, grid, smem, nbt) : launch_mma_nbt<FMT_TQ2_0, __half>(b, p, grid, smem, nbt);
+}

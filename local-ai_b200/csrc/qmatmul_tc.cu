@@ -347,6 +347,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     } else {
         // ============================ MMA issue (one warp) ============================
         bool dead = false;
+        const uint64_t adesc0 = make_desc(smem_u32(a_s), A_LBO, A_SBO), bdesc0 = make_desc(smem_u32(b_s), (uint32_t)B_LBO, 128u);
         for (int tile = 0; tile < total_tiles && !dead; tile++) {
             const int s = tile % SA, use = tile / SA;
             uint32_t ok = 1;
@@ -355,12 +356,15 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
             if (lane == 0) {
                 tc_fence_after();
-                const uint32_t abase = smem_u32(a_s + s * A_STAGE), bbase = smem_u32(b_s + (tile % SB) * B_STAGE);
+                // descriptors differ from tile to tile only in the start-address field (bits 0-13, address >> 4)
+                uint64_t ad = adesc0 + (uint64_t)((uint32_t)(s * A_STAGE) >> 4);
+                uint64_t bd = bdesc0 + (uint64_t)((uint32_t)((tile % SB) * B_STAGE) >> 4);
+                const uint64_t bstep = (uint64_t)((uint32_t)(2 * B_LBO) >> 4);
 #pragma unroll
                 for (int j = 0; j < KT / 16; j++) {
-                    const uint64_t ad = make_desc(abase + j * 2 * A_LBO, A_LBO, A_SBO);
-                    const uint64_t bd = make_desc(bbase + j * 2 * B_LBO, (uint32_t)B_LBO, 128u);
                     umma_f16(tmem_base, ad, bd, idesc, (tile > 0 || j > 0) ? 1u : 0u);
+                    ad += (uint64_t)((2 * A_LBO) >> 4);
+                    bd += bstep;
                 }
                 umma_commit(smem_u32(&mma_done[tile % MAX_BAR]));
             }
@@ -558,3 +562,4 @@ extern "C" __attribute__((visibility("default"))) int lc_debug_tc_profile(lc_ker
     cudaStreamSynchronize(k->ctx->stream);
     return cudaMemcpy(out8, k->dev_status + 2, 8 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? LC_OK : LC_ERR_CUDA;
 }
+

@@ -172,7 +172,21 @@ def test_matvec_is_linear_at_full_size(la, ctx, kernels):
     rel_close(yab, ya + yb, 1e-4, "linearity")
 
 
-# ---- tensor-core (tcgen05) path: m > 8 ----
+# ---- tensor-core paths: m > 8 (register-direct mma.sync up to m = 64, tcgen05 above or when forced) ----
+@pytest.fixture(params=["default", "tcgen05"])
+def tc_kernels(request, la, ctx, kernels, monkeypatch):
+    """The session's kernels object, or one created with LOCAL_CUDA_DECODE_MMA=0 (tcgen05 for every m > 8)."""
+    if request.param == "default":
+        kernels.decode_mma = True
+        yield kernels
+        return
+    monkeypatch.setenv("LOCAL_CUDA_DECODE_MMA", "0")
+    k2 = la.Kernels.new(ctx)
+    k2.decode_mma = False
+    yield k2
+    k2.close()
+
+
 TC_TOL_TQ2 = 1e-3   # TQ2_0 operands are exact in f16
 TC_TOL_Q4 = 1e-3    # vs the f16-weight semantic of the reference's CPU dequant (qat_recover.rs:93)
 TC_TOL_Q4_F32W = 6e-3  # vs the f32-weight oracle: Q4_0 weights are rounded once to f16 before the MMA
@@ -186,8 +200,10 @@ def device_status_ok(kernels):
 
 
 @pytest.mark.parametrize("m,k,n", [(70, 256, 96), (70, 512, 128), (16, 1536, 8192), (64, 1536, 8192), (64, 6144, 1536),
-                                   (200, 512, 64), (9, 256, 1), (33, 2048, 1536)])
-def test_matmul_nt_tq2_0_tensor_core(la, orc, ctx, kernels, m, k, n):
+                                   (200, 512, 64), (9, 256, 1), (33, 2048, 1536), (17, 768, 130), (64, 1536, 2560),
+                                   (40, 1536, 12288), (64, 256, 31)])
+def test_matmul_nt_tq2_0_tensor_core(la, orc, ctx, tc_kernels, m, k, n):
+    kernels = tc_kernels
     """kernels.rs:9551-9600 (m = 70 spans tiles) plus the benchmark shapes (config 2 at M = 16 and 64)."""
     raw, _ = refgen.tq2_0_payload(n, k, 0x2B19) if n * k <= 1 << 20 else (la.synth.tq2_0_weights(n, k, 5, ncodes=4), None)
     a = refgen.sin_matrix(m, k, 0.017, 0.6, np.cos) if n * k <= 1 << 20 else la.synth.normal_f16((m, k), 6)
@@ -197,8 +213,9 @@ def test_matmul_nt_tq2_0_tensor_core(la, orc, ctx, kernels, m, k, n):
 
 
 @pytest.mark.parametrize("m,k,n", [(70, 256, 128), (70, 64, 96), (16, 1536, 300), (64, 1536, 6144), (64, 768, 129),
-                                   (130, 128, 256)])
-def test_matmul_nt_q4_0_tensor_core(la, orc, ctx, kernels, m, k, n):
+                                   (130, 128, 256), (33, 96, 40), (9, 32, 7)])
+def test_matmul_nt_q4_0_tensor_core(la, orc, ctx, tc_kernels, m, k, n):
+    kernels = tc_kernels
     raw, _ = refgen.q4_0_payload(n, k, 0x51A7) if n * k <= 1 << 20 else (la.synth.q4_0_weights(n, k, 7), None)
     a = refgen.sin_matrix(m, k, 0.013, 0.7) if n * k <= 1 << 20 else la.synth.normal_f16((m, k), 8)
     """Operands reach the tensor core as f16((q-8)*d) — the value qat_recover::dequant_q4_0 produces
@@ -208,10 +225,11 @@ def test_matmul_nt_q4_0_tensor_core(la, orc, ctx, kernels, m, k, n):
     want16 = (a.astype(np.float64) @ w16.T).astype(np.float32)
     want32 = orc.matmul_nt(orc.Q4_0, a, raw, m, k, n)
     got = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_into", a, raw, m, k, n)
-    rel_close(got, want16 if k % 128 == 0 else want32, TC_TOL_Q4, f"tcgen05 q4_0 m={m} k={k} n={n} vs its exact reference")
+    f16w = k % 128 == 0 or (kernels.decode_mma and m <= 64)   # else the CUDA-core path (f32 weights) serves the shape
+    rel_close(got, want16 if f16w else want32, TC_TOL_Q4, f"tensor-core q4_0 m={m} k={k} n={n} vs its exact reference")
     rel_close(got, want32, TC_TOL_Q4_F32W, f"tcgen05 q4_0 m={m} k={k} n={n} vs f32 weights")
     got32 = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_f32out_into", a, raw, m, k, n, f32out=True)
-    rel_close(got32, want16, 1e-4 if k % 128 == 0 else TC_TOL_Q4_F32W, "tcgen05 q4_0 f32 out vs f16 weights")
+    rel_close(got32, want16, 1e-4 if f16w else TC_TOL_Q4_F32W, "tensor-core q4_0 f32 out vs f16 weights")
     rel_close(got32, want32, TC_TOL_Q4_F32W, "tcgen05 q4_0 f32 out vs f32 weights")
     device_status_ok(kernels)
 
@@ -230,7 +248,8 @@ def test_tensor_core_and_cuda_core_paths_agree(la, orc, ctx, kernels, monkeypatc
     assert np.max(np.abs(tc - cc)) <= 2e-3 * max(1.0, float(np.abs(cc).max()))
 
 
-def test_split_k_is_deterministic_and_lane_isolated(la, orc, ctx, kernels):
+def test_split_k_is_deterministic_and_lane_isolated(la, orc, ctx, tc_kernels):
+    kernels = tc_kernels
     """Small-n projections run split-K on the tensor-core path (deterministic last-arriver reduction):
     repeated launches and duplicate batch rows must agree bit for bit."""
     m, k, n = 64, 6144, 1536   # the down projection: 12 row tiles x 12 splits
