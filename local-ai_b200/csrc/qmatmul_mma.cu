@@ -13,7 +13,9 @@
 //     cp.async;
 //   * each warp walks its rows' blocks: 2-byte pieces of code bytes -> f16 weights in registers, directly in the
 //     layout of the m16n8k16 A fragment (thread t of a quad owns bytes 2t, 2t+1 of every 8-byte group, which are
-//     the k values 2t, 2t+1 the fragment wants), B fragments by ldmatrix, f32 accumulators in registers.
+//     the k values 2t, 2t+1 the fragment wants; for TQ2_0 the four values a code can take, (q - 1) d, sit in two
+//     registers as a byte table and one prmt assembles two weights), B fragments by ldmatrix, f32 accumulators
+//     in registers.
 // Weights take the MMA's M dimension, the batch its N dimension.  When K is split (grid.z > 1) the CTAs of a
 // tile form a thread-block cluster: each stages its partial tile in its own shared memory and, after a cluster
 // barrier, every CTA adds one slice of the tile over all splits in split order through distributed shared
@@ -167,12 +169,16 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
         const int cb0 = ch * CHB, cblk = min(CHB, nblk - cb0);
         if (FMT == FMT_TQ2_0) {
             // one block: element 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j
-            const __half2 c1025 = __float2half2_rn(1025.0f);
-            __half2 d2[2];
+            // The four weights a code can mean, (q - 1) d, as a byte table for prmt: lut_lo / lut_hi hold the low /
+            // high bytes of {-d, 0, d, 2d}; a selector nibble pair (q, q + 4) then assembles one f16.
+            uint32_t lut_lo[2], lut_hi[2];
 #pragma unroll
             for (int i = 0; i < 2; i++) {
-                const __half d = *reinterpret_cast<const __half *>(rbase[i] + cb0 * BB + 64);
-                d2[i] = __half2half2(rvalid[i] ? d : __float2half(0.0f));
+                const __half d = rvalid[i] ? *reinterpret_cast<const __half *>(rbase[i] + cb0 * BB + 64) : __float2half(0.0f);
+                const uint32_t p01 = (uint32_t)__half_as_ushort(__hneg(d));                       // {-d, 0}
+                const uint32_t p23 = (uint32_t)__half_as_ushort(d) | ((uint32_t)__half_as_ushort(__hadd(d, d)) << 16);
+                lut_lo[i] = __byte_perm(p01, p23, 0x6420);
+                lut_hi[i] = __byte_perm(p01, p23, 0x7531);
             }
 #pragma unroll
             for (int h = 0; h < 2; h++) {
@@ -191,9 +197,9 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
                         uint32_t a[4];
 #pragma unroll
                         for (int i = 0; i < 2; i++) {
-                            const uint32_t codes = (wq[i][qp] >> (2 * l)) & 0x03030303u;
-                            a[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1025), d2[i]));
-                            a[i + 2] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1025), d2[i]));
+                            const uint32_t sel = ((wq[i][qp] >> (2 * l)) & 0x03030303u) * 0x11u + 0x40404040u;
+                            a[i] = __byte_perm(lut_lo[i], lut_hi[i], sel);            // k-fragment 2t, 2t+1
+                            a[i + 2] = __byte_perm(lut_lo[i], lut_hi[i], sel >> 16);  // k-fragment 2t+8, 2t+9
                         }
                         const uint32_t xk = xb + (uint32_t)((128 * h + 32 * l + 16 * qp) * 2);
 #pragma unroll
@@ -353,11 +359,12 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
         p.tile_end[g] = tiles;
     }
     const int nbt = m <= 16 ? 2 : (m <= 32 ? 4 : 8);
-    // Split K (at most 8 ways: one cluster per tile) until there are about two CTAs per SM; whole 256-k chunks per
+    // Split K (at most 8 ways: one cluster per tile) while the grid stays within 1.5 CTAs per SM (measured optimum:
+    // more splits cost more in the exchange than they gain in parallelism); whole 256-k chunks per
     // split, and no more raw bytes per CTA than fit beside the activation buffers.
     const int chb = CHUNK_K / be;                       // blocks per 256 k
     const int nchunk = (p.nb + chb - 1) / chb;
-    int ks = (2 * k->ctx->sm_count + tiles - 1) / tiles;
+    int ks = (3 * k->ctx->sm_count / 2) / tiles;
     if (ks > MAX_KS) ks = MAX_KS;
     if (ks > nchunk) ks = nchunk;
     if (ks < 1) ks = 1;
