@@ -181,6 +181,87 @@ __global__ void argmax_rows_kernel(const float *__restrict__ v, uint32_t *__rest
     }
 }
 
+// The same for long rows (a vocabulary of logits): grid = (chunks, rows).  Every CTA scans one chunk of one row and
+// stores its (value, index) candidate; the last CTA of a row to arrive (a counter that it resets) merges the
+// candidates in chunk order, so ties still go to the lowest index.
+__global__ void argmax_rows_chunked_kernel(const float *__restrict__ v, uint32_t *__restrict__ out, unsigned cols,
+                                           unsigned chunk, float2 *__restrict__ cand, unsigned int *__restrict__ counters) {
+    lc_pdl_trigger();
+    lc_pdl_wait();
+    __shared__ float bv_s[32];
+    __shared__ unsigned bi_s[32];
+    __shared__ unsigned int is_last;
+    const unsigned r = blockIdx.y, c0 = blockIdx.x * chunk, c1 = min(cols, c0 + chunk);
+    const float *row = v + (size_t)r * cols;
+    float bv = -INFINITY;
+    unsigned bi = 0xffffffffu;
+    auto better = [](float a, unsigned ai, float b, unsigned bi2) { return a > b || (a == b && ai < bi2); };
+    if ((((size_t)row & 15) == 0) && (c0 & 3) == 0) {
+        const unsigned n4 = (c1 - c0) / 4;
+        const float4 *p4 = reinterpret_cast<const float4 *>(row + c0);
+        for (unsigned i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 x = __ldcs(p4 + i);
+            const unsigned base = c0 + 4 * i;
+            if (x.x > bv) { bv = x.x; bi = base; }
+            if (x.y > bv) { bv = x.y; bi = base + 1; }
+            if (x.z > bv) { bv = x.z; bi = base + 2; }
+            if (x.w > bv) { bv = x.w; bi = base + 3; }
+        }
+        for (unsigned i = c0 + 4 * n4 + threadIdx.x; i < c1; i += blockDim.x) {
+            const float x = row[i];
+            if (better(x, i, bv, bi)) { bv = x; bi = i; }
+        }
+    } else {
+        for (unsigned i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+            const float x = row[i];
+            if (x > bv) { bv = x; bi = i; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { bv_s[warp] = bv; bi_s[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < nw ? bv_s[lane] : -INFINITY;
+        bi = lane < nw ? bi_s[lane] : 0xffffffffu;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            cand[(size_t)r * gridDim.x + blockIdx.x] = make_float2(bv, __uint_as_float(bi));
+            __threadfence();
+            const unsigned int prev = atomicAdd(&counters[r], 1u);
+            is_last = prev == gridDim.x - 1 ? 1u : 0u;
+            if (is_last) counters[r] = 0u;
+        }
+    }
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    bv = -INFINITY;
+    bi = 0xffffffffu;
+    for (unsigned c = lane; c < gridDim.x; c += 32) {
+        const float2 q = __ldcg(cand + (size_t)r * gridDim.x + c);
+        const unsigned qi = __float_as_uint(q.y);
+        if (better(q.x, qi, bv, bi)) { bv = q.x; bi = qi; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[r] = bi == 0xffffffffu ? 0u : bi;
+}
+
 // Fused per-head RMSNorm + NEOX RoPE in place (shaders/qk_norm.metal:70-144 qk_norm_rope): identical to
 // qk_norm followed by rope_batch_decode, including the f16 rounding between the two.
 // grid = rows * heads, block = head_dim / 2; thread i owns the pair (i, i + head_dim/2).
@@ -465,6 +546,19 @@ int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc
     LC_REQUIRE(values->bytes >= (size_t)rows * cols * 4 && out_index->bytes >= (size_t)rows * 4,
                "argmax_rows_f32: buffers too small");
     if (rows == 0) return LC_OK;
+    if (cols >= 32768 && rows <= 65535) {
+        // long rows: enough chunks that every SM streams a share of the logits
+        unsigned chunks = (4u * (unsigned)k->ctx->sm_count + rows - 1) / rows;
+        if (chunks > 64) chunks = 64;
+        unsigned chunk = ((cols + chunks - 1) / chunks + 1023u) & ~1023u;
+        chunks = (cols + chunk - 1) / chunk;
+        int st = lc_reserve_scratch(k, b, (size_t)rows * chunks * sizeof(float2), rows);
+        if (st != LC_OK) return st;
+        LC_LAUNCH_CHECKED(lc_launch(argmax_rows_chunked_kernel, dim3(chunks, rows), dim3(256), 0, b, (const float *)values->dptr,
+                                    (uint32_t *)out_index->dptr, cols, chunk, (float2 *)k->scratch, k->counters));
+        b->dispatch_count++;
+        return LC_OK;
+    }
     LC_LAUNCH_CHECKED(lc_launch(argmax_rows_kernel, dim3(rows), dim3(1024), 0, b, (const float *)values->dptr, (uint32_t *)out_index->dptr, cols));
     LC_CHECK_LAUNCH("argmax_rows_f32");
     b->dispatch_count++;

@@ -222,3 +222,18 @@ def test_qkv_post_fused_equals_separate_launches(la, orc, ctx, kernels):
     want_q = orc.rope(orc.rms_norm(q, qw, hd, n_lanes * n_q, EPS), positions, theta, hd, n_q, n_lanes, 1.0)
     rel_close(pools[1][0], want_q.astype(np.float32), 4e-3, "fused q norm+rope")
     rel_close(pools[1][0], pools[0][0].astype(np.float32), 2e-3, "fused vs separate q")
+
+
+@pytest.mark.parametrize("rows,n", [(3, 40001), (64, 65536), (5, 1000), (1, 32768)])
+def test_argmax_rows_shapes_and_repeat(la, orc, ctx, kernels, rows, n):
+    """Long rows take the chunked two-stage kernel (odd lengths leave rows unaligned); repeated launches must agree
+    (the per-row arrival counters reset themselves)."""
+    v = la.synth.normal(77, rows * n).astype(np.float32).reshape(rows, n)
+    v[0, n - 1] = v[0, n // 2] = 50.0
+    oi = Guarded(la, ctx, rows * 4)
+    dv = dev(la, ctx, v)
+    for _ in range(3):
+        b = la.CommandBatch.new(ctx)
+        kernels.argmax_rows_f32_into(b, dv, oi.view, rows, n)
+        b.commit_and_wait()
+        assert oi.read(np.uint32).tolist() == [orc.argmax(v[r]) for r in range(rows)]
