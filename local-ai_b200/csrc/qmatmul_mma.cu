@@ -333,6 +333,169 @@ int launch_mma_nbt(lc_batch *b, const MmaParams &p, dim3 grid, size_t smem, int 
     }
 }
 
+
+// ---- wide matrices (the vocabulary projection): Q4_0, 32 < m <= 64, no K split -------------------------------------
+// With 128-row tiles every CTA streams the whole activation matrix from L2 once per tile, which for a 262144-row
+// table is 2048 x 196 KB.  Here a CTA owns 512 rows (16 warps x 32 rows), so the activations are read a quarter as
+// often, is persistent over tiles, and streams raw weights and activations together in 128-k chunks through a
+// three-stage cp.async ring (one __syncthreads per chunk).
+constexpr int W_NW = 16, W_NT = W_NW * 32, W_ROWS = W_NW * 32;
+constexpr int W_CK = 128;                        // k per chunk: 4 Q4_0 blocks
+constexpr int W_RAW_RS = 112;                    // 72 bytes of blocks + up to 15 of skew, odd multiple of 16
+constexpr int W_XS = W_CK * 2 + 16;
+constexpr int W_STAGE = W_ROWS * W_RAW_RS + 64 * W_XS;
+constexpr int W_STAGES = 3;
+
+struct WideParams {
+    const uint8_t *w;
+    void *out;
+    const __half *x;
+    int n, m, K, nb, tiles;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int BB = 18, NBT = 8;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    lc_pdl_trigger();
+    const size_t rb = (size_t)p.nb * BB, w_bytes = rb * (size_t)p.n;
+    const int nchunks = p.K / W_CK;
+    const int my_tiles = ((int)p.tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total = my_tiles * nchunks;
+
+    // chunk `it` of this CTA's sequence: tile blockIdx.x + (it / nchunks) gridDim.x, k chunk it % nchunks
+    auto load_raw = [&](int it) {
+        const int tile = (int)blockIdx.x + (it / nchunks) * (int)gridDim.x, ch = it % nchunks;
+        uint8_t *st = smem + (it % W_STAGES) * W_STAGE;
+        const int row = tile * W_ROWS + tid;        // one row per thread
+        if (row < p.n) {
+            const size_t g0 = (size_t)row * rb + (size_t)ch * 4 * BB, a0 = g0 & ~(size_t)15;
+            const int npieces = (int)((g0 + 4 * BB - a0 + 15) >> 4);
+            for (int pc = 0; pc < npieces; pc++) {
+                const size_t ga = a0 + ((size_t)pc << 4);
+                uint8_t *dst = st + tid * W_RAW_RS + (pc << 4);
+                if (ga + 16 <= w_bytes) {
+                    cp_async16(smem_u32(dst), p.w + ga);
+                } else {
+                    for (int b = 0; b < 16; b++) dst[b] = (ga + b < w_bytes) ? p.w[ga + b] : 0;
+                }
+            }
+        }
+    };
+    auto load_x = [&](int it) {
+        const int ch = it % nchunks;
+        uint8_t *xs = smem + (it % W_STAGES) * W_STAGE + W_ROWS * W_RAW_RS;
+        for (int i = tid; i < 64 * (W_CK / 8); i += W_NT) {
+            const int r = i / (W_CK / 8), pc = i - r * (W_CK / 8);
+            const bool ok = r < p.m;
+            cp_async16(smem_u32(xs + r * W_XS + pc * 16),
+                       ok ? (const void *)(p.x + (size_t)r * p.K + ch * W_CK + pc * 8) : (const void *)p.x, ok ? 16u : 0u);
+        }
+    };
+    // the weights of the first two chunks do not depend on the previous kernel
+    if (total > 0) load_raw(0);
+    if (total > 1) load_raw(1);
+    lc_pdl_wait();
+    if (total > 0) load_x(0);
+    cp_async_commit();
+    if (total > 1) load_x(1);
+    cp_async_commit();
+
+    float c[2][NBT][4];
+#pragma unroll
+    for (int f = 0; f < 2; f++)
+#pragma unroll
+        for (int j = 0; j < NBT; j++) c[f][j][0] = c[f][j][1] = c[f][j][2] = c[f][j][3] = 0.f;
+    const uint32_t xl = (uint32_t)((8 * (lane >> 4) + (lane & 7)) * W_XS + ((lane >> 3) & 1) * 16);
+    const __half2 c1032 = __float2half2_rn(1032.0f);
+    OutT *out = reinterpret_cast<OutT *>(p.out);
+
+    for (int it = 0; it < total; it++) {
+        cp_async_wait<1>();
+        __syncthreads();             // chunk `it` has landed everywhere, and everyone is done with chunk it - 1
+        if (it + 2 < total) {
+            load_raw(it + 2);
+            load_x(it + 2);
+        }
+        cp_async_commit();
+        const int tile = (int)blockIdx.x + (it / nchunks) * (int)gridDim.x, ch = it % nchunks;
+        const uint8_t *st = smem + (it % W_STAGES) * W_STAGE;
+        const uint32_t xb = smem_u32(st + W_ROWS * W_RAW_RS) + xl;
+        const uint8_t *rbase[4];
+        bool rvalid[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = warp * 32 + g + 8 * i, row = tile * W_ROWS + r;
+            const size_t g0 = (size_t)row * rb + (size_t)ch * 4 * BB;
+            rbase[i] = st + r * W_RAW_RS + (int)(g0 & 15);
+            rvalid[i] = row < p.n;
+        }
+#pragma unroll
+        for (int bi = 0; bi < 4; bi++) {
+            __half2 d2[4];
+            uint32_t wq[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint8_t *bp = rbase[i] + bi * BB;
+                const __half d = *reinterpret_cast<const __half *>(bp);
+                d2[i] = __half2half2(rvalid[i] ? d : __float2half(0.0f));
+                wq[i] = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
+            }
+#pragma unroll
+            for (int part = 0; part < 2; part++) {
+                uint32_t a[2][4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t codes = (wq[i] >> (4 * part)) & 0x0F0F0F0Fu;
+                    a[i >> 1][i & 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032), d2[i]));
+                    a[i >> 1][(i & 1) + 2] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032), d2[i]));
+                }
+                const uint32_t xk = xb + (uint32_t)((32 * bi + 16 * part) * 2);
+#pragma unroll
+                for (int j = 0; j < NBT; j += 2) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, xk + (uint32_t)(8 * j * W_XS));
+                    mma16816(c[0][j], a[0], b[0], b[1]);
+                    mma16816(c[1][j], a[1], b[0], b[1]);
+                    mma16816(c[0][j + 1], a[0], b[2], b[3]);
+                    mma16816(c[1][j + 1], a[1], b[2], b[3]);
+                }
+            }
+        }
+        if (ch == nchunks - 1) {
+            // c[f][j][e]: weight row 32 warp + 16 f + g + 8 (e >> 1) of the tile, batch row 8 j + 2 t + (e & 1)
+#pragma unroll
+            for (int f = 0; f < 2; f++)
+#pragma unroll
+                for (int j = 0; j < NBT; j++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int row = tile * W_ROWS + warp * 32 + 16 * f + g + 8 * (e >> 1), col = 8 * j + 2 * t + (e & 1);
+                        if (row < p.n && col < p.m) store_c(out + (size_t)col * p.n + row, c[f][j][e]);
+                        c[f][j][e] = 0.f;
+                    }
+                }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <typename OutT>
+int launch_wide(lc_kernels *k, lc_batch *b, const WideParams &p) {
+    auto kern = qgemm_mma_wide_kernel<OutT>;
+    const size_t smem = (size_t)W_STAGES * W_STAGE;
+    static bool configured = false;
+    if (!configured) {
+        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    const int grid = p.tiles < k->ctx->sm_count ? p.tiles : k->ctx->sm_count;
+    LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(W_NT), smem, b, p));
+    b->dispatch_count++;
+    return LC_OK;
+}
+
 }  // namespace
 
 // Grouped launch: `ng` weight matrices [ns[g], kk] sharing the activations `input` [m, kk], 8 < m <= 64.
@@ -357,6 +520,19 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
         p.n[g] = (int)ns[gi];
         if (g < ng) tiles += ((int)ns[g] + CTA_ROWS - 1) / CTA_ROWS;
         p.tile_end[g] = tiles;
+    }
+    if (fmt == FMT_Q4_0 && ng == 1 && m > 32 && kk % W_CK == 0 && ns[0] >= (uint32_t)(W_ROWS * k->ctx->sm_count) &&
+        (size_t)W_STAGES * W_STAGE <= k->ctx->smem_optin) {
+        WideParams wp;
+        wp.w = (const uint8_t *)weights[0]->dptr;
+        wp.out = outputs[0]->dptr;
+        wp.x = (const __half *)input->dptr;
+        wp.n = (int)ns[0];
+        wp.m = (int)m;
+        wp.K = (int)kk;
+        wp.nb = (int)(kk / 32);
+        wp.tiles = (int)((ns[0] + W_ROWS - 1) / W_ROWS);
+        return f32out ? launch_wide<float>(k, b, wp) : launch_wide<__half>(k, b, wp);
     }
     const int nbt = m <= 16 ? 2 : (m <= 32 ? 4 : 8);
     // Split K (at most 8 ways: one cluster per tile) while the grid stays within 1.5 CTAs per SM (measured optimum:

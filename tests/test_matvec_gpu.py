@@ -262,3 +262,17 @@ def test_split_k_is_deterministic_and_lane_isolated(la, orc, ctx, tc_kernels):
     assert np.array_equal(r1[5], r1[3])
     rel_close(r1, orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n), TC_TOL_TQ2, "split-K down projection")
     device_status_ok(kernels)
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 256, 76000), (40, 384, 75800)])
+def test_matmul_nt_q4_0_wide_matrix(la, orc, ctx, kernels, m, k, n):
+    """Vocabulary-sized Q4_0 projections at decode batch sizes take the persistent 512-row kernel (ragged last tile,
+    several tiles per CTA); results must equal the f16-weight product."""
+    raw = la.synth.q4_0_weights(n, k, 31)
+    a = la.synth.normal_f16((m, k), 32)
+    w16 = orc.dequant(orc.Q4_0, raw, n * k).astype(np.float32).reshape(n, k)
+    want16 = (a.astype(np.float32) @ w16.T)
+    got32 = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_f32out_into", a, raw, m, k, n, f32out=True)
+    rel_close(got32, want16, 2e-4, "wide q4_0 f32 out vs f16 weights")
+    got = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_into", a, raw, m, k, n)
+    rel_close(got, want16, TC_TOL_Q4, "wide q4_0 f16 out")
