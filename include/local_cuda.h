@@ -365,6 +365,12 @@ LC_API int lc_kv_write_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *k_
                                     uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes,
                                     uint32_t ring_capacity, float eps, float rope_theta,
                                     float partial_rotary_factor);
+/* The GeGLU half of the feed-forward block, gelu_mul(matmul_nt_tq2_0(x, W_gate), matmul_nt_tq2_0(x, W_up))
+ * (local-engine/src/layer.rs:825-838), as one launch for decode batches (8 < m <= 64); other m run the two
+ * projections into gate_tmp / up_tmp [m, n] and lc_gelu_mul_into.  `output` may alias `gate_tmp`. */
+LC_API int lc_matmul_nt_tq2_0_geglu_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *w_gate,
+                                         const lc_buf *w_up, lc_buf *gate_tmp, lc_buf *up_tmp, lc_buf *output,
+                                         uint32_t m, uint32_t kk, uint32_t n);
 /* lc_qk_norm_rope_batch_decode_into on the queries and lc_kv_write_batched_into in one launch: everything
  * between the Q/K/V projections and attention of a decode step (layer.rs:757-790). */
 LC_API int lc_qkv_post_batched_into(lc_kernels *k, lc_batch *b, lc_buf *q, const lc_buf *q_norm_weight,

@@ -234,13 +234,7 @@ int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *toke
         STEP(lc_matmul_nt_tq2_0_into(k, b, m->attn, L.wo, m->ffn, n, qd, H));
         // resid = rms_norm(ffn, post_attn) + x ; normed = rms_norm(resid, ffn_norm)
         STEP(lc_rms_norm_add_norm_into(k, b, m->ffn, L.post_attn_norm, x, m->resid, L.ffn_norm, m->normed, H, n, c.rms_eps));
-        {
-            const lc_buf *ws[2] = {L.wgate, L.wup};
-            lc_buf *os[2] = {m->gate, m->up};
-            const uint32_t ns[2] = {I, I};
-            STEP(lc_matmul_nt_tq2_0_grouped(k, b, m->normed, 2, ws, os, ns, n, H));
-        }
-        STEP(lc_gelu_mul_into(k, b, m->gate, m->up, m->gate, n * I));
+        STEP(lc_matmul_nt_tq2_0_geglu_into(k, b, m->normed, L.wgate, L.wup, m->gate, m->up, m->gate, n, H, I));
         STEP(lc_matmul_nt_tq2_0_into(k, b, m->gate, L.wdown, m->ffn, n, I, H));
         // x' = rms_norm(ffn, post_ffn) + resid ; normed = rms_norm(x', next layer's attention norm | final norm)
         const lc_buf *next_norm = li + 1 < nl ? m->layers[li + 1].attn_norm : m->final_norm;

@@ -9,6 +9,7 @@
 // tensor-core path for larger m (qmatmul_tc.cu).  LOCAL_AI_MMA=0 forces the
 // CUDA-core path for every m, as it forces the non-MMA kernels in the reference;
 // LOCAL_CUDA_DECODE_MMA=0 sends 8 < m <= 64 to the tcgen05 path as well.
+#include <stdlib.h>
 #include "lc_internal.h"
 
 int lc_qgemm_cuda_core(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
@@ -69,7 +70,35 @@ int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, 
     return LC_OK;
 }
 
+int lc_qgemm_mma_geglu(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *w_gate, const lc_buf *w_up,
+                       lc_buf *output, uint32_t m, uint32_t kk, uint32_t n);
+
 extern "C" {
+
+// The GeGLU half of the feed-forward block, gelu_tanh(x W_gate^T) * (x W_up^T) (local-engine/src/layer.rs:825-838):
+// one launch on the decode path (8 < m <= 64), else the two projections into `gate_tmp` / `up_tmp` followed by
+// gelu_mul.  `output` may alias `gate_tmp`.
+int lc_matmul_nt_tq2_0_geglu_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *w_gate,
+                                  const lc_buf *w_up, lc_buf *gate_tmp, lc_buf *up_tmp, lc_buf *output, uint32_t m,
+                                  uint32_t kk, uint32_t n) {
+    if (!gate_tmp || !up_tmp) return lc_fail(LC_ERR_INVALID_ARGUMENT, "matmul_nt_tq2_0_geglu: NULL argument");
+    int st = lc_check_qargs(1, "matmul_nt_tq2_0_geglu", k, b, w_gate, input, output, m, kk, n, 2);
+    if (st == LC_OK) st = lc_check_qargs(1, "matmul_nt_tq2_0_geglu", k, b, w_up, input, up_tmp, m, kk, n, 2);
+    if (st == LC_OK) st = lc_check_qargs(1, "matmul_nt_tq2_0_geglu", k, b, w_gate, input, gate_tmp, m, kk, n, 2);
+    if (st != LC_OK) return st;
+    if (n == 0 || m == 0) return LC_OK;
+    static const bool fused_ok = []() { const char *e = getenv("LOCAL_CUDA_GEGLU_FUSED"); return !(e && e[0] == '0'); }();
+    if (fused_ok && k->mma && k->decode_mma && m > 8 && m <= 64) {
+        st = lc_qgemm_mma_geglu(k, b, input, w_gate, w_up, output, m, kk, n);
+        if (st >= 0) return st;
+    }
+    const lc_buf *ws[2] = {w_gate, w_up};
+    lc_buf *os[2] = {gate_tmp, up_tmp};
+    const uint32_t ns[2] = {n, n};
+    st = lc_matmul_nt_tq2_0_grouped(k, b, input, 2, ws, os, ns, m, kk);
+    if (st != LC_OK) return st;
+    return lc_gelu_mul_into(k, b, gate_tmp, up_tmp, output, m * n);
+}
 
 int lc_matmul_nt_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
                            lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {

@@ -47,6 +47,7 @@ struct MmaParams {
     int m, K, nb;          // nb = blocks per weight row
     int ks, bps;           // split-K: grid.z = cluster size = ks, bps = blocks per split
     int raw_rs;            // bytes reserved per row of raw blocks
+    int geglu;             // 1: w[0] = gate, w[1] = up, out[0] = gelu(gate) * up (see lc_qgemm_mma_geglu)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,7 +99,10 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
     lc_pdl_trigger();
     int grp = 0;
     while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
-    const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * CTA_ROWS;
+    // GeGLU mode: a CTA owns 64 rows of the gate matrix (warps 0-3) and the same 64 rows of the up matrix (warps 4-7)
+    if (p.geglu) grp = warp >> 2;
+    const int n0 = p.geglu ? (int)blockIdx.x * (CTA_ROWS / 2) - (warp >> 2) * (CTA_ROWS / 2)
+                           : ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * CTA_ROWS;
     const int n_rows = p.n[grp];
     const uint8_t *wmat = p.w[grp];
     const size_t rb = (size_t)p.nb * BB, w_bytes = rb * (size_t)n_rows;
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
     }
 
     // ---- 4. results.  c[j][e]: weight row 16 warp + g + 8 (e >> 1), batch row 8 j + 2 t + (e & 1) ----
-    OutT *out = reinterpret_cast<OutT *>(p.out[grp]);
+    OutT *out = reinterpret_cast<OutT *>(p.out[p.geglu ? 0 : grp]);
     auto store_tile = [&](const float4 v, int w, int ln, int j) {
         const float e4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -260,22 +264,52 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
             if (row < n_rows && col < p.m) store_c(out + (size_t)col * n_rows + row, e4[e]);
         }
     };
-    if (p.ks == 1) {
+    // GeGLU: gate and up are rounded to f16 as the separate projections would store them, then
+    // gelu_tanh(gate) * up exactly as the element-wise kernel computes it (gelu.metal, layer.rs:825-838)
+    auto geglu = [](float gate, float up) {
+        const float x = __half2float(__float2half_rn(gate)), u = __half2float(__float2half_rn(up));
+        float inner = 0.7978845608f * (x + 0.044715f * (x * x * x));
+        inner = fminf(fmaxf(inner, -10.0f), 10.0f);
+        return 0.5f * x * (1.0f + tanhf(inner)) * u;
+    };
+    auto store_geglu = [&](const float4 gt, const float4 up, int w, int ln, int j) {   // w = 0..3: gate warp
+        const int row0 = (int)blockIdx.x * (CTA_ROWS / 2) + w * WROWS + (ln >> 2), col0 = 8 * j + 2 * (ln & 3);
+        const float g4[4] = {gt.x, gt.y, gt.z, gt.w}, u4[4] = {up.x, up.y, up.z, up.w};
 #pragma unroll
-        for (int j = 0; j < NBT; j++) store_tile(make_float4(c[j][0], c[j][1], c[j][2], c[j][3]), warp, lane, j);
+        for (int e = 0; e < 4; e++) {
+            const int row = row0 + 8 * (e >> 1), col = col0 + (e & 1);
+            if (row < n_rows && col < p.m) store_c(out + (size_t)col * n_rows + row, geglu(g4[e], u4[e]));
+        }
+    };
+    float4 *red = reinterpret_cast<float4 *>(x_s);           // [NBT][NT]
+    if (p.ks == 1) {
+        if (!p.geglu) {
+#pragma unroll
+            for (int j = 0; j < NBT; j++) store_tile(make_float4(c[j][0], c[j][1], c[j][2], c[j][3]), warp, lane, j);
+            return;
+        }
+        cp_async_wait<0>();
+        if (warp >= 4) {
+#pragma unroll
+            for (int j = 0; j < NBT; j++) red[j * NT + tid] = make_float4(c[j][0], c[j][1], c[j][2], c[j][3]);
+        }
+        __syncthreads();
+        if (warp < 4) {
+#pragma unroll
+            for (int j = 0; j < NBT; j++)
+                store_geglu(make_float4(c[j][0], c[j][1], c[j][2], c[j][3]), red[j * NT + tid + 128], warp, lane, j);
+        }
         return;
     }
     // Split K: the ks CTAs of this tile are one cluster.  Partial tiles are exchanged through shared memory.
     cp_async_wait<0>();
-    float4 *red = reinterpret_cast<float4 *>(x_s);           // [NBT][NT]
 #pragma unroll
     for (int j = 0; j < NBT; j++) red[j * NT + tid] = make_float4(c[j][0], c[j][1], c[j][2], c[j][3]);
     cluster_sync();
     // items (j, source warp) are dealt round-robin to the CTAs of the cluster; a warp adds the ks partials of an
     // item in split order and stores it
     const int rank = (int)blockIdx.z;
-    for (int item = rank + p.ks * warp; item < NBT * NW; item += p.ks * NW) {
-        const int j = item / NW, w = item - j * NW;
+    auto gather = [&](int j, int w) {
         const uint32_t la = smem_u32(red + j * NT + w * 32 + lane);
         float4 v[MAX_KS];
 #pragma unroll
@@ -285,7 +319,19 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
         for (int sp = 0; sp < MAX_KS; sp++) {
             acc.x += v[sp].x; acc.y += v[sp].y; acc.z += v[sp].z; acc.w += v[sp].w;
         }
-        store_tile(acc, w, lane, j);
+        return acc;
+    };
+    if (!p.geglu) {
+        for (int item = rank + p.ks * warp; item < NBT * NW; item += p.ks * NW) {
+            const int j = item / NW, w = item - j * NW;
+            store_tile(gather(j, w), w, lane, j);
+        }
+    } else {
+        for (int item = rank + p.ks * warp; item < NBT * 4; item += p.ks * NW) {
+            const int j = item / 4, w = item - j * 4;
+            const float4 gt = gather(j, w), up = gather(j, w + 4);
+            store_geglu(gt, up, w, lane, j);
+        }
     }
     cluster_sync();   // no CTA leaves while a peer may still read its shared memory
 }
@@ -501,9 +547,9 @@ int launch_wide(lc_kernels *k, lc_batch *b, const WideParams &p) {
 // Grouped launch: `ng` weight matrices [ns[g], kk] sharing the activations `input` [m, kk], 8 < m <= 64.
 // Returns LC_OK after a launch, a positive status on error, or -1 when the shape is outside what this kernel
 // covers (the caller then uses another path).
-int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
-                         const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
-                         uint32_t kk) {
+static int qgemm_mma_launch(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
+                            const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
+                            uint32_t kk, bool geglu) {
     const int be = fmt == FMT_Q4_0 ? 32 : 256, bb = fmt == FMT_Q4_0 ? 18 : 66;
     if (m > 64 || ng < 1 || ng > MAX_GROUPS || kk % be != 0 || !lc_aligned(input->dptr, 16)) return -1;
     MmaParams p;
@@ -521,7 +567,7 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
         if (g < ng) tiles += ((int)ns[g] + CTA_ROWS - 1) / CTA_ROWS;
         p.tile_end[g] = tiles;
     }
-    if (fmt == FMT_Q4_0 && ng == 1 && m > 32 && kk % W_CK == 0 && ns[0] >= (uint32_t)(W_ROWS * k->ctx->sm_count) &&
+    if (!geglu && fmt == FMT_Q4_0 && ng == 1 && m > 32 && kk % W_CK == 0 && ns[0] >= (uint32_t)(W_ROWS * k->ctx->sm_count) &&
         (size_t)W_STAGES * W_STAGE <= k->ctx->smem_optin) {
         WideParams wp;
         wp.w = (const uint8_t *)weights[0]->dptr;
@@ -534,6 +580,8 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
         wp.tiles = (int)((ns[0] + W_ROWS - 1) / W_ROWS);
         return f32out ? launch_wide<float>(k, b, wp) : launch_wide<__half>(k, b, wp);
     }
+    p.geglu = geglu ? 1 : 0;
+    if (geglu) tiles = ((int)ns[0] + CTA_ROWS / 2 - 1) / (CTA_ROWS / 2);
     const int nbt = m <= 16 ? 2 : (m <= 32 ? 4 : 8);
     // Split K (at most 8 ways: one cluster per tile) while the grid stays within 1.5 CTAs per SM (measured optimum:
     // more splits cost more in the exchange than they gain in parallelism); whole 256-k chunks per
@@ -556,4 +604,19 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
     if (fmt == FMT_Q4_0)
         return f32out ? launch_mma_nbt<FMT_Q4_0, float>(b, p, grid, smem, nbt) : launch_mma_nbt<FMT_Q4_0, __half>(b, p, grid, smem, nbt);
     return f32out ? launch_mma_nbt<FMT_TQ2_0, float>(b, p, grid, smem, nbt) : launch_mma_nbt<FMT_TQ2_0, __half>(b, p, grid, smem, nbt);
+}
+
+int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
+                         const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
+                         uint32_t kk) {
+    return qgemm_mma_launch(fmt, f32out, k, b, input, ng, weights, outputs, ns, m, kk, false);
+}
+
+// out[m, n] = gelu_tanh(x W_gate^T) * (x W_up^T) in one launch (TQ2_0, f16 out), 8 < m <= 64; -1 when not covered.
+int lc_qgemm_mma_geglu(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *w_gate, const lc_buf *w_up,
+                       lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    const lc_buf *ws[2] = {w_gate, w_up};
+    lc_buf *os[2] = {output, output};
+    const uint32_t ns[2] = {n, n};
+    return qgemm_mma_launch(FMT_TQ2_0, false, k, b, input, 2, ws, os, ns, m, kk, true);
 }

@@ -276,3 +276,31 @@ def test_matmul_nt_q4_0_wide_matrix(la, orc, ctx, kernels, m, k, n):
     rel_close(got32, want16, 2e-4, "wide q4_0 f32 out vs f16 weights")
     got = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_into", a, raw, m, k, n)
     rel_close(got, want16, TC_TOL_Q4, "wide q4_0 f16 out")
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 1536, 6144), (33, 512, 200), (16, 256, 64), (64, 2048, 1000), (4, 512, 256), (70, 512, 256)])
+def test_geglu_fused_equals_separate_launches(la, orc, ctx, kernels, m, k, n):
+    """gelu_tanh(x Wg^T) * (x Wu^T): one launch for decode batches, the three separate dispatches otherwise; both
+    must give what matmul, matmul, gelu_mul give (up to the f32 summation order of the K splits: gate and up are
+    rounded to f16 in between, as the separate projections store them) and meet the oracle."""
+    wg, wu = la.synth.tq2_0_weights(n, k, 51), la.synth.tq2_0_weights(n, k, 52)
+    a = la.synth.normal_f16((m, k), 53, 0.5)
+    d = lambda arr: la.CudaBuffer.from_slice(ctx, arr)
+    da, dg, du = d(a), d(wg), d(wu)
+    out = Guarded(la, ctx, m * n * 2)
+    gt, ut = la.CudaBuffer.empty(ctx, m * n * 2), la.CudaBuffer.empty(ctx, m * n * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.matmul_nt_tq2_0_geglu_into(b, da, dg, du, gt, ut, out.view, m, k, n)
+    assert b.dispatch_count() == (1 if 8 < m <= 64 else (2 if m > 64 else 3))   # fused | grouped + gelu | 2 + gelu
+    b.commit_and_wait()
+    fused = out.read(np.float16)
+    g2, u2, o2 = la.CudaBuffer.empty(ctx, m * n * 2), la.CudaBuffer.empty(ctx, m * n * 2), la.CudaBuffer.empty(ctx, m * n * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.matmul_nt_tq2_0_into(b, da, dg, g2, m, k, n)
+    kernels.matmul_nt_tq2_0_into(b, da, du, u2, m, k, n)
+    kernels.gelu_mul_into(b, g2, u2, o2, m * n)
+    b.commit_and_wait()
+    rel_close(fused.astype(np.float32), o2.as_slice(np.float16, m * n).astype(np.float32), 2e-3, "geglu fused vs separate")
+    want_g = orc.matmul_nt(orc.TQ2_0, a, wg, m, k, n).astype(np.float16)
+    want_u = orc.matmul_nt(orc.TQ2_0, a, wu, m, k, n).astype(np.float16)
+    rel_close(fused.astype(np.float32), orc.gelu_mul(want_g.ravel(), want_u.ravel()).astype(np.float32), 4e-3, "geglu vs oracle")
