@@ -277,15 +277,51 @@ class DecodeStep:
     def value(self, ms_per_step: float) -> float:
         return self.lanes / (ms_per_step * 1e-3)
 
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, mean over one GeGLU and one down
+    # launch of an ncu capture (profiles/qgemm_mma_tq2_0_m64.md: 5.12 MB and 3.27 MB, cold cache).
+    FFN_TRAFFIC_BYTES = 4194800
+
     def roofline(self, ms_per_step: float, peak: float, peak_kind: str, timed):
-        """Whole-step HBM roofline (the step is HBM-bound: weights + KV are read once per step) plus the
-        live duration of the dominant kernel class, measured by running those launches alone."""
-        achieved = self.alg_bytes_per_step / (ms_per_step * 1e-3) / 1e9
+        """The dominant kernel by time is the decode matmul (qgemm_mma_kernel, TQ2_0, m = lanes): its two largest
+        launch shapes, the fused GeGLU projection and the down projection of every layer, are run alone here (one
+        graph, every layer's own weights, 2 x n_layers launches) and timed with CUDA events.  Algorithmic bytes per
+        launch = rows * row_bytes + m * cols * 2 + m * rows * 2.  The whole-step figures are reported beside it."""
+        la, ctx, cfg, m = self.la, self.ctx, self.cfg, self.lanes
+        names = la.model.LAYER_TENSORS
+        gi, ui, di = names.index("wgate"), names.index("wup"), names.index("wdown")
+        x = la.CudaBuffer.from_slice(ctx, la.synth.normal_f16((m, cfg.hidden), 91))
+        gate, up = la.CudaBuffer.empty(ctx, m * cfg.inter * 2), la.CudaBuffer.empty(ctx, m * cfg.inter * 2)
+        ffn = la.CudaBuffer.empty(ctx, m * cfg.hidden * 2)
+
+        def enqueue(b):
+            for li in range(cfg.n_layers):
+                bufs = self.model._keep[li]
+                self.k.matmul_nt_tq2_0_geglu_into(b, x, bufs[gi], bufs[ui], gate, up, gate, m, cfg.hidden, cfg.inter)
+                self.k.matmul_nt_tq2_0_into(b, gate, bufs[di], ffn, m, cfg.inter, cfg.hidden)
+        b = la.CommandBatch.new(ctx)
+        enqueue(b)
+        n_launch = b.dispatch_count()
+        b.commit_and_wait()
+        b = la.CommandBatch.capture(ctx)
+        enqueue(b)
+        graph = b.end_capture()
+        ms = timed(graph.launch, 10, 3)
+        graph.destroy()
+        tq = lambda r, c: r * (c // 256) * 66
+        bytes_geglu = 2 * tq(cfg.inter, cfg.hidden) + m * cfg.hidden * 2 + m * cfg.inter * 2
+        bytes_down = tq(cfg.hidden, cfg.inter) + m * cfg.inter * 2 + m * cfg.hidden * 2
+        per_launch = (bytes_geglu + bytes_down) / 2
+        us = ms * 1e3 / n_launch
+        achieved = per_launch / (us * 1e-6) / 1e9
+        whole = self.alg_bytes_per_step / (ms_per_step * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_kind": peak_kind, "kernel": "whole step (all launches of the graph)",
-                "algorithmic_bytes_per_step": self.alg_bytes_per_step,
-                "bound_tok_s": self.lanes / (self.alg_bytes_per_step / (peak * 1e9)),
-                "frac_of_nominal_8tbs": achieved / 8000.0}
+                "traffic": self.FFN_TRAFFIC_BYTES if m == 64 else None, "peak_kind": peak_kind,
+                "kernel": (f"{'qgemm_mma_kernel' if m <= 64 else 'qgemm_tc_kernel (tcgen05) + gelu_mul'}<TQ2_0, m={m}>: GeGLU + down "
+                           f"projections of {cfg.n_layers} layers, {n_launch} launches"),
+                "us_per_launch": us, "algorithmic_bytes_per_launch": per_launch,
+                "launches_timed_alone_share_of_step": ms / ms_per_step,
+                "whole_step": {"achieved": whole, "frac": whole / peak, "algorithmic_bytes_per_step": self.alg_bytes_per_step,
+                               "bound_tok_s": self.lanes / (self.alg_bytes_per_step / (peak * 1e9))}}
 
     def cpu_sample(self, orc, threads: int):
         lanes = 2
