@@ -244,9 +244,10 @@ class DecodeStep:
         """Size-independent checks at full size: tokens in range, lane isolation (duplicate lanes agree)."""
         nt = self.next_tokens.as_slice(np.uint32)
         assert np.all(nt < self.cfg.vocab), "argmax out of range"
-        logits = self.model.logits_buffer().as_slice(np.float32, 2 * self.cfg.vocab).reshape(2, -1)
+        nl = min(2, self.lanes)
+        logits = self.model.logits_buffer().as_slice(np.float32, nl * self.cfg.vocab).reshape(nl, -1)
         assert np.all(np.isfinite(logits)), "non-finite logits"
-        assert nt[0] == int(np.argmax(logits[0])) and nt[1] == int(np.argmax(logits[1])), "argmax kernel disagrees"
+        assert all(nt[i] == int(np.argmax(logits[i])) for i in range(nl)), "argmax kernel disagrees"
 
     def prepare_e2e(self):
         self.h_in = self.la.PinnedHost(2 * self.lanes * 4, dtype=np.uint32)

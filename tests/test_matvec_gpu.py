@@ -304,3 +304,19 @@ def test_geglu_fused_equals_separate_launches(la, orc, ctx, kernels, m, k, n):
     want_g = orc.matmul_nt(orc.TQ2_0, a, wg, m, k, n).astype(np.float16)
     want_u = orc.matmul_nt(orc.TQ2_0, a, wu, m, k, n).astype(np.float16)
     rel_close(fused.astype(np.float32), orc.gelu_mul(want_g.ravel(), want_u.ravel()).astype(np.float32), 4e-3, "geglu vs oracle")
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 256, 76000), (8, 384, 75800), (3, 1536, 80000)])
+def test_q4_0_wide_matrix_small_batch_keeps_exact_weights(la, orc, ctx, kernels, m, k, n):
+    """Batch <= 8 against a vocabulary-sized Q4_0 table: tensor-core kernel with integer operands and per-block f32
+    scaling, so the result must meet the f32-weight oracle at the matvec tolerance (not only the f16-weight one)."""
+    raw = la.synth.q4_0_weights(n, k, 61)
+    a = la.synth.normal_f16((m, k), 62)
+    want = orc.matmul_nt(orc.Q4_0, a, raw, m, k, n)
+    got32 = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_f32out_into", a, raw, m, k, n, f32out=True)
+    rel_close(got32, want, 2e-4, "wide q4_0 small batch, f32 out")
+    got = run_matmul(la, ctx, kernels, "matmul_nt_q4_0_into", a, raw, m, k, n)
+    rel_close(got, want, TOL, "wide q4_0 small batch, f16 out")
+    if m == 1:
+        y = run_matvec(la, ctx, kernels, "matvec_q4_0_f32out", raw, a[0], n, k, True, True)
+        rel_close(y, want[0], 2e-4, "matvec_q4_0_f32out on a wide table")
