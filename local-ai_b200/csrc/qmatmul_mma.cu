@@ -399,10 +399,6 @@ struct WideParams {
     int n, m, K, nb, tiles;
 };
 
-// NBT = 8: 32 < m <= 64, weights d (q - 8) rounded once to f16 (the tensor-core semantic of the batched paths).
-// NBT = 1: m <= 8 (the batch-1 vocabulary matvec); the A operand holds the integers q - 8 (exact in f16), each
-// 32-k block is accumulated on its own and scaled by d in f32, so the result keeps the CUDA-core paths' exact-weight
-// semantic.
 template <typename OutT, int NBT>
 __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -484,42 +480,14 @@ __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParam
 #pragma unroll
         for (int bi = 0; bi < 4; bi++) {
             __half2 d2[4];
-            float df[4];
             uint32_t wq[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint8_t *bp = rbase[i] + bi * BB;
                 const __half d = rvalid[i] ? *reinterpret_cast<const __half *>(bp) : __float2half(0.0f);
                 d2[i] = __half2half2(d);
-                df[i] = __half2float(d);
                 wq[i] = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
             }
-            if constexpr (NBT == 1) {
-                float cb[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-                for (int part = 0; part < 2; part++) {
-                    uint32_t a[2][4];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const uint32_t codes = (wq[i] >> (4 * part)) & 0x0F0F0F0Fu;
-                        a[i >> 1][i & 1] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032));
-                        a[i >> 1][(i & 1) + 2] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032));
-                    }
-                    uint32_t b0, b1;
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];\n"
-                                 : "=r"(b0), "=r"(b1)
-                                 : "r"(xb + (uint32_t)((32 * bi + 16 * part) * 2)));
-                    mma16816(cb[0], a[0], b0, b1);
-                    mma16816(cb[1], a[1], b0, b1);
-                }
-#pragma unroll
-                for (int f = 0; f < 2; f++) {
-                    c[f][0][0] = fmaf(df[2 * f], cb[f][0], c[f][0][0]);
-                    c[f][0][1] = fmaf(df[2 * f], cb[f][1], c[f][0][1]);
-                    c[f][0][2] = fmaf(df[2 * f + 1], cb[f][2], c[f][0][2]);
-                    c[f][0][3] = fmaf(df[2 * f + 1], cb[f][3], c[f][0][3]);
-                }
-            } else {
 #pragma unroll
             for (int part = 0; part < 2; part++) {
                 uint32_t a[2][4];
@@ -539,7 +507,6 @@ __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParam
                     mma16816(c[0][j + 1], a[0], b[2], b[3]);
                     mma16816(c[1][j + 1], a[1], b[2], b[3]);
                 }
-            }
             }
         }
         if (ch == nchunks - 1) {
@@ -585,9 +552,7 @@ static int qgemm_mma_launch(int fmt, bool f32out, lc_kernels *k, lc_batch *b, co
                             uint32_t kk, bool geglu) {
     const int be = fmt == FMT_Q4_0 ? 32 : 256, bb = fmt == FMT_Q4_0 ? 18 : 66;
     if (m > 64 || ng < 1 || ng > MAX_GROUPS || kk % be != 0 || !lc_aligned(input->dptr, 16)) return -1;
-    const bool wide_ok = !geglu && fmt == FMT_Q4_0 && ng == 1 && (m > 32 || m <= 8) && kk % W_CK == 0 &&
-                         ns[0] >= (uint32_t)(W_ROWS * k->ctx->sm_count) && (size_t)W_STAGES * W_STAGE <= k->ctx->smem_optin;
-    if (m <= 8 && !wide_ok) return -1;   // small batches: only the wide (vocabulary) kernel here
+    if (m <= 8) return -1;   // small batches: qmatvec_mma.cu / qmatvec.cu
     MmaParams p;
     p.x = (const __half *)input->dptr;
     p.m = (int)m;
@@ -603,7 +568,7 @@ static int qgemm_mma_launch(int fmt, bool f32out, lc_kernels *k, lc_batch *b, co
         if (g < ng) tiles += ((int)ns[g] + CTA_ROWS - 1) / CTA_ROWS;
         p.tile_end[g] = tiles;
     }
-    if (!geglu && fmt == FMT_Q4_0 && ng == 1 && (m > 32 || m <= 8) && kk % W_CK == 0 && ns[0] >= (uint32_t)(W_ROWS * k->ctx->sm_count) &&
+    if (!geglu && fmt == FMT_Q4_0 && ng == 1 && m > 32 && kk % W_CK == 0 && ns[0] >= (uint32_t)(W_ROWS * k->ctx->sm_count) &&
         (size_t)W_STAGES * W_STAGE <= k->ctx->smem_optin) {
         WideParams wp;
         wp.w = (const uint8_t *)weights[0]->dptr;
@@ -614,7 +579,6 @@ static int qgemm_mma_launch(int fmt, bool f32out, lc_kernels *k, lc_batch *b, co
         wp.K = (int)kk;
         wp.nb = (int)(kk / 32);
         wp.tiles = (int)((ns[0] + W_ROWS - 1) / W_ROWS);
-        if (m <= 8) return f32out ? launch_wide<float, 1>(k, b, wp) : launch_wide<__half, 1>(k, b, wp);
         return f32out ? launch_wide<float, 8>(k, b, wp) : launch_wide<__half, 8>(k, b, wp);
     }
     p.geglu = geglu ? 1 : 0;

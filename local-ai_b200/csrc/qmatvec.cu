@@ -277,20 +277,16 @@ static int check_qargs(const char *name, lc_kernels *k, lc_batch *b, const lc_bu
 }
 
 // Entry used by the other translation units (matmul routing, decode step).
-// qmatmul_mma.cu; for m <= 8 it serves only vocabulary-sized Q4_0 tables (persistent tensor-core kernel with exact
-// per-block scaling) and returns -1 for everything else.
-int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
-                         const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
-                         uint32_t kk);
+// qmatvec_mma.cu: streaming tensor-core kernel for m <= 8 and matrices large enough for bandwidth to matter;
+// returns -1 for everything else.
+int lc_qgemv_mma_stream(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                        lc_buf *output, uint32_t m, uint32_t kk, uint32_t n);
 
 int lc_qgemm_cuda_core(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
                        const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
     if (n == 0) return LC_OK;
-    if (k->mma && k->decode_mma && m <= 8 && fmt == FMT_Q4_0) {
-        const lc_buf *ws[1] = {weight};
-        lc_buf *os[1] = {output};
-        const uint32_t ns[1] = {n};
-        const int st = lc_qgemm_mma_grouped(fmt, f32out, k, b, input, 1, ws, os, ns, m, kk);
+    if (k->mma && k->decode_mma && m <= 8) {
+        const int st = lc_qgemv_mma_stream(fmt, f32out, k, b, input, weight, output, m, kk, n);
         if (st >= 0) return st;
     }
     const uint8_t *w = (const uint8_t *)weight->dptr;

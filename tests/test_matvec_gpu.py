@@ -320,3 +320,16 @@ def test_q4_0_wide_matrix_small_batch_keeps_exact_weights(la, orc, ctx, kernels,
     if m == 1:
         y = run_matvec(la, ctx, kernels, "matvec_q4_0_f32out", raw, a[0], n, k, True, True)
         rel_close(y, want[0], 2e-4, "matvec_q4_0_f32out on a wide table")
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 256, 19000), (8, 512, 20001), (2, 1536, 19100)])
+def test_tq2_0_streaming_small_batch(la, orc, ctx, kernels, m, k, n):
+    """Batch <= 8 over a TQ2_0 matrix with enough rows for the streaming tensor-core kernel (ragged last group)."""
+    raw = la.synth.tq2_0_weights(n, k, 71, ncodes=4)
+    a = la.synth.normal_f16((m, k), 72)
+    want = orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n)
+    got = run_matmul(la, ctx, kernels, "matmul_nt_tq2_0_into", a, raw, m, k, n)
+    rel_close(got, want, TOL, "streaming tq2_0 small batch")
+    if m == 1:
+        y = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", raw, a[0], n, k, True, True)
+        rel_close(y, want[0], 2e-4, "matvec_tq2_0_f32out, streaming")
