@@ -63,7 +63,9 @@ template <int FMT> struct Fmt;
 template <> struct Fmt<FMT_Q4_0> { static constexpr int bytes = 18; };
 template <> struct Fmt<FMT_TQ2_0> { static constexpr int bytes = 66; };
 
-template <int FMT, typename OutT>
+// UPQ > 0: the warp's K quarter is UPQ units long and its activation fragments (8 k-steps x 2 registers per unit)
+// stay in registers for the whole launch; UPQ = 0: any length, fragments re-read from shared memory with ldmatrix.
+template <int FMT, typename OutT, int UPQ>
 __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int BB = Fmt<FMT>::bytes;
@@ -112,6 +114,18 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
     // ldmatrix.x2 lane address: lanes 0-7 rows of the first k half, lanes 8-15 the second
     const uint32_t xl = smem_u32(x_s) + (uint32_t)((lane & 7) * p.xs + ((lane >> 3) & 1) * 16);
     OutT *out = reinterpret_cast<OutT *>(p.out);
+    uint32_t breg[UPQ > 0 ? UPQ * 8 : 1][2];
+    if (UPQ > 0) {
+        cp_async_wait<1>();
+        __syncthreads();          // the activations have landed
+#pragma unroll
+        for (int uu = 0; uu < (UPQ > 0 ? UPQ : 1); uu++)
+#pragma unroll
+            for (int s8 = 0; s8 < 8; s8++) {
+                breg[uu * 8 + s8][0] = breg[uu * 8 + s8][1] = 0u;
+                if (u0 + uu < u1) ldmatrix_x2(breg[uu * 8 + s8][0], breg[uu * 8 + s8][1], xl + (uint32_t)(((u0 + uu) * UNIT_K + 16 * s8) * 2));
+            }
+    }
 
     auto reduce_store = [&](int it) {      // warps kq == 0: add the four quarters of group `it` and store
         const int grp = (int)blockIdx.x + it * (int)gridDim.x;
@@ -151,7 +165,10 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
         float c[4] = {0.f, 0.f, 0.f, 0.f};
         if (FMT == FMT_TQ2_0) {
             // unit u = half h of block b: element 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j
-            for (int u = u0; u < u1; u++) {
+#pragma unroll
+            for (int uu = 0; uu < (UPQ > 0 ? UPQ : 64); uu++) {
+                const int u = u0 + uu;
+                if (u >= u1) break;
                 const int b = u >> 1, h = u & 1;
                 uint32_t lut_lo[2], lut_hi[2], wq[2][2];
 #pragma unroll
@@ -178,7 +195,12 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
                             a[i + 2] = __byte_perm(lut_lo[i], lut_hi[i], sel >> 16);
                         }
                         uint32_t b0, b1;
-                        ldmatrix_x2(b0, b1, xl + (uint32_t)((u * UNIT_K + 32 * l + 16 * qp) * 2));
+                        if (UPQ > 0) {
+                            b0 = breg[uu * 8 + 2 * l + qp][0];
+                            b1 = breg[uu * 8 + 2 * l + qp][1];
+                        } else {
+                            ldmatrix_x2(b0, b1, xl + (uint32_t)((u * UNIT_K + 32 * l + 16 * qp) * 2));
+                        }
                         mma16816(c, a, b0, b1);
                     }
                 }
@@ -186,7 +208,10 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
         } else {
             // unit u = blocks 4u .. 4u+3; block: f16 scale, then byte i holds k = i (low nibble) and i + 16 (high)
             const __half2 c1032 = __float2half2_rn(1032.0f);
-            for (int u = u0; u < u1; u++) {
+#pragma unroll
+            for (int uu = 0; uu < (UPQ > 0 ? UPQ : 64); uu++) {
+                const int u = u0 + uu;
+                if (u >= u1) break;
 #pragma unroll
                 for (int bi = 0; bi < 4; bi++) {
                     const int b = 4 * u + bi;
@@ -209,7 +234,12 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
                             a[i + 2] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032));
                         }
                         uint32_t b0, b1;
-                        ldmatrix_x2(b0, b1, xl + (uint32_t)((b * 32 + 16 * part) * 2));
+                        if (UPQ > 0) {
+                            b0 = breg[uu * 8 + 2 * bi + part][0];
+                            b1 = breg[uu * 8 + 2 * bi + part][1];
+                        } else {
+                            ldmatrix_x2(b0, b1, xl + (uint32_t)((b * 32 + 16 * part) * 2));
+                        }
                         mma16816(cb, a, b0, b1);
                     }
                     c[0] = fmaf(df[0], cb[0], c[0]);
@@ -226,9 +256,9 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
     if (my_groups > 0 && kq == 0) reduce_store(my_groups - 1);
 }
 
-template <int FMT, typename OutT>
-int launch_stream(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
-    auto kern = qgemv_mma_stream_kernel<FMT, OutT>;
+template <int FMT, typename OutT, int UPQ>
+int launch_stream_u(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
+    auto kern = qgemv_mma_stream_kernel<FMT, OutT, UPQ>;
     static size_t configured = 0;
     if (smem > configured) {
         LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -238,6 +268,17 @@ int launch_stream(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem
     LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT), smem, b, p));
     b->dispatch_count++;
     return LC_OK;
+}
+
+template <int FMT, typename OutT>
+int launch_stream(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
+    const int upq = (p.K / UNIT_K + 3) / 4;
+    switch (upq) {
+        case 1: return launch_stream_u<FMT, OutT, 1>(k, b, p, smem);
+        case 2: return launch_stream_u<FMT, OutT, 2>(k, b, p, smem);
+        case 3: return launch_stream_u<FMT, OutT, 3>(k, b, p, smem);
+        default: return launch_stream_u<FMT, OutT, 0>(k, b, p, smem);
+    }
 }
 
 }  // namespace
