@@ -388,8 +388,12 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
         }
     }
     const bool direct = (n_splits == 1 && !fused);
+    // the tensor-core kernel merges up to 8 splits itself (one thread-block cluster per lane and kv head)
+    static const bool cluster_allowed = []() { const char *e = getenv("LOCAL_CUDA_ATTN_CLUSTER"); return !(e && e[0] == '0'); }();
+    const bool cluster_merge = use_mma && cluster_allowed && n_splits <= 8 &&
+                               lc_aligned(out->dptr, 16) && (!fused || lc_aligned(signs->dptr, 16));
 
-    if (!direct) {
+    if (!direct && !cluster_merge) {
         int st = lc_reserve_scratch(k, b, qn / hd * n_splits * (size_t)(hd + 2) * sizeof(float), 0);
         if (st != LC_OK) return st;
     }
@@ -402,7 +406,9 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     p.kn = (const __half *)kn->dptr;
     p.vn = (const __half *)vn->dptr;
     p.levels = (const float *)levels->dptr;
-    p.out = direct ? (float *)out->dptr : nullptr;
+    p.out = (direct || (cluster_merge && !fused)) ? (float *)out->dptr : nullptr;
+    p.out_f16 = (cluster_merge && fused) ? (__half *)out->dptr : nullptr;
+    p.cluster_merge = cluster_merge ? 1 : 0;
     p.partial = (float *)k->scratch;
     p.positions = positions ? (const uint32_t *)positions->dptr : nullptr;
     p.kv_len = kv_len;
@@ -429,7 +435,7 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
             default: st = launch_split_b<512>(b, p, grid, g, bits); break;
         }
     }
-    if (st != LC_OK || direct) return st;
+    if (st != LC_OK || direct || cluster_merge) return st;
     if (fused)
         LC_LAUNCH_CHECKED(lc_launch(tq_attn_merge_kernel<true>, dim3(n_lanes * n_q), dim3(hd), 0, b, (const float *)k->scratch, (const float *)signs->dptr, nullptr, (__half *)out->dptr, hd, n_splits));
     else
@@ -591,6 +597,8 @@ extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const 
     if (n_splits < 1) n_splits = 1;
 
     TqAttnParams p;
+    p.out_f16 = nullptr;
+    p.cluster_merge = 0;
     p.rq = nullptr;
     p.q = (const __half *)q->dptr;
     p.signs = (const float *)signs->dptr;

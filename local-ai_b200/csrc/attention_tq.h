@@ -16,6 +16,11 @@ struct TqAttnParams {
     uint32_t lane_capacity, n_q, n_kv, window, ring, n_splits, group;  // group = n_q / n_kv
     uint32_t fused_q, direct_out;
     float scale;
+    // cluster_merge: the n_splits CTAs of a (lane, kv head) are one thread-block cluster; they exchange their partials
+    // through distributed shared memory and write the final result themselves (f32 rotated-space `out`, or, with
+    // fused_q, the inverse-rotated f16 `out_f16`) -- no partial buffer, no merge launch.
+    __half *out_f16;
+    uint32_t cluster_merge;
 };
 
 // Tensor-core variant for tq2 / head_dim 256 (attention_tq_mma.cu). Same grid and partial layout as the

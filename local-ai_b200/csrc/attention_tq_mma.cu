@@ -36,7 +36,7 @@ constexpr int ACC_BYTES = NW * 16 * 4 * 32 * 4;   // merge staging, reuses the f
 constexpr int DEPTH = 6;         // ring slots per warp (DEPTH - 1 tiles in flight)
 constexpr int RING_OFF = LUT_BYTES + G * HD * 4 + 256 * 8;
 constexpr int SMEM_BYTES = RING_OFF + NW * DEPTH * (4 * 32 * 16 + 32 * 4);
-static_assert(SMEM_BYTES >= ACC_BYTES + 4 * NW * G * 4, "merge staging must fit");
+static_assert(SMEM_BYTES >= ACC_BYTES + 1024 + G * HD * 4, "merge staging must fit");
 static_assert(NW == G && NT == 256, "the prologue maps warps to heads and threads to code bytes");
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -57,6 +57,33 @@ __device__ __forceinline__ void cp_async4(void *dst, const void *src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// a shared-memory word / 16 bytes of CTA `rank` of this cluster (or of this CTA when the launch is not clustered)
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank, bool clustered) {
+    float v;
+    if (clustered) {
+        uint32_t ra;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(addr), "r"(rank));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(ra));
+    } else {
+        asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+    }
+    return v;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t rank, bool clustered) {
+    float4 v;
+    if (clustered) {
+        uint32_t ra;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(addr), "r"(rank));
+        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra));
+    } else {
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    }
+    return v;
+}
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
@@ -409,6 +436,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     // Per (warp, head) weights exp(m_w - max) and the merged (max, sum); thread h < G does head h.
     float *f_s = l_s + NW * G;       // [NW][G]
     float *ml_s = f_s + NW * G;      // [G][2]
+    float *cpart = ml_s + 2 * G + 16;  // [G][HD] this CTA's merged, unnormalised tile (cluster merge only)
     if (threadIdx.x < G) {
         const int h = threadIdx.x;
         float gmax = -INFINITY;
@@ -438,7 +466,9 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
             float acc = 0.f;
 #pragma unroll
             for (int w = 0; w < NW; w++) acc += f_s[w * G + h] * acc_s[((w * 16 + s) * 4 + j) * 32 + lane];
-            if (h < gvalid) {
+            if (p.cluster_merge) {
+                cpart[h * HD + d] = acc;
+            } else if (h < gvalid) {
                 const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
                 if (p.direct_out) {
                     const float gsum = ml_s[2 * h + 1];
@@ -449,11 +479,74 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
             }
         }
     }
-    if (!p.direct_out && threadIdx.x < 2 * gvalid) {
-        const int h = threadIdx.x >> 1;
-        const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
-        p.partial[(qh * p.n_splits + split) * (size_t)(HD + 2) + (threadIdx.x & 1)] = ml_s[threadIdx.x];
+    if (!p.cluster_merge) {
+        if (!p.direct_out && threadIdx.x < 2 * gvalid) {
+            const int h = threadIdx.x >> 1;
+            const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
+            p.partial[(qh * p.n_splits + split) * (size_t)(HD + 2) + (threadIdx.x & 1)] = ml_s[threadIdx.x];
+        }
+        return;
     }
+    // ---- splits of this (lane, kv head): one cluster.  Head h is finished by CTA h mod n_splits, one warp per head:
+    // the same arithmetic, in the same order, as tq_attn_merge_kernel (attention_tq.cu) ----
+    if (p.n_splits > 1) cluster_sync(); else __syncthreads();
+    const uint32_t ml_a = smem_u32(ml_s), cp_a = smem_u32(cpart);
+    for (int h = (int)split + (int)p.n_splits * warp; h < gvalid; h += (int)p.n_splits * NW) {
+        float gmax = -INFINITY;
+        for (uint32_t sp = 0; sp < p.n_splits; sp++) gmax = fmaxf(gmax, ld_cluster_f32(ml_a + (2 * h) * 4, sp, p.n_splits > 1));
+        float gsum = 0.f, ov[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) ov[i] = 0.f;
+        for (uint32_t sp = 0; sp < p.n_splits; sp++) {
+            const float ms = ld_cluster_f32(ml_a + (2 * h) * 4, sp, p.n_splits > 1);
+            const float ls = ld_cluster_f32(ml_a + (2 * h + 1) * 4, sp, p.n_splits > 1);
+            const float f = (ms == -INFINITY) ? 0.f : expf(ms - gmax);
+            gsum += f * ls;
+            const float4 a0 = ld_cluster_f4(cp_a + (h * HD + 8 * lane) * 4, sp, p.n_splits > 1);
+            const float4 a1 = ld_cluster_f4(cp_a + (h * HD + 8 * lane + 4) * 4, sp, p.n_splits > 1);
+            ov[0] += f * a0.x; ov[1] += f * a0.y; ov[2] += f * a0.z; ov[3] += f * a0.w;
+            ov[4] += f * a1.x; ov[5] += f * a1.y; ov[6] += f * a1.z; ov[7] += f * a1.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) ov[i] = gsum > 0.f ? ov[i] / gsum : 0.f;
+        const size_t qh = (size_t)lane_idx * p.n_q + qh0 + h;
+        if (!p.fused_q) {
+            *reinterpret_cast<float4 *>(p.out + qh * HD + 8 * lane) = make_float4(ov[0], ov[1], ov[2], ov[3]);
+            *reinterpret_cast<float4 *>(p.out + qh * HD + 8 * lane + 4) = make_float4(ov[4], ov[5], ov[6], ov[7]);
+            continue;
+        }
+        // inverse rotation: Walsh-Hadamard butterflies (strides 1, 2, 4 in the thread, 8..128 across lanes), 1/sqrt(d), signs
+#pragma unroll
+        for (int len = 1; len < 8; len <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (!(i & len)) {
+                    const float a = ov[i], b2 = ov[i + len];
+                    ov[i] = a + b2;
+                    ov[i + len] = a - b2;
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+            const bool upper = lane & m;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float o2 = __shfl_xor_sync(0xffffffffu, ov[i], m);
+                ov[i] = upper ? o2 - ov[i] : ov[i] + o2;
+            }
+        }
+        const float4 s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
+        const float4 s1 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane + 4);
+        const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float inv = 1.0f / sqrtf((float)HD);
+        uint4 packed;
+        __half2 *hp = reinterpret_cast<__half2 *>(&packed);
+#pragma unroll
+        for (int i = 0; i < 4; i++) hp[i] = __floats2half2_rn(ov[2 * i] * inv * sg[2 * i], ov[2 * i + 1] * inv * sg[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(p.out_f16 + qh * HD + 8 * lane) = packed;
+    }
+    if (p.n_splits > 1) cluster_sync();   // no CTA leaves while a peer may still read its shared memory
 }
 
 }  // namespace
@@ -465,7 +558,28 @@ int lc_tq2_attn_mma_launch(lc_batch *b, const TqAttnParams &p, dim3 grid) {
         LC_CUDA_TRY(cudaFuncSetAttribute(tq2_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    LC_LAUNCH_CHECKED(lc_launch(tq2_attn_mma_kernel, grid, dim3(NT), smem, b, p));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = b->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (b->ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (p.cluster_merge && p.n_splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = p.n_splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        na++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    LC_LAUNCH_CHECKED(cudaLaunchKernelEx(&cfg, tq2_attn_mma_kernel, p));
     b->dispatch_count++;
     return LC_OK;
 }
