@@ -251,3 +251,49 @@ def test_attention_is_convex_combination_at_32k(la, orc, ctx, kernels):
     row = np.float32(one_n) * levels[(np.unpackbits(one_c, bitorder="little").reshape(hd, bits) * (1 << np.arange(bits))).sum(1)]
     for h in range(n_q):
         rel_close(got[h], row, 1e-3, f"constant-V head {h}")
+
+
+@pytest.mark.gpu
+def test_cluster_merge_path_equals_split_and_merge_launches(la, orc, ctx, kernels, tmp_path):
+    """LOCAL_CUDA_ATTN_CLUSTER=1 (read once per process, hence the child process) lets the tensor-core kernel merge
+    its splits through distributed shared memory and rotate back itself: one launch instead of two, and the same
+    arithmetic in the same order as the merge kernel, so the outputs must be bit-identical."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "cluster_attn.py"
+    script.write_text('''
+import sys, numpy as np
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+import __graft_entry__ as entry
+la = entry.load_package()
+ctx = la.CudaContext.new(0); k = la.Kernels.new(ctx)
+hd, n_q, n_kv, bits, lanes, cap = 256, 8, 1, 2, 3, 1536
+rows = lanes * cap
+d = lambda a: la.CudaBuffer.from_slice(ctx, a)
+kc = (la.synth.splitmix64(11, rows * 64 // 8).view(np.uint8)); vc = (la.synth.splitmix64(12, rows * 64 // 8).view(np.uint8))
+kn = (16.0 * la.synth.uniform(13, rows, 0.9, 1.1)).astype(np.float16); vn = (16.0 * la.synth.uniform(14, rows, 0.9, 1.1)).astype(np.float16)
+q = la.synth.normal_f16((lanes, n_q, hd), 15)
+pos = np.array([1400, 700, 40], np.uint32)
+out = la.CudaBuffer.empty(ctx, lanes * n_q * hd * 2)
+b = la.CommandBatch.new(ctx)
+k.tq_attention_batched_into(b, d(q), d(kc), d(kn), d(vc), d(vn), d(la.tq_levels(hd, bits)), d(la.tq_signs(hd, la.TQ_SEED)), out, d(pos),
+                            hd, cap, n_q, n_kv, 0, bits, lanes, 0, 0.0625)
+n = b.dispatch_count(); b.commit_and_wait()
+np.save(sys.argv[1], out.as_slice(np.uint16, lanes * n_q * hd)); print("launches", n)
+''' % (str(entry_root()), str(entry_root() / "tests")))
+    outs = {}
+    for flag in ("0", "1"):
+        env = dict(os.environ, LOCAL_CUDA_ATTN_CLUSTER=flag)
+        path = tmp_path / f"out{flag}.npy"
+        r = subprocess.run([sys.executable, str(script), str(path)], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert f"launches {2 - int(flag)}" in r.stdout
+        outs[flag] = np.load(path)
+    assert np.array_equal(outs["0"], outs["1"])
+    assert np.isfinite(outs["1"].view(np.float16).astype(np.float32)).all()
+
+
+def entry_root():
+    from pathlib import Path
+    return Path(__file__).resolve().parent.parent
