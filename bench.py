@@ -543,14 +543,18 @@ def run_reference(args, rank: int, world: int) -> None:
     threads = orc.num_threads()
     note = ("CPU restatement of the reference's arithmetic (oracle/); the reference's Metal path is unavailable on "
             "this box and its Rust toolchain is absent")
-    if name.startswith("decode"):
+    if name.startswith("decode") or name.startswith("ragged"):
         import ctypes as C
 
         class Cfg:  # the lc_model_config field names the oracle model reads
             pass
 
+        ragged = name.startswith("ragged")
         lanes_full, context, n_layers, vocab = {"decode_b64": (64, 8192, 35, 262144), "decode_b1": (1, 8192, 35, 262144),
-                                                "decode_b64_small": (64, 2048, 5, 32768)}[name]
+                                                "decode_b64_small": (64, 2048, 5, 32768),
+                                                "ragged512": (512, 2048, 35, 262144), "ragged512_allgather": (512, 2048, 35, 262144),
+                                                "ragged64_small": (64, 2048, 5, 32768),
+                                                "ragged64_small_allgather": (64, 2048, 5, 32768)}[name]
         cfg = Cfg()
         cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.inter = 1536, 8, 1, 256, 6144
         cfg.vocab, cfg.n_layers, cfg.kv_bits = vocab, n_layers, 2
@@ -570,10 +574,13 @@ def run_reference(args, rank: int, world: int) -> None:
             om.decode_batch_step(tok, pos)
         dt = (time.perf_counter() - t0) / args.steps
         val = sample_lanes / dt
-        metric, unit = f"decode_tok_s_batch{lanes_full}", "tok/s"
-        sample = (f"each step = {sample_lanes} of the {lanes_full} lanes, one token each at context {context}, all {n_layers} "
+        metric, unit = (f"decode_tok_s_ragged{lanes_full}" if ragged else f"decode_tok_s_batch{lanes_full}"), "tok/s"
+        sample = (f"each step = {sample_lanes} of the {lanes_full} lanes, one token each at context {context}"
+                  f"{' (the median of the lognormal contexts)' if ragged else ''}, all {n_layers} "
                   f"layers + vocabulary projection, {threads} OpenMP threads")
-        wl_name = f"decode step, E2B-like dense decoder {n_layers} layers, batch {lanes_full}, context {context}"
+        wl_name = (f"ragged decode, {lanes_full} sequences (lognormal contexts, median 2048) of the E2B-like decoder" if ragged else
+                   f"decode step, E2B-like dense decoder {n_layers} layers, batch {lanes_full}, context {context}, "
+                   f"TQ2_0 weights + Q4_0 vocab {vocab}, tq2 KV")
     else:
         shapes = {"matvec_tq2_0": ("tq2_0", 8192, 1536, 1), "matvec_q4_0": ("q4_0", 6144, 1536, 1),
                   "matmul_tq2_0_m16": ("tq2_0", 8192, 1536, 16), "matmul_tq2_0_m64": ("tq2_0", 8192, 1536, 64),
