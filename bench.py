@@ -646,28 +646,33 @@ def main() -> None:
     wl.prepare()
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
 
-    def barrier():
+    def barrier(collective: bool = True):
         ctx.synchronize()
         torch.cuda.synchronize()
-        if world > 1:
+        if world > 1 and collective:
             dist.barrier()
 
-    def timed(step_fn, steps: int, warmup: int) -> float:
+    def timed(step_fn, steps: int, warmup: int, collective: bool = True) -> float:
+        """CUDA-event time per step; with `collective` every rank must call it (barrier on both sides, max over
+        ranks), without it the measurement is local to the calling rank."""
         for _ in range(warmup):
             step_fn()
-        barrier()
+        barrier(collective)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(steps):
             step_fn()
         e1.record(stream)
-        barrier()
+        barrier(collective)
         ms = e0.elapsed_time(e1) / steps
-        if world > 1:
+        if world > 1 and collective:
             t = torch.tensor([ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
+
+    def timed_local(step_fn, steps: int, warmup: int) -> float:   # rank 0 alone (roofline of the dominant kernel)
+        return timed(step_fn, steps, warmup, collective=False)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -694,7 +699,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": wl.name, "l2_policy": wl.l2_note(), "launch": "one CUDA graph per step",
                    "replicas": world},
-        "roofline": wl.roofline(ms, peak, peak_kind, timed),
+        "roofline": wl.roofline(ms, peak, peak_kind, timed_local),
         "e2e": {"value": wl.value(ms_e2e) * world, "unit": unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
         "gpu_launches": wl.launches_per_step * args.steps,
         "clocks": clocks,
