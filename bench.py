@@ -279,7 +279,7 @@ class DecodeStep:
         return self.lanes / (ms_per_step * 1e-3)
 
     # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, mean over one GeGLU and one down
-    # launch of an ncu capture (profiles/qgemm_mma_tq2_0_m64.md: 5.12 MB and 3.27 MB, cold cache).
+    # launch of an ncu capture of the 5-layer workload (5.12 MB and 3.27 MB, cold cache; summary committed with the profiles).
     FFN_TRAFFIC_BYTES = 4194800
 
     def roofline(self, ms_per_step: float, peak: float, peak_kind: str, timed):
