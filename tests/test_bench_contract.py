@@ -1,0 +1,39 @@
+"""bench.py's contract, as far as it can be checked without a GPU: the reference arm runs on the host cores and
+prints one JSON line with the agreed keys, and the only timing helper the rank-0-only roofline step may use is the
+one without collectives."""
+import json
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_reference_arm_prints_the_contract_line():
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--workload", "decode_b64_small",
+                        "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "decode_tok_s_batch64" and line["unit"] == "tok/s"
+    assert line["higher_is_better"] is True and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in line["config"] and "model" not in line["config"]
+
+
+def test_reference_arm_is_rank_zero_only():
+    env = {"RANK": "1", "LOCAL_RANK": "1", "WORLD_SIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29555"}
+    import os
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
+                       capture_output=True, text=True, timeout=120, env=dict(os.environ, **env))
+    assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_rank_zero_only_steps_use_no_collective():
+    src = (ROOT / "bench.py").read_text()
+    main = src[src.index("def main()"):]
+    after_return = main[main.index("if rank != 0:"):]
+    # everything after the other ranks have left: no barrier, no all_reduce, and the roofline gets the local timer
+    assert "wl.roofline(ms, peak, peak_kind, timed_local)" in after_return
+    assert not re.search(r"\bbarrier\(\)|all_reduce|timed\(", after_return)
