@@ -450,10 +450,7 @@ class RaggedDecode(DecodeStep):
                 self.dist.all_gather_into_tensor(self.t_logits_all, self.t_logits_slice)
             else:
                 self.t_logits_all[0].copy_(self.t_logits_slice)
-            vals, idx = self.t_logits_all.max(dim=2)            # [world, total]
-            best = vals.max(dim=0).values
-            shard = (vals == best).to(torch.int32).argmax(dim=0)  # first shard holding the maximum = lowest rows
-            self.t_next = idx.gather(0, shard[None])[0] + shard * self.rows
+            self.t_next = la.sharding.greedy_from_logit_slices(self.t_logits_all, self.rows)
         self._pend = pend
 
     def l2_note(self):

@@ -51,3 +51,15 @@ def merge_argmax(values: np.ndarray, indices: np.ndarray) -> np.ndarray:
         tok = np.where(better, i, tok)
         best = np.where(better, v, best)
     return tok.astype(np.uint32)
+
+
+def greedy_from_logit_slices(logits_all, rows: int):
+    """The row-split vocabulary variant after the all-gather: `logits_all` is a torch tensor [world, lanes, rows]
+    (shard r holds table rows [r * rows, (r + 1) * rows) for every lane).  Returns the greedy token per lane with the
+    reference's first-maximum rule: torch's max / argmax return the first maximal index, and among shards holding the
+    same maximum the lowest shard (= lowest rows) wins."""
+    import torch
+    vals, idx = logits_all.max(dim=2)                       # [world, lanes]
+    best = vals.max(dim=0).values
+    shard = (vals == best).to(torch.int32).argmax(dim=0)    # first shard holding the maximum
+    return idx.gather(0, shard[None])[0] + shard * rows

@@ -53,6 +53,20 @@ def test_merge_argmax_equals_first_max_scan(la, orc):
     assert got.tolist() == want.tolist()
 
 
+def test_greedy_from_logit_slices_equals_first_max_scan(la, orc):
+    import torch
+    rng = np.random.default_rng(5)
+    lanes, vocab, world = 9, 2048, 4
+    logits = rng.standard_normal((lanes, vocab)).astype(np.float32)
+    logits[1, 100] = logits[1, 1900] = 9.0      # tie across shards
+    logits[2, 700] = logits[2, 701] = 9.0       # tie inside a shard
+    logits[3, :] = -np.inf
+    rows = vocab // world
+    sl = torch.from_numpy(np.stack([logits[:, r * rows:(r + 1) * rows] for r in range(world)]))
+    got = la.sharding.greedy_from_logit_slices(sl, rows).numpy()
+    assert got.tolist() == [orc.argmax(logits[i]) for i in range(lanes)]
+
+
 RANK_SCRIPT = textwrap.dedent('''
     import os, sys, numpy as np
     sys.path.insert(0, os.environ["REPO_ROOT"])
@@ -90,6 +104,14 @@ RANK_SCRIPT = textwrap.dedent('''
     tok = sharding.merge_argmax(vals, idxs)
     full = np.stack([synth.normal(100 + int(l), hidden) for l in order]).astype(np.float32) @ table.T
     assert tok.tolist() == full.argmax(axis=1).tolist(), (tok, full.argmax(axis=1))
+    # the variant that all-gathers the f32 logit slices themselves (equal slices: all_gather_into_tensor)
+    rows = hi - lo
+    assert vocab % world == 0 and rows == vocab // world
+    sl = torch.from_numpy(np.ascontiguousarray(logits.astype(np.float32)))
+    allsl = torch.empty(world * lanes, rows)          # gloo wants the concatenated form; NCCL also takes [world, ...]
+    dist.all_gather_into_tensor(allsl, sl)
+    tok2 = sharding.greedy_from_logit_slices(allsl.view(world, lanes, rows), rows).numpy()
+    assert tok2.tolist() == full.argmax(axis=1).tolist()
     t = torch.tensor([float(rank + 1)]); dist.all_reduce(t, op=dist.ReduceOp.MAX)
     assert t.item() == world
     dist.barrier(); dist.destroy_process_group()
