@@ -17,6 +17,20 @@
  *    serial-encoder semantics of batch.rs:59-66.
  *  - Buffers must outlive the batch / graph that references them.
  *  - Handles are not thread-safe; use one context per host thread, one per GPU.
+ *    lc_batch_begin makes its context's device current on the calling thread; a
+ *    thread that drives contexts of several GPUs must not interleave the enqueues
+ *    of batches that belong to different devices.
+ *  - Kernels start copying their constant operands (weights, norm weights,
+ *    levels, signs) while the previous kernel of the stream is still running
+ *    (programmatic dependent launch).  Such a buffer must therefore not be
+ *    written by the kernel enqueued immediately before the call that reads it as
+ *    a constant operand; callers that build weights on the device in the preceding
+ *    dispatch set LOCAL_CUDA_PDL=0 (no early start) or enqueue any other dispatch
+ *    in between.  Activations, positions and KV pools carry no such rule.
+ *  - Split-K scratch owned by an `lc_kernels` grows on demand, outside graph
+ *    capture only.  A block that was handed out once stays allocated until
+ *    lc_kernels_destroy, so a captured graph keeps working after later, larger
+ *    eager calls on the same object.
  *  - There is no CPU fallback: every compute entry point launches a CUDA kernel
  *    or fails with a status.
  */
@@ -124,8 +138,12 @@ LC_API void lc_host_free(void *ptr);
 LC_API int lc_kernels_create(lc_ctx *ctx, lc_kernels **out);
 LC_API void lc_kernels_destroy(lc_kernels *k);
 
-/* Device-side status word: kernels that wait on hardware barriers bound every wait and record
- * a non-zero value here instead of hanging.  Returns LC_ERR_TIMEOUT when it is set. */
+/* Device-side status word, for what the host cannot see before a launch.  Kernels that wait on
+ * hardware barriers bound every wait and record 1 or 2 here instead of hanging (-> LC_ERR_TIMEOUT).
+ * The per-lane entry points read positions from a device buffer: a position that points past its
+ * lane's pool rows (ring_capacity == 0 and position >= lane_capacity) writes no KV row and attends
+ * only over the rows that exist, and records 3 (-> LC_ERR_INVALID_ARGUMENT).  *status receives the
+ * word; LC_OK when it is 0.  The word stays set until the object is destroyed. */
 LC_API int lc_kernels_device_status(lc_kernels *k, int *status);
 
 /* Quantized matvec: output[rows] = matrix[rows, cols] x vector[cols], f16 input,
@@ -292,7 +310,8 @@ LC_API int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf
  * Limit: num_q_heads * (head_dim + 2) * 4 bytes per split must fit in 4 MiB (the split count
  * is lowered to fit, else LC_ERR_INVALID_ARGUMENT).  All calls share the array: calls that
  * overlap on the GPU race, so keep them on one stream.  The first call on each device
- * resolves the array's address and should be made before any stream capture. */
+ * resolves the array's address and should be made before any stream capture.  Always runs the
+ * CUDA-core split kernel (the tensor-core kernel of the regular entry point is not used here). */
 LC_API int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const lc_buf *k_codes,
                                         const lc_buf *k_norms, const lc_buf *v_codes,
                                         const lc_buf *v_norms, const lc_buf *levels, const lc_buf *signs,

@@ -385,6 +385,8 @@ int lc_kernels_create(lc_ctx *ctx, lc_kernels **out) {
     k->smallm = env_enabled("LOCAL_AI_SMALLM");
     k->mma = env_enabled("LOCAL_AI_MMA");
     k->decode_mma = env_enabled("LOCAL_CUDA_DECODE_MMA");
+    k->decode_tc = env_enabled("LOCAL_CUDA_DECODE_TC");
+    { const char *e = getenv("LOCAL_CUDA_TEST_WAIT_EXPIRY"); k->test_wait_expiry = e && strcmp(e, "1") == 0; }
     const char *nm = getenv("LOCAL_CUDA_TQ_NORM");
     k->kv_norm_mode = (nm && strcmp(nm, "tree") == 0) ? 1 : 0;
     cudaError_t e = cudaMalloc((void **)&k->dev_status, 128);  // status word + tuning stamps
@@ -403,28 +405,31 @@ void lc_kernels_destroy(lc_kernels *k) {
     cudaStreamSynchronize(k->ctx->stream);
     if (k->scratch) cudaFree(k->scratch);
     if (k->counters) cudaFree(k->counters);
+    for (void *p : k->retired) cudaFree(p);
     if (k->dev_status) cudaFree(k->dev_status);
     delete k;
 }
 
 }  // extern "C"
 
+// A captured graph keeps the scratch and counter addresses it was recorded with, so a block that has
+// ever been handed out is never freed before lc_kernels_destroy: growth allocates a new block and retires
+// the old one (kept alive in `retired`).  Graphs recorded earlier go on using their own, still valid, block.
 int lc_reserve_scratch(lc_kernels *k, lc_batch *b, size_t bytes, size_t counters) {
     if (bytes > k->scratch_bytes) {
         if (b && b->capturing)
             return lc_fail(LC_ERR_INVALID_ARGUMENT,
                            "split-K scratch must grow to %zu bytes during graph capture; run the "
                            "same call once outside capture first", bytes);
-        LC_CUDA_TRY(cudaStreamSynchronize(k->ctx->stream));
-        if (k->scratch) cudaFree(k->scratch);
-        k->scratch = nullptr;
-        k->scratch_bytes = 0;
         size_t want = bytes + bytes / 2;
-        cudaError_t e = cudaMalloc(&k->scratch, want);
+        void *fresh = nullptr;
+        cudaError_t e = cudaMalloc(&fresh, want);
         if (e != cudaSuccess) {
             cudaGetLastError();
             return lc_fail(LC_ERR_BUFFER_ALLOCATION, "scratch size=%zu: %s", want, cudaGetErrorString(e));
         }
+        if (k->scratch) k->retired.push_back(k->scratch);
+        k->scratch = fresh;
         k->scratch_bytes = want;
     }
     if (counters > k->counters_len) {
@@ -432,17 +437,22 @@ int lc_reserve_scratch(lc_kernels *k, lc_batch *b, size_t bytes, size_t counters
             return lc_fail(LC_ERR_INVALID_ARGUMENT,
                            "split-K counters must grow during graph capture; run the same call once "
                            "outside capture first");
-        LC_CUDA_TRY(cudaStreamSynchronize(k->ctx->stream));
-        if (k->counters) cudaFree(k->counters);
-        k->counters = nullptr;
-        k->counters_len = 0;
         size_t want = counters * 2;
-        cudaError_t e = cudaMalloc((void **)&k->counters, want * sizeof(unsigned int));
+        unsigned int *fresh = nullptr;
+        cudaError_t e = cudaMalloc((void **)&fresh, want * sizeof(unsigned int));
         if (e != cudaSuccess) {
             cudaGetLastError();
             return lc_fail(LC_ERR_BUFFER_ALLOCATION, "counters: %s", cudaGetErrorString(e));
         }
-        LC_CUDA_TRY(cudaMemsetAsync(k->counters, 0, want * sizeof(unsigned int), k->ctx->stream));
+        // zeroed in stream order, before any kernel that is enqueued after this call can use them
+        cudaStream_t s = b ? b->stream : k->ctx->stream;
+        e = cudaMemsetAsync(fresh, 0, want * sizeof(unsigned int), s);
+        if (e != cudaSuccess) {
+            cudaFree(fresh);
+            return lc_fail(LC_ERR_CUDA, "counters memset: %s", cudaGetErrorString(e));
+        }
+        if (k->counters) k->retired.push_back(k->counters);
+        k->counters = fresh;
         k->counters_len = want;
     }
     return LC_OK;

@@ -69,6 +69,10 @@ __global__ void __launch_bounds__(NT) tq_attn_split_kernel(const TqAttnParams p)
     if (p.positions) {
         pos = p.positions[lane_idx];
         seq_len = pos + 1u;
+        if (p.ring == 0u && seq_len > p.lane_capacity) {   // never read past the lane's rows
+            seq_len = p.lane_capacity;
+            if (p.status && threadIdx.x == 0) atomicExch(p.status, LC_DEV_STATUS_POSITION);
+        }
     } else {
         pos = p.current_pos;
         seq_len = min(p.kv_len, pos + 1u);
@@ -284,11 +288,8 @@ int launch_split(lc_batch *b, const TqAttnParams &p, dim3 grid) {
     const size_t floats = (size_t)HD * G + 16 + (size_t)NW * TILE * G + comb;
     const size_t smem = floats * sizeof(float);
     auto kern = tq_attn_split_kernel<HD, BITS, G>;
-    static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT), smem, b, p));
     LC_CHECK_LAUNCH("flash_attention_tq");
     b->dispatch_count++;
@@ -354,6 +355,10 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
                    vn->bytes >= rows * n_kv * 2,
                "%s: KV buffers hold fewer than %zu rows", name, rows);
     LC_REQUIRE(lc_aligned(kc->dptr, 16) && lc_aligned(vc->dptr, 16), "%s: code buffers must be 16-byte aligned", name);
+    LC_REQUIRE(lc_aligned(rq_or_q->dptr, fused ? 2 : 4) && lc_aligned(out->dptr, fused ? 2 : 4) &&
+                   lc_aligned(levels->dptr, 4) && (!fused || lc_aligned(signs->dptr, 4)) && lc_aligned(kn->dptr, 2) &&
+                   lc_aligned(vn->dptr, 2),
+               "%s: a buffer is not aligned to its element size", name);
 
     const uint32_t group = n_q / n_kv;
     int g = group >= 8 ? 8 : (group > 4 ? 8 : (group > 2 ? 4 : (group > 1 ? 2 : 1)));
@@ -362,8 +367,10 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     static const bool mma_allowed = []() { const char *e = getenv("LOCAL_CUDA_ATTN_MMA"); return !(e && e[0] == '0'); }();
     // (the tensor-core kernel copies norms as aligned 4-byte words)
     const size_t norm_words = ((rows * n_kv + 1) & ~(size_t)1) * 2;
+    // (... and loads the query and the signs as 16-byte vectors: buffers wrapped at other offsets take the CUDA-core kernel)
     const bool use_mma = mma_allowed && hd == 256 && bits == 2 && lc_aligned(kn->dptr, 4) && lc_aligned(vn->dptr, 4) &&
-                         kn->bytes >= norm_words && vn->bytes >= norm_words && (ring == 0 || ring >= 16);
+                         kn->bytes >= norm_words && vn->bytes >= norm_words && (ring == 0 || ring >= 16) &&
+                         lc_aligned(rq_or_q->dptr, 16) && (!fused || lc_aligned(signs->dptr, 16));
     if (use_mma) g = 8;
     const uint32_t gchunks = (group + g - 1) / g;
     const uint32_t base = n_lanes * n_kv * gchunks;
@@ -427,6 +434,7 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     p.fused_q = fused ? 1 : 0;
     p.direct_out = direct ? 1 : 0;
     p.scale = scale;
+    p.status = k->dev_status;
     dim3 grid(n_splits, n_kv * gchunks, n_lanes);
     int st;
     if (use_mma) {
@@ -521,30 +529,39 @@ int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *q, co
 //  * two calls that overlap on the GPU (different streams, or two host threads)
 //    race on the array.  Issue them on one stream, or serialise them.
 //  * the first call on each device looks up the array's device address
-//    (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make
-//    that first call before any stream capture begins.
+//    (cudaGetSymbolAddress) and, like every launch site of this library, raises
+//    the kernels' shared-memory limit on that device; make that first call
+//    before any stream capture begins.
+//  * this entry point always runs the CUDA-core split kernel, for every head
+//    size and bit width; the regular entry point's tensor-core kernel (tq2 at
+//    head_dim 256) is not used here, so at that shape it is the slower of the
+//    two, with the same results to within the tests' tolerance.
 constexpr size_t LC_NOALLOC_SCRATCH_FLOATS = (size_t)1 << 20;  // 4 MiB
 static __device__ __align__(256) float g_noalloc_scratch[LC_NOALLOC_SCRATCH_FLOATS];
 
 namespace {
 
-constexpr int NOALLOC_MAX_DEVICES = 64;
-float *g_noalloc_ptr[NOALLOC_MAX_DEVICES];  // device address of g_noalloc_scratch, per device
+std::atomic<float *> g_noalloc_ptr[LC_MAX_DEVICES];  // device address of g_noalloc_scratch, per device
 
 // The array's name is a host-side stand-in here, not a device address: resolve
-// it once per device, with that device current.
+// it once per device, with that device current, and leave the caller's current
+// device as it was.  Two threads that race on a device's first call both resolve
+// the same address, so the slot only needs to be written atomically.
 int noalloc_scratch_for(int device, float **out) {
-    if (device < 0 || device >= NOALLOC_MAX_DEVICES)
+    if (device < 0 || device >= LC_MAX_DEVICES)
         return lc_fail(LC_ERR_INVALID_ARGUMENT, "tq_attention_noalloc: device %d out of range", device);
-    if (!g_noalloc_ptr[device]) {
-        LC_CUDA_TRY(cudaSetDevice(device));
-        float *ptr = nullptr;
+    float *ptr = g_noalloc_ptr[device].load(std::memory_order_acquire);
+    if (!ptr) {
+        int prev = -1;
+        LC_CUDA_TRY(cudaGetDevice(&prev));
+        if (prev != device) LC_CUDA_TRY(cudaSetDevice(device));
         cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch);
+        if (prev != device) cudaSetDevice(prev);
         if (e != cudaSuccess || !ptr)
             return lc_fail(LC_ERR_CUDA, "tq_attention_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        g_noalloc_ptr[device] = ptr;
+        g_noalloc_ptr[device].store(ptr, std::memory_order_release);
     }
-    *out = g_noalloc_ptr[device];
+    *out = ptr;
     return LC_OK;
 }
 
@@ -626,6 +643,7 @@ extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const 
     p.fused_q = 1;
     p.direct_out = 0;
     p.scale = softmax_scale;
+    p.status = nullptr;
     dim3 grid(n_splits, num_kv_heads * gchunks, 1);
     switch (head_dim) {
         case 64: st = launch_split_b<64>(b, p, grid, g, bits); break;

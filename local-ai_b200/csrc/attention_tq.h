@@ -21,6 +21,10 @@ struct TqAttnParams {
     // fused_q, the inverse-rotated f16 `out_f16`) -- no partial buffer, no merge launch.
     __half *out_f16;
     uint32_t cluster_merge;
+    // Device-resident positions cannot be checked on the host: a lane whose position lies beyond its pool rows
+    // (ring == 0 and position >= lane_capacity) is clamped to the rows that exist and *status is set to
+    // LC_DEV_STATUS_POSITION (NULL: no report).
+    int *status;
 };
 
 // Tensor-core variant for tq2 / head_dim 256 (attention_tq_mma.cu). Same grid and partial layout as the

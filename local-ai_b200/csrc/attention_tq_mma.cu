@@ -143,6 +143,10 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     if (p.positions) {
         pos = p.positions[lane_idx];
         seq_len = pos + 1u;
+        if (p.ring == 0u && seq_len > p.lane_capacity) {   // never read past the lane's rows
+            seq_len = p.lane_capacity;
+            if (p.status && threadIdx.x == 0) atomicExch(p.status, LC_DEV_STATUS_POSITION);
+        }
     } else {
         pos = p.current_pos;
         seq_len = min(p.kv_len, pos + 1u);
@@ -553,11 +557,8 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
 
 int lc_tq2_attn_mma_launch(lc_batch *b, const TqAttnParams &p, dim3 grid) {
     const size_t smem = SMEM_BYTES;
-    static bool configured = false;
-    if (!configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(tq2_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(tq2_attn_mma_kernel, optin, b->ctx, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(NT);

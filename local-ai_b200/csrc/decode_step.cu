@@ -18,12 +18,15 @@
 // lane_rows = ring capacity on sliding-window layers) and the scratch; weights are
 // borrowed buffers.  The whole step can be captured into one CUDA graph.
 #include <math.h>
+#include <stdlib.h>
 #include <vector>
 
 #include "lc_internal.h"
 
 int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
                                lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk);
+
+constexpr uint32_t LC_MAX_CHAINS = 4;
 
 struct lc_model_layer {
     const lc_buf *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr,
@@ -44,6 +47,12 @@ struct lc_model {
     lc_buf *x = nullptr, *x2 = nullptr, *normed = nullptr, *q = nullptr, *kbuf = nullptr, *vbuf = nullptr,
            *attn = nullptr, *resid = nullptr, *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
     std::vector<lc_buf *> owned;
+    // lane-group chains (see chain_count): side streams, their own kernels objects (split-K scratch is per object) and
+    // the fork / join events
+    uint32_t default_chains = 1;
+    cudaStream_t side_s[LC_MAX_CHAINS - 1] = {};
+    lc_kernels *side_k[LC_MAX_CHAINS - 1] = {};
+    cudaEvent_t fork_ev = nullptr, join_ev[LC_MAX_CHAINS - 1] = {};
 };
 
 namespace {
@@ -113,12 +122,35 @@ int lc_model_create(lc_ctx *ctx, lc_kernels *k, const lc_model_config *cfg, lc_m
         (st = alloc(m, n * c.inter * 2, &m->gate)) || (st = alloc(m, n * c.inter * 2, &m->up)) ||
         (st = alloc(m, n * c.hidden * 2, &m->ffn)) || (st = alloc(m, n * (size_t)c.vocab * 4, &m->logits)))
         return fail(st);
+    {
+        const char *e = getenv("LOCAL_CUDA_DECODE_CHAINS");
+        const long v = e ? strtol(e, nullptr, 10) : 1;
+        m->default_chains = v < 1 ? 1u : (v > (long)LC_MAX_CHAINS ? LC_MAX_CHAINS : (uint32_t)v);
+    }
+    if (cudaEventCreateWithFlags(&m->fork_ev, cudaEventDisableTiming) != cudaSuccess)
+        return fail(lc_fail(LC_ERR_CUDA, "lc_model_create: event"));
+    for (uint32_t i = 0; i + 1 < LC_MAX_CHAINS; i++) {
+        if (cudaStreamCreateWithFlags(&m->side_s[i], cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&m->join_ev[i], cudaEventDisableTiming) != cudaSuccess)
+            return fail(lc_fail(LC_ERR_CUDA, "lc_model_create: side stream"));
+        if ((st = lc_kernels_create(ctx, &m->side_k[i])) != LC_OK) return fail(st);
+    }
     *out = m;
     return LC_OK;
 }
 
 void lc_model_destroy(lc_model *m) {
     if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    for (uint32_t i = 0; i + 1 < LC_MAX_CHAINS; i++) {
+        if (m->side_s[i]) {
+            cudaStreamSynchronize(m->side_s[i]);
+            cudaStreamDestroy(m->side_s[i]);
+        }
+        if (m->join_ev[i]) cudaEventDestroy(m->join_ev[i]);
+        if (m->side_k[i]) lc_kernels_destroy(m->side_k[i]);
+    }
+    if (m->fork_ev) cudaEventDestroy(m->fork_ev);
     for (lc_buf *b : m->owned) lc_buf_free(b);
     delete m;
 }
@@ -200,46 +232,114 @@ int lc_model_reset_lane(lc_model *m, uint32_t lane) {
     return LC_OK;
 }
 
+// The per-layer part of the step for lanes [lane0, lane0 + n): every buffer is addressed through a view that starts
+// at the chain's first lane, so the kernels see an ordinary n-lane step.
+static int run_layers(lc_model *m, lc_kernels *k, lc_batch *b, const lc_buf *positions, uint32_t lane0, uint32_t n) {
+    const lc_model_config &c = m->cfg;
+    const uint32_t H = c.hidden, HD = c.head_dim, NQ = c.n_q_heads, NKV = c.n_kv_heads, I = c.inter;
+    const uint32_t qd = NQ * HD, kd = NKV * HD;
+    const size_t cb = lc_tq_code_bytes(c.head_dim, c.kv_bits);
+    auto view = [](const lc_buf *src, size_t off) {
+        lc_buf v = *src;
+        v.dptr = (char *)src->dptr + off;
+        v.bytes = src->bytes - off;
+        v.owned = false;
+        return v;
+    };
+    lc_buf pos = view(positions, (size_t)lane0 * 4);
+    lc_buf xa = view(m->x, (size_t)lane0 * H * 2), xb = view(m->x2, (size_t)lane0 * H * 2);
+    lc_buf normed = view(m->normed, (size_t)lane0 * H * 2), q = view(m->q, (size_t)lane0 * qd * 2);
+    lc_buf kbuf = view(m->kbuf, (size_t)lane0 * kd * 2), vbuf = view(m->vbuf, (size_t)lane0 * kd * 2);
+    lc_buf attn = view(m->attn, (size_t)lane0 * qd * 2), resid = view(m->resid, (size_t)lane0 * H * 2);
+    lc_buf gate = view(m->gate, (size_t)lane0 * I * 2), up = view(m->up, (size_t)lane0 * I * 2);
+    lc_buf ffn = view(m->ffn, (size_t)lane0 * H * 2);
+    lc_buf *x = &xa, *xn = &xb;
+    const size_t nl = m->layers.size();
+    int st;
+#define STEP(call) do { if ((st = (call)) != LC_OK) return st; } while (0)
+    for (size_t li = 0; li < nl; li++) {
+        lc_model_layer &L = m->layers[li];
+        const size_t row0 = (size_t)lane0 * L.lane_rows * NKV;
+        lc_buf kc = view(L.k_codes, row0 * cb), vc = view(L.v_codes, row0 * cb);
+        lc_buf kn = view(L.k_norms, row0 * 2), vn = view(L.v_norms, row0 * 2);
+        // Q, K, V in one grouped launch (same activations); q_norm + RoPE fused; the KV write fused
+        {
+            const lc_buf *ws[3] = {L.wq, L.wk, L.wv};
+            lc_buf *os[3] = {&q, &kbuf, &vbuf};
+            const uint32_t ns[3] = {qd, kd, kd};
+            STEP(lc_matmul_nt_tq2_0_grouped(k, b, &normed, 3, ws, os, ns, n, H));
+        }
+        STEP(lc_qkv_post_batched_into(k, b, &q, L.q_norm, NQ, &kbuf, &vbuf, L.k_norm, &pos, m->levels, m->signs, &kc, &kn,
+                                      &vc, &vn, HD, NKV, L.lane_rows, c.kv_bits, n, L.ring, c.rms_eps, c.rope_theta, 1.0f));
+        STEP(lc_tq_attention_batched_into(k, b, &q, &kc, &kn, &vc, &vn, m->levels, m->signs, &attn, &pos, HD, L.lane_rows,
+                                          NQ, NKV, L.window, c.kv_bits, n, L.ring, c.softmax_scale));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, &attn, L.wo, &ffn, n, qd, H));
+        // resid = rms_norm(ffn, post_attn) + x ; normed = rms_norm(resid, ffn_norm)
+        STEP(lc_rms_norm_add_norm_into(k, b, &ffn, L.post_attn_norm, x, &resid, L.ffn_norm, &normed, H, n, c.rms_eps));
+        STEP(lc_matmul_nt_tq2_0_geglu_into(k, b, &normed, L.wgate, L.wup, &gate, &up, &gate, n, H, I));
+        STEP(lc_matmul_nt_tq2_0_into(k, b, &gate, L.wdown, &ffn, n, I, H));
+        // x' = rms_norm(ffn, post_ffn) + resid ; normed = rms_norm(x', next layer's attention norm | final norm)
+        const lc_buf *next_norm = li + 1 < nl ? m->layers[li + 1].attn_norm : m->final_norm;
+        STEP(lc_rms_norm_add_norm_into(k, b, &ffn, L.post_ffn_norm, &resid, xn, next_norm, &normed, H, n, c.rms_eps));
+        lc_buf *t = x; x = xn; xn = t;
+    }
+#undef STEP
+    return LC_OK;
+}
+
+// How many independent lane groups ("chains") the layers of a step are issued as.  The per-layer kernels of a decode
+// step are short and strictly dependent, so one chain leaves most SMs idle most of the time; lanes are independent
+// between the embedding and the vocabulary projection, so two or four chains on forked streams fill the gaps (each
+// re-reads the layer's weights, from L2 when the chains stay close).  LOCAL_CUDA_DECODE_CHAINS overrides.
+static uint32_t chain_count(const lc_model *m, uint32_t n_lanes) {
+    uint32_t want = m->default_chains;
+    if (n_lanes < 32) want = 1;
+    else if (n_lanes < 64 && want > 2) want = 2;
+    if (want > LC_MAX_CHAINS) want = LC_MAX_CHAINS;
+    return want < 1 ? 1 : want;
+}
+
 int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *tokens, const lc_buf *positions,
                                     uint32_t n_lanes, uint32_t want_logits, lc_buf *next_tokens) {
     if (!m || !b || !tokens || !positions) return lc_fail(LC_ERR_INVALID_ARGUMENT, "decode_batch_step: NULL argument");
     const lc_model_config &c = m->cfg;
     LC_REQUIRE(n_lanes >= 1 && n_lanes <= c.max_lanes, "decode_batch_step: n_lanes %u not in 1..=%u", n_lanes, c.max_lanes);
     LC_REQUIRE(m->embed && m->final_norm, "decode_batch_step: embedding not set");
+    LC_REQUIRE(tokens->bytes >= (size_t)n_lanes * 4 && positions->bytes >= (size_t)n_lanes * 4,
+               "decode_batch_step: tokens / positions hold fewer than %u entries", n_lanes);
     for (const lc_model_layer &L : m->layers) LC_REQUIRE(L.wq, "decode_batch_step: a layer has no weights");
     lc_kernels *k = m->k;
-    const uint32_t H = c.hidden, HD = c.head_dim, NQ = c.n_q_heads, NKV = c.n_kv_heads, I = c.inter, n = n_lanes;
-    const uint32_t qd = NQ * HD, kd = NKV * HD;
+    const uint32_t H = c.hidden, n = n_lanes;
     int st;
 #define STEP(call) do { if ((st = (call)) != LC_OK) return st; } while (0)
     STEP(lc_embed_rows_q4_0_into(k, b, m->embed, tokens, m->x, n, H, c.vocab, c.embed_scale));
-    lc_buf *x = m->x, *xn = m->x2;
-    const size_t nl = m->layers.size();
-    STEP(lc_rms_norm_into(k, b, x, m->layers[0].attn_norm, m->normed, H, n, c.rms_eps));
-    for (size_t li = 0; li < nl; li++) {
-        lc_model_layer &L = m->layers[li];
-        // Q, K, V in one grouped launch (same activations); q_norm + RoPE fused; the KV write fused
-        {
-            const lc_buf *ws[3] = {L.wq, L.wk, L.wv};
-            lc_buf *os[3] = {m->q, m->kbuf, m->vbuf};
-            const uint32_t ns[3] = {qd, kd, kd};
-            STEP(lc_matmul_nt_tq2_0_grouped(k, b, m->normed, 3, ws, os, ns, n, H));
+    STEP(lc_rms_norm_into(k, b, m->x, m->layers[0].attn_norm, m->normed, H, n, c.rms_eps));
+    const uint32_t chains = chain_count(m, n);
+    if (chains <= 1) {
+        STEP(run_layers(m, k, b, positions, 0, n));
+    } else {
+        // fork: chain 0 stays on the batch's stream, chains 1.. run on the model's side streams (captured into the same
+        // graph when the batch is capturing); join before the vocabulary projection
+        const uint32_t per = ((n + chains - 1) / chains + 7) & ~7u;
+        cudaStream_t main_s = b->stream;
+        LC_CUDA_TRY(cudaEventRecord(m->fork_ev, main_s));
+        uint32_t lane0 = per;
+        for (uint32_t ci = 1; ci < chains && lane0 < n; ci++, lane0 += per) {
+            lc_kernels *kc = m->side_k[ci - 1];
+            kc->batchm = k->batchm; kc->smallm = k->smallm; kc->mma = k->mma; kc->decode_mma = k->decode_mma; kc->decode_tc = k->decode_tc;
+            kc->kv_norm_mode = k->kv_norm_mode;
+            lc_batch side = *b;
+            side.stream = m->side_s[ci - 1];
+            side.dispatch_count = 0;
+            LC_CUDA_TRY(cudaStreamWaitEvent(side.stream, m->fork_ev, 0));
+            st = run_layers(m, kc, &side, positions, lane0, (lane0 + per <= n ? per : n - lane0));
+            b->dispatch_count += side.dispatch_count;
+            // join even after a failure so that a capture in progress stays well-formed
+            cudaEventRecord(m->join_ev[ci - 1], side.stream);
+            cudaStreamWaitEvent(main_s, m->join_ev[ci - 1], 0);
+            if (st != LC_OK) return st;
         }
-        STEP(lc_qkv_post_batched_into(k, b, m->q, L.q_norm, NQ, m->kbuf, m->vbuf, L.k_norm, positions, m->levels, m->signs,
-                                      L.k_codes, L.k_norms, L.v_codes, L.v_norms, HD, NKV, L.lane_rows, c.kv_bits, n, L.ring,
-                                      c.rms_eps, c.rope_theta, 1.0f));
-        STEP(lc_tq_attention_batched_into(k, b, m->q, L.k_codes, L.k_norms, L.v_codes, L.v_norms, m->levels, m->signs,
-                                          m->attn, positions, HD, L.lane_rows, NQ, NKV, L.window, c.kv_bits, n, L.ring,
-                                          c.softmax_scale));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->attn, L.wo, m->ffn, n, qd, H));
-        // resid = rms_norm(ffn, post_attn) + x ; normed = rms_norm(resid, ffn_norm)
-        STEP(lc_rms_norm_add_norm_into(k, b, m->ffn, L.post_attn_norm, x, m->resid, L.ffn_norm, m->normed, H, n, c.rms_eps));
-        STEP(lc_matmul_nt_tq2_0_geglu_into(k, b, m->normed, L.wgate, L.wup, m->gate, m->up, m->gate, n, H, I));
-        STEP(lc_matmul_nt_tq2_0_into(k, b, m->gate, L.wdown, m->ffn, n, I, H));
-        // x' = rms_norm(ffn, post_ffn) + resid ; normed = rms_norm(x', next layer's attention norm | final norm)
-        const lc_buf *next_norm = li + 1 < nl ? m->layers[li + 1].attn_norm : m->final_norm;
-        STEP(lc_rms_norm_add_norm_into(k, b, m->ffn, L.post_ffn_norm, m->resid, xn, next_norm, m->normed, H, n, c.rms_eps));
-        lc_buf *t = x; x = xn; xn = t;
+        STEP(run_layers(m, k, b, positions, 0, per < n ? per : n));
     }
     if (want_logits || next_tokens) {
         STEP(lc_matmul_nt_q4_0_f32out_into(k, b, m->normed, m->embed, m->logits, n, H, c.vocab));

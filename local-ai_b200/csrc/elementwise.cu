@@ -605,13 +605,8 @@ int lc_rms_norm_add_norm_into(lc_kernels *k, lc_batch *b, const lc_buf *input, c
     }
     const unsigned threads = dim >= 1024 ? 512 : (dim >= 256 ? 256 : 64);
     const size_t smem = (size_t)dim * 2;
-    if (smem > 48 * 1024) {
-        static size_t configured = 0;
-        if (smem > configured) {
-            LC_CUDA_TRY(cudaFuncSetAttribute(rms_norm_add_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured = smem;
-        }
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(rms_norm_add_norm_kernel, optin, b->ctx, smem));
     LC_LAUNCH_CHECKED(lc_launch(rms_norm_add_norm_kernel, dim3(rows), dim3(threads), smem, b, (const __half *)input->dptr,
                                 (const __half *)weight->dptr, (const __half *)residual->dptr, (__half *)out_residual->dptr,
                                 (const __half *)weight2->dptr, (__half *)out_normed->dptr, dim, eps));

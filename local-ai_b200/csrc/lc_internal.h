@@ -3,7 +3,9 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <atomic>
 #include <string>
+#include <vector>
 
 #include "../../include/local_cuda.h"
 
@@ -48,6 +50,7 @@ struct lc_kernels {
     bool batchm = true;  // LOCAL_AI_BATCHM: register-resident small-M path
     bool smallm = true;  // LOCAL_AI_SMALLM
     bool mma = true;     // LOCAL_AI_MMA: tensor-core path for larger M
+    bool decode_tc = true;   // LOCAL_CUDA_DECODE_TC: lean tcgen05 kernel for TQ2_0 at 8 < M <= 64
     bool decode_mma = true;  // LOCAL_CUDA_DECODE_MMA: register-direct mma.sync path for 8 < M <= 64 (0: tcgen05 there too)
     int kv_norm_mode = 0;  // LOCAL_CUDA_TQ_NORM: 0 sequential (Rust codec order), 1 tree (Metal order)
     // Library-owned scratch for split-K partials (grown outside graph capture).
@@ -55,8 +58,17 @@ struct lc_kernels {
     size_t scratch_bytes = 0;
     unsigned int *counters = nullptr;  // per-(lane,head) arrival counters, zero between launches
     size_t counters_len = 0;
+    std::vector<void *> retired;  // outgrown scratch / counter blocks: graphs recorded earlier still point at them
     int *dev_status = nullptr;  // device-side error word (bounded waits report here)
+    // LOCAL_CUDA_TEST_WAIT_EXPIRY=1 (read at creation): the tcgen05 matmul's barrier waits use a short limit and wait for
+    // an arrival that never comes, so the expiry path (status word, early exit, TMEM release) can be exercised on purpose.
+    bool test_wait_expiry = false;
 };
+
+// Values of the device-side status word (lc_kernels::dev_status).
+constexpr int LC_DEV_STATUS_WAIT_EXPIRED = 1;      // a bounded barrier wait ran out (large-tile tcgen05 matmul)
+constexpr int LC_DEV_STATUS_WAIT_EXPIRED_TCD = 2;  // the same in the decode tcgen05 matmul
+constexpr int LC_DEV_STATUS_POSITION = 3;          // a device-resident position pointed past its lane's pool rows
 
 // Record a failure for lc_last_error() and return `code`.
 int lc_fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
@@ -113,6 +125,23 @@ static inline cudaError_t lc_launch(void (*kern)(KArgs...), dim3 grid, dim3 bloc
 __device__ __forceinline__ void lc_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void lc_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
+
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of a kernel.  One
+// lc_smem_optin (a function-local static at each launch site, i.e. one per kernel instantiation) remembers
+// the largest size already granted on each device, so every device a context is created on gets its own call.
+constexpr int LC_MAX_DEVICES = 64;
+struct lc_smem_optin {
+    std::atomic<size_t> granted[LC_MAX_DEVICES];
+};
+template <typename Kern>
+static inline cudaError_t lc_ensure_smem(Kern kern, lc_smem_optin &state, const lc_ctx *ctx, size_t smem) {
+    if (smem <= 48 * 1024) return cudaSuccess;
+    const int dev = ctx->device;
+    if (dev >= 0 && dev < LC_MAX_DEVICES && state.granted[dev].load(std::memory_order_relaxed) >= smem) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess && dev >= 0 && dev < LC_MAX_DEVICES) state.granted[dev].store(smem, std::memory_order_relaxed);
+    return e;
+}
 
 static inline bool lc_aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 

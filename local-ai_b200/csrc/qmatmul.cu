@@ -2,13 +2,15 @@
 // stand-in for Kernels::matmul_nt_q4_0_into / matmul_nt_tq2_0_into
 // (local-metal/src/kernels.rs:6459-6563).  The reference picks between four
 // Metal kernels by m (batchm <= 4, smallm <= 8, simdgroup MMA, scalar tile);
-// here the choice is between three: the register-resident CUDA-core path that
-// streams the weights once for up to 16 rows (qmatvec.cu, m <= 8), the
-// register-direct mma.sync path for decode batches (qmatmul_mma.cu, 8 < m <= 64,
-// where launch latency rather than tensor throughput decides) and the tcgen05
-// tensor-core path for larger m (qmatmul_tc.cu).  LOCAL_AI_MMA=0 forces the
-// CUDA-core path for every m, as it forces the non-MMA kernels in the reference;
-// LOCAL_CUDA_DECODE_MMA=0 sends 8 < m <= 64 to the tcgen05 path as well.
+// here: the register-resident CUDA-core path that streams the weights once for
+// up to 16 rows (qmatvec.cu, m <= 8); for decode batches (8 < m <= 64) the lean
+// tcgen05 kernel (qmatmul_tcd.cu: TQ2_0, f16 out) or the register-direct
+// mma.sync kernel (qmatmul_mma.cu: Q4_0, f32 out, shapes the former declines);
+// and the large-tile tcgen05 kernel for larger m (qmatmul_tc.cu).
+// LOCAL_AI_MMA=0 forces the CUDA-core path for every m, as it forces the non-MMA
+// kernels in the reference; LOCAL_CUDA_DECODE_TC=0 / LOCAL_CUDA_DECODE_MMA=0
+// switch the two decode kernels off (with both off, 8 < m <= 64 runs on
+// qmatmul_tc.cu as well).
 #include <stdlib.h>
 #include "lc_internal.h"
 
@@ -26,18 +28,28 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
                          const lc_buf *const *weights, lc_buf *const *outputs, const uint32_t *ns, uint32_t m,
                          uint32_t kk);
 
+// qmatmul_tcd.cu: tcgen05 decode matmul (TQ2_0, f16 out, 8 < m <= 64); same return contract.
+int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
+                        lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk, bool geglu);
+
 static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch *b, const lc_buf *input,
                  const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
     int st = lc_check_qargs(fmt, name, k, b, weight, input, output, m, kk, n, f32out ? 4 : 2);
     if (st != LC_OK) return st;
     if (n == 0) return LC_OK;
     if (k->mma && m > 8) {
-        if (k->decode_mma && m <= 64) {
+        if (m <= 64) {
             const lc_buf *ws[1] = {weight};
             lc_buf *os[1] = {output};
             const uint32_t ns[1] = {n};
-            st = lc_qgemm_mma_grouped(fmt, f32out, k, b, input, 1, ws, os, ns, m, kk);
-            if (st >= 0) return st;
+            if (k->decode_tc && fmt == 1 && !f32out) {
+                st = lc_qgemm_tcd_launch(k, b, input, 1, ws, os, ns, m, kk, false);
+                if (st >= 0) return st;
+            }
+            if (k->decode_mma) {
+                st = lc_qgemm_mma_grouped(fmt, f32out, k, b, input, 1, ws, os, ns, m, kk);
+                if (st >= 0) return st;
+            }
         }
         st = lc_qgemm_tcgen05(fmt, f32out, k, b, input, weight, output, m, kk, n);
         if (st >= 0) return st;
@@ -59,7 +71,8 @@ int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, 
     }
     if (k->mma && m > 8) {
         int st = -1;
-        if (k->decode_mma && m <= 64) st = lc_qgemm_mma_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
+        if (k->decode_tc && m <= 64) st = lc_qgemm_tcd_launch(k, b, input, ng, weights, outputs, ns, m, kk, false);
+        if (st < 0 && k->decode_mma && m <= 64) st = lc_qgemm_mma_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
         if (st < 0) st = lc_qgemm_tcgen05_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
         if (st >= 0) return st;
     }
@@ -88,9 +101,18 @@ int lc_matmul_nt_tq2_0_geglu_into(lc_kernels *k, lc_batch *b, const lc_buf *inpu
     if (st != LC_OK) return st;
     if (n == 0 || m == 0) return LC_OK;
     static const bool fused_ok = []() { const char *e = getenv("LOCAL_CUDA_GEGLU_FUSED"); return !(e && e[0] == '0'); }();
-    if (fused_ok && k->mma && k->decode_mma && m > 8 && m <= 64) {
-        st = lc_qgemm_mma_geglu(k, b, input, w_gate, w_up, output, m, kk, n);
-        if (st >= 0) return st;
+    if (fused_ok && k->mma && m > 8 && m <= 64) {
+        if (k->decode_tc) {
+            const lc_buf *ws[2] = {w_gate, w_up};
+            lc_buf *os[2] = {output, output};
+            const uint32_t ns[2] = {n, n};
+            st = lc_qgemm_tcd_launch(k, b, input, 2, ws, os, ns, m, kk, true);
+            if (st >= 0) return st;
+        }
+        if (k->decode_mma) {
+            st = lc_qgemm_mma_geglu(k, b, input, w_gate, w_up, output, m, kk, n);
+            if (st >= 0) return st;
+        }
     }
     const lc_buf *ws[2] = {w_gate, w_up};
     lc_buf *os[2] = {gate_tmp, up_tmp};

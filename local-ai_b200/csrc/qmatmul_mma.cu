@@ -21,8 +21,10 @@
 // barrier, every CTA adds one slice of the tile over all splits in split order through distributed shared
 // memory and stores it -- deterministic, with no round trip through global memory.
 //
-// Numerics: identical to the tcgen05 path.  TQ2_0 weights d (q - 1) are exact in f16; Q4_0 weights d (q - 8)
-// are rounded once to f16; accumulation is f32.
+// Numerics: TQ2_0 weights d (q - 1) are exact in f16.  For Q4_0 the MMA operand is the integer q - 8 (exact in
+// f16); the two k-steps of a 32-k block accumulate on their own and the block's f32 sum is scaled by d in f32, so
+// the weights keep the f32 value d (q - 8) the reference's kernels use (shaders/matvec_quant.metal:25,477-506).
+// Accumulation is f32.
 #include "lc_internal.h"
 
 namespace {
@@ -217,34 +219,39 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
                 }
             }
         } else {
-            // up to 8 blocks of 32 k: f16 scale, then byte i holds k = i (low nibble) and k = i + 16 (high nibble)
+            // up to 8 blocks of 32 k: f16 scale, then byte i holds k = i (low nibble) and k = i + 16 (high nibble).
+            // The operand is the integer q - 8; each block's sum is scaled by d in f32 (exact f32 weights).
             const __half2 c1032 = __float2half2_rn(1032.0f);
             for (int bi = 0; bi < cblk; bi++) {
-                __half2 d2[2];
-                uint32_t wq[2];
+                float df[2];
+                uint32_t a[2][4];
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const uint8_t *bp = rbase[i] + (cb0 + bi) * BB;
-                    const __half d = *reinterpret_cast<const __half *>(bp);
-                    d2[i] = __half2half2(rvalid[i] ? d : __float2half(0.0f));
-                    wq[i] = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
-                }
+                    df[i] = rvalid[i] ? __half2float(*reinterpret_cast<const __half *>(bp)) : 0.0f;
+                    const uint32_t wq = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
 #pragma unroll
-                for (int part = 0; part < 2; part++) {
-                    uint32_t a[4];
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        const uint32_t codes = (wq[i] >> (4 * part)) & 0x0F0F0F0Fu;
-                        a[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032), d2[i]));
-                        a[i + 2] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032), d2[i]));
+                    for (int part = 0; part < 2; part++) {
+                        const uint32_t codes = (wq >> (4 * part)) & 0x0F0F0F0Fu;
+                        a[part][i] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032));
+                        a[part][i + 2] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032));
                     }
-                    const uint32_t xk = xb + (uint32_t)((32 * bi + 16 * part) * 2);
+                }
+                const uint32_t xk = xb + (uint32_t)(32 * bi * 2);
 #pragma unroll
-                    for (int j = 0; j < NBT; j += 2) {
+                for (int j = 0; j < NBT; j += 2) {
+                    float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int part = 0; part < 2; part++) {
                         uint32_t b[4];
-                        ldmatrix_x4(b, xk + (uint32_t)(8 * j * XS));
-                        mma16816(c[j], a, b[0], b[1]);
-                        mma16816(c[j + 1], a, b[2], b[3]);
+                        ldmatrix_x4(b, xk + (uint32_t)(16 * part * 2 + 8 * j * XS));
+                        mma16816(t0, a[part], b[0], b[1]);
+                        mma16816(t1, a[part], b[2], b[3]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        c[j][e] = fmaf(df[e >> 1], t0[e], c[j][e]);
+                        c[j + 1][e] = fmaf(df[e >> 1], t1[e], c[j + 1][e]);
                     }
                 }
             }
@@ -339,11 +346,8 @@ __global__ void __launch_bounds__(NT) qgemm_mma_kernel(const MmaParams p) {
 template <int FMT, int NBT, typename OutT>
 int launch_mma(lc_batch *b, const MmaParams &p, dim3 grid, size_t smem) {
     auto kern = qgemm_mma_kernel<FMT, NBT, OutT>;
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(NT);
@@ -479,33 +483,40 @@ __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParam
         }
 #pragma unroll
         for (int bi = 0; bi < 4; bi++) {
-            __half2 d2[4];
-            uint32_t wq[4];
+            // the operand is the integer q - 8; the block's sum is scaled by d in f32 (exact f32 weights)
+            float df[4];
+            uint32_t a[2][2][4];   // [k half of the block][fragment][register]
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint8_t *bp = rbase[i] + bi * BB;
-                const __half d = rvalid[i] ? *reinterpret_cast<const __half *>(bp) : __float2half(0.0f);
-                d2[i] = __half2half2(d);
-                wq[i] = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
-            }
+                df[i] = rvalid[i] ? __half2float(*reinterpret_cast<const __half *>(bp)) : 0.0f;
+                const uint32_t wq = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
 #pragma unroll
-            for (int part = 0; part < 2; part++) {
-                uint32_t a[2][4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t codes = (wq[i] >> (4 * part)) & 0x0F0F0F0Fu;
-                    a[i >> 1][i & 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032), d2[i]));
-                    a[i >> 1][(i & 1) + 2] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032), d2[i]));
+                for (int part = 0; part < 2; part++) {
+                    const uint32_t codes = (wq >> (4 * part)) & 0x0F0F0F0Fu;
+                    a[part][i >> 1][i & 1] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032));
+                    a[part][i >> 1][(i & 1) + 2] = h2_bits(__hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032));
                 }
-                const uint32_t xk = xb + (uint32_t)((32 * bi + 16 * part) * 2);
+            }
+            const uint32_t xk = xb + (uint32_t)(32 * bi * 2);
 #pragma unroll
-                for (int j = 0; j + 1 < NBT; j += 2) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, xk + (uint32_t)(8 * j * W_XS));
-                    mma16816(c[0][j], a[0], b[0], b[1]);
-                    mma16816(c[1][j], a[1], b[0], b[1]);
-                    mma16816(c[0][j + 1], a[0], b[2], b[3]);
-                    mma16816(c[1][j + 1], a[1], b[2], b[3]);
+            for (int j = 0; j + 1 < NBT; j += 2) {
+                uint32_t b[2][4];
+                ldmatrix_x4(b[0], xk + (uint32_t)(8 * j * W_XS));
+                ldmatrix_x4(b[1], xk + (uint32_t)(32 + 8 * j * W_XS));
+#pragma unroll
+                for (int f = 0; f < 2; f++) {
+                    float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int part = 0; part < 2; part++) {
+                        mma16816(t0, a[part][f], b[part][0], b[part][1]);
+                        mma16816(t1, a[part][f], b[part][2], b[part][3]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        c[f][j][e] = fmaf(df[2 * f + (e >> 1)], t0[e], c[f][j][e]);
+                        c[f][j + 1][e] = fmaf(df[2 * f + (e >> 1)], t1[e], c[f][j + 1][e]);
+                    }
                 }
             }
         }
@@ -531,11 +542,8 @@ template <typename OutT, int NBT>
 int launch_wide(lc_kernels *k, lc_batch *b, const WideParams &p) {
     auto kern = qgemm_mma_wide_kernel<OutT, NBT>;
     const size_t smem = (size_t)W_STAGES * W_STAGE;
-    static bool configured = false;
-    if (!configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     const int grid = p.tiles < k->ctx->sm_count ? p.tiles : k->ctx->sm_count;
     LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(W_NT), smem, b, p));
     b->dispatch_count++;

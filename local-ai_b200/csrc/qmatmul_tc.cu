@@ -23,8 +23,11 @@
 //
 // Numerics: TQ2_0 weights d*(q-1) in {-d, 0, d, 2d} are exact in f16, so the
 // result equals the CUDA-core path up to f32 summation order.  Q4_0 weights
-// d*(q-8) are rounded once to f16 (relative 2^-12), as the reference's own
-// half-precision MMA kernels do (matvec_quant.metal:590-798).
+// d*(q-8) need up to 15 significant bits; the reference's M > 8 kernel keeps
+// them in f32 (matvec_quant.metal:477-506).  Here every 128-k tile of Q4_0 runs
+// as two pipeline steps over the same activations: the f16-rounded weights, then
+// the f16 of what the rounding dropped (exact but for f16 underflow, ~3e-8
+// absolute), so the accumulated product matches the f32-weight one.
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status
 // word, skips to the TMEM release and returns.
@@ -63,8 +66,8 @@ __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
 }
 // Bounded wait; false on expiry.
-__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; i++) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -136,7 +139,8 @@ struct TcParams {
     int sb;                // activation stages (6 when they fit, else 3); weight stages are fixed at 2
     int tmem_cols;         // power of two >= max(32, NB)
     int *status;
-    long long *prof;   // optional: cycle stamps of CTA (0,0,0), for tuning
+    uint32_t wait_limit;   // polls before a barrier wait gives up
+    uint32_t extra_arrivals;   // 0; 1 in the expiry self-test: the "weights ready" barriers then expect an arrival nobody makes
 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t addr) {
@@ -173,8 +177,6 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     lc_pdl_trigger();
-    const bool prof = p.prof && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-    if (prof && tid == 0) p.prof[0] = clock64();
     int grp = 0;
     while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
     const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * TILE_ROWS, m0 = blockIdx.y * MAX_NB;
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     if (tid == 0) {
-        for (int i = 0; i < SA; i++) mbar_init(smem_u32(&a_full[i]), N_UNPACK_WARPS);
+        for (int i = 0; i < SA; i++) mbar_init(smem_u32(&a_full[i]), N_UNPACK_WARPS + p.extra_arrivals);
         for (int i = 0; i < MAX_BAR; i++) mbar_init(smem_u32(&mma_done[i]), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -200,10 +202,11 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (prof && tid == 0) p.prof[1] = clock64();
     const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+    // pipeline steps per 128-k tile: Q4_0 runs each tile twice (rounded weights, then the rounding remainder)
+    constexpr int REP = (FMT == FMT_Q4_0) ? 2 : 1;
     const int nphases = (kbe - kbs + PB - 1) / PB;
-    const int total_tiles = ((kbe - kbs) * BE) / KT;
+    const int total_tiles = ((kbe - kbs) * BE) / KT * REP;
     const int kg_base = kbs * BE;   // first k of this CTA
 
     if (warp < N_UNPACK_WARPS) {
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         const int rows_valid = p.m - m0;
         auto load_b = [&](int tl) {
             uint32_t dst = smem_u32(b_s + (tl % SB) * B_STAGE) + (uint32_t)(warp * B_LBO + 16 * lane);
-            const __half *src = x_lane + (size_t)tl * KT;
+            const __half *src = x_lane + (size_t)(tl / REP) * KT;
             for (int mrow = lane; mrow < NB; mrow += 32) {
                 const bool ok = mrow < rows_valid;
                 cp_async16(dst, ok ? (const void *)src : (const void *)p.x, ok ? 16u : 0u);
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         // MMAs of tile tl have completed (frees weight stage tl % SA and activation stage tl % SB).
         auto mma_finished = [&](int tl) -> bool {
             uint32_t ok = 1;
-            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[tl % MAX_BAR]), (uint32_t)((tl / MAX_BAR) & 1)) ? 1u : 0u;
+            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[tl % MAX_BAR]), (uint32_t)((tl / MAX_BAR) & 1), p.wait_limit) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             return ok && !*abort_flag;
         };
@@ -264,8 +267,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             }
             cp_async_wait<0>();
             __syncwarp();
-            if (prof && tid == 0 && ph == 0) p.prof[2] = clock64();
-            const int ntiles = ((kb1 - kb0) * BE) / KT;
+            const int ntiles = ((kb1 - kb0) * BE) / KT * REP;
             // Per-thread constants of this phase: where each of its rows starts in the raw area (the row's
             // 16-byte skew differs from row to row) and whether the row exists.
             constexpr int NIT = (FMT == FMT_TQ2_0) ? ROWS_PER_WARP / 2 : ROWS_PER_WARP;
@@ -313,10 +315,12 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                         }
                     }
                 } else {
-                    // tile t = blocks 4t..4t+3 of the phase; lane = (block b, 2-byte piece hh):
-                    // low nibbles k = 32b + 2hh + {0,1}, high nibbles 16 further (two k-chunks on).
+                    // step t = blocks 4(t/2)..4(t/2)+3 of the phase, rounded weights (t even) or remainder (t odd);
+                    // lane = (block b, 2-byte piece hh): low nibbles k = 32b + 2hh + {0,1}, high nibbles 16 further
+                    // (two k-chunks on).
                     const int b = lane >> 3, hh = lane & 7;
-                    const int boff = (4 * t + b) * BB;
+                    const int boff = (4 * (t >> 1) + b) * BB;
+                    const bool rem = t & 1;
                     uint8_t *dst = ast + 16 * r_base + (hh & 3) * 4 + (4 * b + (hh >> 2)) * A_LBO;
                     uint32_t w16[NIT];
                     __half dd[NIT];
@@ -329,9 +333,16 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
 #pragma unroll
                     for (int i = 0; i < NIT; i++) {
                         const __half2 d2 = __half2half2(valid[i] ? dd[i] : __float2half(0.0f));
+                        const float df = __low2float(d2);
                         const uint32_t tlo = __byte_perm(w16[i], 0u, 0x4140);
-                        const __half2 lo = __hmul2(__hsub2(bits_h2((tlo & 0x000F000Fu) | 0x64006400u), c1032), d2);
-                        const __half2 hi = __hmul2(__hsub2(bits_h2(((tlo >> 4) & 0x000F000Fu) | 0x64006400u), c1032), d2);
+                        const __half2 qlo = __hsub2(bits_h2((tlo & 0x000F000Fu) | 0x64006400u), c1032);          // q - 8, exact
+                        const __half2 qhi = __hsub2(bits_h2(((tlo >> 4) & 0x000F000Fu) | 0x64006400u), c1032);
+                        __half2 lo = __hmul2(qlo, d2), hi = __hmul2(qhi, d2);                                     // rounded weights
+                        if (rem) {   // what the rounding dropped: d (q - 8) is exact in f32
+                            const float2 ql = __half22float2(qlo), qh = __half22float2(qhi), rl = __half22float2(lo), rh = __half22float2(hi);
+                            lo = __floats2half2_rn(ql.x * df - rl.x, ql.y * df - rl.y);
+                            hi = __floats2half2_rn(qh.x * df - rh.x, qh.y * df - rh.y);
+                        }
                         *reinterpret_cast<uint32_t *>(dst + 16 * i) = h2_bits(lo);
                         *reinterpret_cast<uint32_t *>(dst + 16 * i + 2 * A_LBO) = h2_bits(hi);
                     }
@@ -343,7 +354,6 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
                 if (lane == 0) mbar_arrive(smem_u32(&a_full[s]));
             }
         }
-        if (prof && tid == 0) p.prof[3] = clock64();
     } else {
         // ============================ MMA issue (one warp) ============================
         bool dead = false;
@@ -351,7 +361,7 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         for (int tile = 0; tile < total_tiles && !dead; tile++) {
             const int s = tile % SA, use = tile / SA;
             uint32_t ok = 1;
-            if (lane == 0) ok = mbar_wait(smem_u32(&a_full[s]), (uint32_t)(use & 1)) ? 1u : 0u;
+            if (lane == 0) ok = mbar_wait(smem_u32(&a_full[s]), (uint32_t)(use & 1), p.wait_limit) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
             if (lane == 0) {
@@ -374,15 +384,13 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
         if (!dead && total_tiles > 0) {
             const int last = total_tiles - 1;
             uint32_t ok = 1;
-            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[last % MAX_BAR]), (uint32_t)((last / MAX_BAR) & 1)) ? 1u : 0u;
+            if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[last % MAX_BAR]), (uint32_t)((last / MAX_BAR) & 1), p.wait_limit) ? 1u : 0u;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) *abort_flag = 1;
         }
-        if (prof && lane == 0) p.prof[4] = clock64();
     }
     tc_fence_before();
     __syncthreads();
-    if (prof && tid == 0) p.prof[5] = clock64();
     tc_fence_after();
     const bool failed = *abort_flag != 0;
     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
@@ -405,7 +413,6 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             }
         }
     }
-    if (prof && tid == 0) p.prof[6] = clock64();
     if (p.ks > 1 && !failed) {
         // Deterministic split-K: every split stores its f32 partial tile; the last CTA to arrive adds the
         // partials in split order and writes the result.
@@ -450,7 +457,6 @@ __global__ void __launch_bounds__(NT2, 1) qgemm_tc_kernel(const TcParams p) {
             }
         }
     }
-    if (prof && tid == 0) p.prof[7] = clock64();
     if (failed && tid == 0) atomicExch(p.status, 1);
     tc_fence_before();
     __syncthreads();
@@ -467,11 +473,8 @@ int launch_tc(lc_kernels *k, lc_batch *b, TcParams &p, dim3 grid) {
     p.sb = need(6) <= k->ctx->smem_optin ? 6 : 3;
     const size_t smem = need(p.sb);
     auto kern = qgemm_tc_kernel<FMT, OutT>;
-    static size_t configured = 0;
-    if (smem > configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT2), smem, b, p));
     LC_CHECK_LAUNCH("qgemm_tcgen05");
     b->dispatch_count++;
@@ -509,7 +512,8 @@ int lc_qgemm_tcgen05_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, c
     p.tmem_cols = cols;
     p.sb = 3;
     p.status = k->dev_status;
-    p.prof = getenv("LOCAL_CUDA_TC_PROFILE") ? (long long *)(k->dev_status + 2) : nullptr;
+    p.wait_limit = k->test_wait_expiry ? 4096u : WAIT_LIMIT;
+    p.extra_arrivals = k->test_wait_expiry ? 1u : 0u;
     const int mtiles = (int)((m + MAX_NB - 1) / MAX_NB);
     // split-K so that small-n projections still fill the GPU: each split gets whole blocks and at least two k-tiles.
     const int min_blocks = fmt == FMT_Q4_0 ? 8 : 1;   // 8 Q4_0 blocks = 256 k = 2 k-tiles; 1 TQ2_0 block = 2 k-tiles
@@ -550,16 +554,10 @@ extern "C" int lc_kernels_device_status(lc_kernels *k, int *status) {
     if (!k || !status) return lc_fail(LC_ERR_INVALID_ARGUMENT, "lc_kernels_device_status: NULL argument");
     LC_CUDA_TRY(cudaMemcpyAsync(status, k->dev_status, sizeof(int), cudaMemcpyDeviceToHost, k->ctx->stream));
     LC_CUDA_TRY(cudaStreamSynchronize(k->ctx->stream));
+    if (*status == LC_DEV_STATUS_POSITION)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT,
+                       "a position in a device buffer pointed past its lane's pool rows (the row was not written / the "
+                       "context was clamped)");
     if (*status) return lc_fail(LC_ERR_TIMEOUT, "a device-side bounded wait expired (status %d)", *status);
     return LC_OK;
 }
-
-// Tuning aid: the eight cycle stamps the tensor-core matmul records for its first CTA when
-// LOCAL_CUDA_TC_PROFILE is set (entry, set-up done, weights landed, unpack done, MMAs drained,
-// after the CTA barrier, after the accumulator read-out, after the split-K merge).
-extern "C" __attribute__((visibility("default"))) int lc_debug_tc_profile(lc_kernels *k, long long *out8) {
-    if (!k || !out8) return LC_ERR_INVALID_ARGUMENT;
-    cudaStreamSynchronize(k->ctx->stream);
-    return cudaMemcpy(out8, k->dev_status + 2, 8 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? LC_OK : LC_ERR_CUDA;
-}
-

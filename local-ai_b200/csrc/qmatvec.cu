@@ -220,11 +220,8 @@ int launch_qgemv(lc_kernels *k, lc_batch *b, const uint8_t *w, size_t w_bytes, c
     const size_t xbytes = XSMEM ? (((size_t)MT * K * 2 + 15) & ~(size_t)15) : 0;
     const size_t smem = xbytes + (size_t)rpc * rb + 32;
     auto kern = qgemv_kernel<FMT, MT, OutT, XSMEM>;
-    static size_t configured = 0;  // per instantiation
-    if (smem > 48 * 1024 && smem > configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static lc_smem_optin optin;  // per instantiation
+    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     int gx = k->ctx->sm_count * 4;
     if (gx > nchunks) gx = nchunks;
     dim3 grid(gx, (m + MT - 1) / MT);

@@ -259,11 +259,8 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
 template <int FMT, typename OutT, int UPQ>
 int launch_stream_u(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
     auto kern = qgemv_mma_stream_kernel<FMT, OutT, UPQ>;
-    static size_t configured = 0;
-    if (smem > configured) {
-        LC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     const int grid = p.groups < k->ctx->sm_count ? p.groups : k->ctx->sm_count;
     LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT), smem, b, p));
     b->dispatch_count++;

@@ -106,7 +106,7 @@ __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *
                                  const float *__restrict__ signs, uint8_t *__restrict__ packed,
                                  __half *__restrict__ norms, const uint32_t *__restrict__ positions,
                                  unsigned hd, unsigned n_kv, unsigned lane_capacity, unsigned bits,
-                                 unsigned position, unsigned ring, int norm_mode) {
+                                 unsigned position, unsigned ring, int norm_mode, int *status) {
     lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
     lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[MAX_HD];
@@ -119,6 +119,10 @@ __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *
     if (BATCHED) {
         const unsigned pos = positions[row];
         const unsigned ppos = ring ? pos % ring : pos;
+        if (ppos >= lane_capacity) {   // a device-resident position past the lane's rows: write nothing, report
+            if (t == 0) atomicExch(status, LC_DEV_STATUS_POSITION);
+            return;
+        }
         slot = ((size_t)row * lane_capacity + ppos) * n_kv + head;
     } else {
         const unsigned logical = position + row;
@@ -142,7 +146,7 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
                                 uint8_t *__restrict__ k_packed, __half *__restrict__ k_norms,
                                 uint8_t *__restrict__ v_packed, __half *__restrict__ v_norms, unsigned hd, unsigned n_kv,
                                 unsigned lane_capacity, unsigned bits, unsigned ring, float eps, float theta,
-                                float rotary_factor, int norm_mode) {
+                                float rotary_factor, int norm_mode, int *status) {
     lc_pdl_trigger();
     __shared__ float sh[MAX_HD];
     __shared__ float red[MAX_HD];
@@ -190,7 +194,12 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
         qrow[t] = __float2half_rn(xr);
         return;
     }
-    const size_t slot = ((size_t)row * lane_capacity + (ring ? pos % ring : pos)) * n_kv + head;
+    const unsigned ppos = ring ? pos % ring : pos;
+    if (ppos >= lane_capacity) {   // a device-resident position past the lane's rows: write nothing, report
+        if (t == 0) atomicExch(status, LC_DEV_STATUS_POSITION);
+        return;
+    }
+    const size_t slot = ((size_t)row * lane_capacity + ppos) * n_kv + head;
     const unsigned code_bytes = (hd * bits + 7) >> 3;
     encode_row(xr, t, hd, bits, levels, signs, norm_mode, (role == 1 ? k_packed : v_packed) + slot * code_bytes,
                (role == 1 ? k_norms : v_norms) + slot, sh, red, code_sh, &norm_sh);
@@ -372,7 +381,7 @@ int lc_encode_kv_turboquant_into(lc_kernels *k, lc_batch *b, const lc_buf *input
     if (groups == 0) return LC_OK;
     LC_LAUNCH_CHECKED(lc_launch(encode_kv_kernel<false>, dim3((unsigned)groups), dim3(head_dim), 0, b, (const __half *)input->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
         (uint8_t *)packed->dptr, (__half *)norms->dptr, nullptr, head_dim, n_kv_heads, 0, bits, position,
-        ring_capacity, k->kv_norm_mode));
+        ring_capacity, k->kv_norm_mode, k->dev_status));
     LC_CHECK_LAUNCH("encode_kv_turboquant");
     b->dispatch_count++;
     return LC_OK;
@@ -412,7 +421,7 @@ int lc_encode_kv_turboquant_batched_into(lc_kernels *k, lc_batch *b, const lc_bu
     if (groups == 0) return LC_OK;
     LC_LAUNCH_CHECKED(lc_launch(encode_kv_kernel<true>, dim3((unsigned)groups), dim3(head_dim), 0, b, (const __half *)input->dptr, (const float *)levels->dptr, (const float *)signs->dptr,
         (uint8_t *)packed->dptr, (__half *)norms->dptr, (const uint32_t *)positions->dptr, head_dim, n_kv_heads,
-        lane_capacity, bits, 0, ring_capacity, k->kv_norm_mode));
+        lane_capacity, bits, 0, ring_capacity, k->kv_norm_mode, k->dev_status));
     LC_CHECK_LAUNCH("encode_kv_turboquant_batched");
     b->dispatch_count++;
     return LC_OK;
@@ -507,7 +516,7 @@ static int kv_write_common(const char *name, lc_kernels *k, lc_batch *b, lc_buf 
                                 (const float *)levels->dptr, (const float *)signs->dptr, (uint8_t *)k_packed->dptr,
                                 (__half *)k_norms->dptr, (uint8_t *)v_packed->dptr, (__half *)v_norms->dptr, head_dim,
                                 n_kv_heads, lane_capacity, bits, ring_capacity, eps, rope_theta, partial_rotary_factor,
-                                k->kv_norm_mode));
+                                k->kv_norm_mode, k->dev_status));
     b->dispatch_count++;
     return LC_OK;
 }

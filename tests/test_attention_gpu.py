@@ -230,8 +230,9 @@ def test_attention_sliding(la, orc, ctx, kernels):
 
 
 def test_attention_is_convex_combination_at_32k(la, orc, ctx, kernels):
-    """Size-independent properties at the benchmark context (32768 rows, tq2): with every V row equal
-    the output equals that row whatever the scores; and splits agree with the oracle on a strided subsample."""
+    """Size-independent property at the benchmark context (32768 rows, tq2): with every V row equal the output
+    equals that row whatever the scores (the oracle comparison at this context is
+    test_attention_at_the_benchmark_contexts)."""
     hd, n_q, n_kv, bits, total = 256, 8, 1, 2, 32768
     levels, signs = la.tq_levels(hd, bits), la.tq_signs(hd, la.TQ_SEED)
     cb = la.tq_code_bytes(hd, bits)
@@ -251,6 +252,69 @@ def test_attention_is_convex_combination_at_32k(la, orc, ctx, kernels):
     row = np.float32(one_n) * levels[(np.unpackbits(one_c, bitorder="little").reshape(hd, bits) * (1 << np.arange(bits))).sum(1)]
     for h in range(n_q):
         rel_close(got[h], row, 1e-3, f"constant-V head {h}")
+
+def random_cache(la, hd, bits, rows, seed):
+    """Random code bytes and norms ~ |N(0, I_hd)|: the attention kernels and the oracle consume codes and norms, so a
+    parity check at benchmark sizes does not need rows that went through the encoder."""
+    cb = la.tq_code_bytes(hd, bits)
+    pad = (-rows * cb) % 8
+    kc = la.synth.splitmix64(seed, (rows * cb + pad) // 8).view(np.uint8)[:rows * cb].copy()
+    vc = la.synth.splitmix64(seed + 1, (rows * cb + pad) // 8).view(np.uint8)[:rows * cb].copy()
+    kn = (np.sqrt(hd) * la.synth.uniform(seed + 2, rows, 0.8, 1.2)).astype(np.float16)
+    vn = (np.sqrt(hd) * la.synth.uniform(seed + 3, rows, 0.8, 1.2)).astype(np.float16)
+    return kc, kn, vc, vn
+
+
+@pytest.mark.parametrize("bits,total", [(2, 4096), (2, 32768), (2, 131072), (3, 32768), (4, 32768)])
+def test_attention_at_the_benchmark_contexts(la, orc, ctx, kernels, bits, total):
+    """Batch 1 at the contexts of the attention benchmark configuration (4096, 32768, 131072; tq3 and tq4 at 32768),
+    every output element against the oracle: the rotated-space entry point at 1e-3 and the fused f16 entry point at
+    2e-3, softmax scale 1/sqrt(256)."""
+    hd, n_q, n_kv = 256, 8, 1
+    levels, signs = la.tq_levels(hd, bits), la.tq_signs(hd, la.TQ_SEED)
+    kc, kn, vc, vn = random_cache(la, hd, bits, total, 9000 + bits)
+    f = lambda a: la.CudaBuffer.from_slice(ctx, a)
+    kcb, knb, vcb, vnb, lvb, sgb = f(kc), f(kn), f(vc), f(vn), f(levels), f(signs)
+    q16 = la.synth.normal_f16((n_q, hd), 9100 + bits)
+    rq = orc.hadamard_rotate(q16.astype(np.float32), signs, hd, n_q, True, False)
+    out = Guarded(la, ctx, n_q * hd * 4)
+    b = la.CommandBatch.new(ctx)
+    kernels.flash_attention_tq_into(b, f(rq), kcb, knb, vcb, vnb, lvb, out.view, hd, total, total - 1, n_q, n_kv, 0, bits, 0, 0.0625)
+    b.commit_and_wait()
+    want = orc.flash_attention_tq(rq, kc, kn, vc, vn, levels, hd, total, total - 1, n_q, n_kv, 0, bits, 0, 0.0625)
+    rel_close(out.read(np.float32), want, 1e-3, f"flash_attention_tq tq{bits} at {total}")
+    fo = Guarded(la, ctx, n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.tq_attention_into(b, f(q16), kcb, knb, vcb, vnb, lvb, sgb, fo.view, hd, total, total - 1, n_q, n_kv, 0, bits, 0, 0.0625)
+    b.commit_and_wait()
+    wantf = orc.tq_attention_fused(q16, kc, kn, vc, vn, levels, signs, None, hd, 0, n_q, n_kv, 0, bits, 1, 0, 0.0625,
+                                   total, total - 1).astype(np.float32)
+    rel_close(fo.read(np.float16), wantf, 2e-3, f"tq_attention tq{bits} at {total}")
+
+
+def test_attention_64_lanes_at_8193_keys_lane_by_lane(la, orc, ctx, kernels):
+    """The attention launch of the batch-64 decode benchmark (64 lanes, every lane at position 8192, tq2, the split
+    count the launch heuristic picks for it) with five lanes compared against the oracle element by element."""
+    hd, n_q, n_kv, bits, lanes, cap, pos = 256, 8, 1, 2, 64, 8192 + 512, 8192
+    levels, signs = la.tq_levels(hd, bits), la.tq_signs(hd, la.TQ_SEED)
+    cb = la.tq_code_bytes(hd, bits)
+    kc, kn, vc, vn = random_cache(la, hd, bits, lanes * cap, 9500)
+    f = lambda a: la.CudaBuffer.from_slice(ctx, a)
+    q16 = la.synth.normal_f16((lanes, n_q, hd), 9600)
+    positions = np.full(lanes, pos, np.uint32)
+    fo = Guarded(la, ctx, lanes * n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.tq_attention_batched_into(b, f(q16), f(kc), f(kn), f(vc), f(vn), f(levels), f(signs), fo.view, f(positions), hd,
+                                      cap, n_q, n_kv, 0, bits, lanes, 0, 0.0625)
+    b.commit_and_wait()
+    got = fo.read(np.float16).astype(np.float32).reshape(lanes, n_q * hd)
+    assert np.all(np.isfinite(got))
+    for lane in (0, 1, 21, 42, 63):
+        rows = slice(lane * cap, (lane + 1) * cap)
+        crows = slice(lane * cap * cb, (lane + 1) * cap * cb)
+        want = orc.tq_attention_fused(q16[lane], kc[crows], kn[rows], vc[crows], vn[rows], levels, signs, None, hd, 0, n_q,
+                                      n_kv, 0, bits, 1, 0, 0.0625, pos + 1, pos).astype(np.float32)
+        rel_close(got[lane], want, 2e-3, f"lane {lane} of 64 at 8193 keys")
 
 
 @pytest.mark.gpu
@@ -297,3 +361,66 @@ np.save(sys.argv[1], out.as_slice(np.uint16, lanes * n_q * hd)); print("launches
 def entry_root():
     from pathlib import Path
     return Path(__file__).resolve().parent.parent
+
+
+def test_query_buffer_at_an_odd_offset_takes_the_general_kernel(la, orc, ctx, kernels):
+    """The tensor-core kernel loads the query and the signs as 16-byte vectors.  A query wrapped two bytes into an
+    allocation must not reach it: the call is served by the CUDA-core kernel and still meets the oracle."""
+    hd, n_q, n_kv, bits, total = 256, 8, 1, 2, 700
+    c = Cache(la, orc, ctx, hd, n_kv, bits, total, seed=4242)
+    c.fill_single(total, 0)
+    kc, kn, vc, vn, lv, sg = c.device()
+    q16 = la.synth.normal_f16((n_q, hd), 4243)
+    raw = la.CudaBuffer.empty(ctx, n_q * hd * 2 + 16)
+    raw.copy_from_bytes(q16.view(np.uint8).reshape(-1), offset=2)
+    qv = la.CudaBuffer.wrap(ctx, raw.device_ptr + 2, n_q * hd * 2)
+    fo = Guarded(la, ctx, n_q * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    kernels.tq_attention_into(b, qv, kc, kn, vc, vn, lv, sg, fo.view, hd, total, total - 1, n_q, n_kv, 0, bits, 0, 0.0625)
+    b.commit_and_wait()
+    want = orc.tq_attention_fused(q16, c.kc, c.kn, c.vc, c.vn, c.levels, c.signs, None, hd, 0, n_q, n_kv, 0, bits, 1, 0,
+                                  0.0625, total, total - 1).astype(np.float32)
+    rel_close(fo.read(np.float16), want, 2e-3, "query at a 2-byte offset")
+    # an f32 rotated query that is not even 4-byte aligned is refused with a status
+    rqv = la.CudaBuffer.wrap(ctx, raw.device_ptr + 2, 16)
+    b = la.CommandBatch.new(ctx)
+    with pytest.raises(la.Error) as ei:
+        kernels.flash_attention_tq_into(b, rqv, kc, kn, vc, vn, lv, fo.view, 64, 1, 0, 1, 1, 0, bits, 0, 1.0)
+    assert ei.value.kind == "InvalidArgument"
+    b.commit_and_wait()
+
+
+def test_captured_graph_survives_later_scratch_growth(la, orc, ctx):
+    """A captured graph keeps the split-K scratch address it was recorded with.  A later, larger eager call on the same
+    kernels object makes the scratch grow; the old block must stay alive, so replaying the graph afterwards still
+    gives the recorded call's result."""
+    hd, n_q, n_kv, bits = 128, 4, 1, 3
+    k2 = la.Kernels.new(ctx)
+    small = Cache(la, orc, ctx, hd, n_kv, bits, 600, seed=611)
+    small.fill_single(600, 0)
+    kc, kn, vc, vn, lv, sg = small.device()
+    q16 = la.synth.normal_f16((n_q, hd), 612)
+    qb = la.CudaBuffer.from_slice(ctx, q16)
+    out = la.CudaBuffer.empty(ctx, n_q * hd * 2)
+    call = lambda b: k2.tq_attention_into(b, qb, kc, kn, vc, vn, lv, sg, out, hd, 600, 599, n_q, n_kv, 0, bits, 0, 0.125)
+    b = la.CommandBatch.new(ctx)
+    call(b)                      # sizes the scratch for this shape
+    b.commit_and_wait()
+    first = out.as_slice(np.uint16).copy()
+    b = la.CommandBatch.capture(ctx)
+    call(b)
+    graph = b.end_capture()
+    # a much larger call: 64 heads of 512 and a long context need far more partials
+    big = Cache(la, orc, ctx, 512, 8, 2, 9000, seed=613)
+    bkc, bkn, bvc, bvn, blv, bsg = big.device()
+    bq = la.CudaBuffer.from_slice(ctx, la.synth.normal_f16((64, 512), 614))
+    bout = la.CudaBuffer.empty(ctx, 64 * 512 * 2)
+    b = la.CommandBatch.new(ctx)
+    k2.tq_attention_into(b, bq, bkc, bkn, bvc, bvn, blv, bsg, bout, 512, 9000, 8999, 64, 8, 0, 2, 0, 1.0)
+    b.commit_and_wait()
+    out.zero()
+    graph.launch()
+    ctx.synchronize()
+    assert np.array_equal(out.as_slice(np.uint16), first)
+    graph.destroy()
+    k2.close()

@@ -165,3 +165,90 @@ def test_reset_lane_zeroes_its_rows(la, orc, ctx, kernels):
         rows = kv["lane_rows"]
         kn = kv["k_norms"].as_slice(np.float16).reshape(2, rows)
         assert kn[0, 0] != 0 and np.all(kn[1] == 0)
+
+
+# ---- the kernel routes the batch-64 benchmark takes ----
+def bench_route_cfg(la, max_lanes, max_context=1024, vocab=76032):
+    """The benchmark model's layer shape (hidden 1536, 8 q / 1 kv heads of 256, GeGLU 6144, tq2 KV, 512-slot ring)
+    cut to two layers -- one sliding-window, one full -- and a vocabulary just large enough for the persistent
+    512-row projection kernel and the chunked argmax."""
+    return la.ModelConfig(hidden=1536, n_q_heads=8, n_kv_heads=1, head_dim=256, inter=6144, vocab=vocab, n_layers=2,
+                          kv_bits=2, max_lanes=max_lanes, max_context=max_context, swa_window=512, swa_ring=512,
+                          full_every=2, rms_eps=1e-6, rope_theta=1e6, softmax_scale=1.0 / 16.0,
+                          embed_scale=float(np.sqrt(np.float32(1536))))
+
+
+@pytest.fixture(scope="module")
+def bench_route_model(la, orc, ctx, kernels):
+    cfg = bench_route_cfg(la, 64)
+    layers = [la.model.synth_layer(cfg, i, seed=9) for i in range(cfg.n_layers)]
+    emb, fnorm = la.model.synth_embedding(cfg, seed=9)
+    gm = la.DecodeModel(ctx, kernels, cfg)
+    for i, t in enumerate(layers):
+        gm.set_layer(i, t)
+    gm.set_embedding(emb, fnorm)
+    geo = []
+    for i in range(cfg.n_layers):
+        kv = gm.kv_buffers(i)
+        geo.append((kv["lane_rows"], kv["ring"], kv["window"]))
+    assert geo == [(512, 512, 512), (cfg.max_context, 0, 0)]
+    om = orc.OracleModel(cfg, layers, emb, fnorm, geo)
+    # history: every lane's pools hold properly encoded rows for positions 0 .. 899 (the ring has wrapped)
+    levels, signs = orc.tq_levels(cfg.head_dim, cfg.kv_bits), orc.tq_signs(cfg.head_dim, la.TQ_SEED)
+    hist = 900
+    for li, pool in enumerate(om.pools):
+        lane_rows, ring, _ = geo[li]
+        cb = la.tq_code_bytes(cfg.head_dim, cfg.kv_bits)
+        for lane in range(cfg.max_lanes):
+            for j, (codes, norms) in enumerate((("k_codes", "k_norms"), ("v_codes", "v_norms"))):
+                rows = la.synth.normal_f16((hist, 1, cfg.head_dim), 7000 + 1000 * li + 10 * lane + j)
+                c = pool[codes][lane * lane_rows * cb:(lane + 1) * lane_rows * cb]
+                n = pool[norms][lane * lane_rows:(lane + 1) * lane_rows]
+                orc.encode_kv(rows, levels, signs, c, n, cfg.head_dim, 1, hist, cfg.kv_bits, 0, ring)
+    return cfg, gm, om, hist
+
+
+@pytest.mark.parametrize("lanes", [64, 33, 9])
+def test_step_at_the_benchmark_kernel_routes(la, orc, ctx, kernels, bench_route_model, lanes):
+    """One teacher-forced step against the oracle on the shapes the batch-64 benchmark runs, so that the kernels
+    the benchmark's graph is made of are checked in composition: the tcgen05 decode projections (grouped Q/K/V, O,
+    fused GeGLU, down), the fused q/k norm + RoPE + KV write, tensor-core attention over tq2 codes (ragged
+    positions, a wrapped 512-slot ring and a full layer), the norm pairs, the persistent 512-row vocabulary
+    projection (more than 32 lanes) and the chunked argmax.  Pools are identical before the step; logits must agree
+    to 2e-3 of the logit scale when the freshly written KV rows come out byte-identical, else within the
+    reference's own envelope (pipeline/batched.rs:471-477, 701-725)."""
+    cfg, gm, om, hist = bench_route_model
+    sync_pools(gm, om)
+    rng = np.random.default_rng(40 + lanes)
+    tokens = rng.integers(0, cfg.vocab, lanes).astype(np.uint32)
+    positions = (hist - rng.integers(0, 300, lanes)).astype(np.uint32)    # ragged, all past the ring's first wrap
+    positions[0] = hist
+    want, want_h = om.decode_batch_step(tokens, positions)
+    tb, pb = la.CudaBuffer.from_slice(ctx, tokens), la.CudaBuffer.from_slice(ctx, positions)
+    nt = la.CudaBuffer.empty(ctx, lanes * 4)
+    b = la.CommandBatch.new(ctx)
+    gm.decode_batch_step_into(b, tb, pb, lanes, True, nt)
+    # embed, first norm, 2 x (Q/K/V, q/k/v post, attention split + merge, O, norm pair, GeGLU, down, norm pair),
+    # vocabulary, argmax: the grouped and fused forms were taken
+    assert b.dispatch_count() == 2 + 2 * 9 + 2
+    b.commit_and_wait()
+    got = gm.logits_buffer().as_slice(np.float32, lanes * cfg.vocab).reshape(lanes, cfg.vocab)
+    got_h = gm.hidden_buffer().as_slice(np.float16, lanes * cfg.hidden).reshape(lanes, cfg.hidden)
+    got_tok = nt.as_slice(np.uint32)
+    mism = 0
+    for i, pool in enumerate(om.pools):
+        kv = gm.kv_buffers(i)
+        for name in ("k_codes", "v_codes", "k_norms", "v_norms"):
+            mism += int(np.sum(kv[name].as_slice(np.uint8) != pool[name].view(np.uint8)))
+    assert np.all(np.isfinite(got))
+    scale = max(1.0, float(np.abs(want).max()))
+    err = float(np.abs(got - want).max()) / scale
+    tol = 2e-3 if mism == 0 else 0.15
+    assert err <= tol, f"{lanes} lanes: logits off by {err:.3e} of scale with {mism} differing KV bytes"
+    argmax_consistent(got_tok, want, tol * scale)
+    assert np.array_equal(got_tok, np.argmax(got, axis=1).astype(np.uint32)), "device argmax vs its own logits"
+    written = cfg.n_layers * 2 * lanes * (cfg.head_dim * cfg.kv_bits // 8 + 2)
+    assert mism <= 0.01 * written, f"{mism} of {written} freshly written KV bytes differ"
+    if mism == 0:
+        hs = max(1.0, float(np.abs(want_h.astype(np.float32)).max()))
+        assert np.abs(got_h.astype(np.float32) - want_h.astype(np.float32)).max() <= 4e-3 * hs

@@ -48,3 +48,26 @@ def test_lognormal_contexts(la):
     c = la.synth.lognormal_contexts(512, 9)
     assert c.min() >= 16 and c.max() <= 131072
     assert 1500 < np.median(c) < 2800
+
+
+def test_reference_arm_and_gpu_arm_build_the_same_model(la):
+    """oracle/synth_model.py restates the package's seeding rule so that the CPU reference arm of the benchmark does
+    not need the CUDA library; both arms must time the same weights, byte for byte."""
+    import importlib.util
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("orc_synth_model", root / "oracle" / "synth_model.py")
+    sm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sm)
+    cfg = la.ModelConfig(hidden=512, n_q_heads=4, n_kv_heads=1, head_dim=128, inter=1024, vocab=640, n_layers=6,
+                         kv_bits=2, max_lanes=2, max_context=700, swa_window=512, swa_ring=512, full_every=5,
+                         rms_eps=1e-6, rope_theta=1e6, softmax_scale=0.125, embed_scale=1.0)
+    layers, emb, fnorm, geo = sm.build(la.synth, cfg, 188, seed=4)
+    for i, t in enumerate(layers):
+        want = la.model.synth_layer(cfg, i, seed=4)
+        assert set(t) == set(want)
+        for name in want:
+            assert t[name].dtype == want[name].dtype and np.array_equal(t[name], want[name]), (i, name)
+    e2, f2 = la.model.synth_embedding(cfg, seed=4)
+    assert np.array_equal(emb, e2) and np.array_equal(fnorm, f2)
+    assert geo[4] == (cfg.max_context, 0, 0) and geo[0] == (512, 512, 512)

@@ -211,3 +211,47 @@ def test_encode_decode_round_trip_at_scale(la, orc, ctx, kernels):
     assert np.allclose(norms, np.linalg.norm(xf, axis=1), rtol=2e-3)
     cos = np.sum(xh * xf, axis=1) / (np.linalg.norm(xh, axis=1) * np.linalg.norm(xf, axis=1))
     assert cos.min() > 0.90 and cos.mean() > 0.93
+
+
+def test_device_position_past_the_lane_rows_is_skipped_and_reported(la, orc, ctx):
+    """Positions of the per-lane entry points live in a device buffer the host cannot check.  A lane whose position lies
+    past its pool rows (no ring) must not be written -- its neighbours' rows and the guard band stay untouched -- the
+    other lanes are encoded as usual, attention over that lane is clamped to the rows that exist, and the kernels
+    object's status word reports it as InvalidArgument."""
+    import ctypes as C
+    hd, n_kv, bits, cap, n_lanes = 256, 1, 2, 8, 3
+    k2 = la.Kernels.new(ctx)
+    levels, signs = codec(la, orc, hd, bits)
+    cb = la.tq_code_bytes(hd, bits)
+    x = la.synth.normal_f16((n_lanes, n_kv, hd), seed=77)
+    positions = np.array([3, 8 + 5, 7], np.uint32)          # lane 1 points 6 rows past its 8
+    rows = n_lanes * cap
+    packed, norms = Guarded(la, ctx, rows * cb), Guarded(la, ctx, rows * 2)
+    packed.buf.zero(0, rows * cb)
+    norms.buf.zero(0, rows * 2)
+    d = lambda a: la.CudaBuffer.from_slice(ctx, a)
+    lv, sg, pb = d(levels), d(signs), d(positions)
+    b = la.CommandBatch.new(ctx)
+    k2.encode_kv_turboquant_batched_into(b, d(x), lv, sg, packed.view, norms.view, pb, hd, n_kv, cap, bits, n_lanes, 0)
+    b.commit_and_wait()
+    got_c, got_n = packed.read(np.uint8).reshape(rows, cb), norms.read(np.uint16)
+    want_c, want_n = np.zeros(rows * cb, np.uint8), np.zeros(rows, np.float16)
+    ok = np.array([3, 0, 7], np.uint32)                       # the oracle encodes lanes 0 and 2 only
+    orc.encode_kv_batched(x, levels, signs, want_c, want_n, ok, hd, n_kv, cap, bits, n_lanes, 0)
+    want_c = want_c.reshape(rows, cb)
+    want_c[cap + 0] = 0
+    want_n[cap + 0] = 0
+    assert np.array_equal(got_c, want_c) and np.array_equal(got_n, want_n.view(np.uint16))
+    # attention with the same positions: finite output, lane 1 clamped to its 8 rows (all zero norms here)
+    q = la.synth.normal_f16((n_lanes, 8, hd), seed=78)
+    out = Guarded(la, ctx, n_lanes * 8 * hd * 2)
+    b = la.CommandBatch.new(ctx)
+    k2.tq_attention_batched_into(b, d(q), packed.view, norms.view, packed.view, norms.view, lv, sg, out.view, pb, hd, cap,
+                                 8, n_kv, 0, bits, n_lanes, 0, 0.0625)
+    b.commit_and_wait()
+    assert np.all(np.isfinite(out.read(np.float16).astype(np.float32)))
+    st = C.c_int(0)
+    with pytest.raises(la.Error) as ei:
+        k2.kernels_device_status(C.addressof(st))
+    assert ei.value.kind == "InvalidArgument" and st.value == 3
+    k2.close()
