@@ -5,24 +5,28 @@
 //
 // A decode projection is a few microseconds of work that sits behind the kernel before it, so the kernel is built
 // around the length of the dependent chain after that kernel finishes:
-//   * weights take the MMA's M (128 rows per accumulator; a GeGLU CTA holds two accumulators, 128 gate rows and the
-//     same 128 rows of the up matrix), the batch its N (64, zero padded), f32 accumulators in TMEM;
+//   * weights take the MMA's M (128 rows per CTA; a GeGLU CTA holds 64 gate rows and the same 64 rows of the up
+//     matrix, so gate and up of an output element meet in one CTA), the batch its N (64, zero padded), f32
+//     accumulators in TMEM;
 //   * at most one CTA per SM and one wave per launch: K is split over a thread-block cluster so that the CTA count
 //     stays within the SM count, which also keeps the number of CTAs that re-read the same activations from L2 low;
 //   * before the dependency wait: TMEM allocation, barrier set-up, the raw quantized rows of the CTA's K range
 //     brought in by bulk copies (cp.async.bulk, one per row segment, completion counted on an mbarrier), and as many
-//     operand stages dequantized as shared memory holds -- none of it depends on the predecessor;
-//   * after the wait two warps bring in the activations of the CTA's whole K range (every stage in flight at once;
-//     the first access after a kernel boundary costs well over a microsecond, so nothing is requested late), the
-//     dequantizing warps keep turning code bytes into f16 weights (the four values a 2-bit code can mean, (q - 1) d,
-//     sit in two registers as a byte table; one prmt assembles two weights; 16-byte stores into the K-major
-//     128-byte-swizzled operand layout), and four warps issue tcgen05.mma.cta_group::1.kind::f16.  Issuing one MMA costs a
-//     warp about 210 cycles whatever its shape (measured: M 64 / 128, N 16 .. 256 all the same), far more than the
-//     32 cycles of arithmetic in a 128 x 64 x 16 step, but MMAs issued by different warps overlap fully (4 warps: 53
-//     cycles per MMA).  So the four K = 16 steps of a 64-k stage belong to four issuing warps, each with its own TMEM
+//     operand slots dequantized as shared memory holds -- none of it depends on the predecessor;
+//   * the pipeline runs in steps of 128 k (one 32-byte half of a TQ2_0 block per row: both 64-k operand tiles of a
+//     step come from the same code bytes), because every hand-over costs its thread a few hundred cycles: a barrier
+//     test ~150, an MMA issue ~210, a commit ~90 (measured), whatever the amount of data behind it;
+//   * after the wait one thread requests the activations of every step with TMA (cp.async.bulk.tensor, 128-byte
+//     swizzle applied by the copy engine, rows beyond m zero-filled by the tensor map's bounds), the dequantizing
+//     warps keep turning code bytes into f16 weights (the four values a 2-bit code can mean, (q - 1) d, sit in two
+//     registers as a byte table; one prmt assembles two weights; 16-byte stores into the K-major 128-byte-swizzled
+//     operand layout), and four warps issue tcgen05.mma.cta_group::1.kind::f16.  Issuing one MMA costs a warp about
+//     210 cycles whatever its shape (measured: M 64 / 128, N 16 .. 256 all the same), far more than the 32 cycles of
+//     arithmetic in a 128 x 64 x 16 MMA, but MMAs issued by different warps overlap fully (4 warps: 53 cycles per
+//     MMA).  So the four K = 16 slices of a 64-k tile belong to four issuing warps, each with its own TMEM
 //     accumulator (four partial sums over interleaved k, added in a fixed order in the epilogue); every issuer
-//     commits its step to the stage's mbarrier, which hands the stage back after the fourth arrival;
-//   * CTAs walk their stages from different starting points so that the CTAs of a launch do not all ask L2 for the
+//     commits its MMAs of a step to the step's mbarrier, which hands the slots back after the fourth arrival;
+//   * CTAs walk their steps from different starting points so that the CTAs of a launch do not all ask L2 for the
 //     same activation lines at the same moment;
 //   * the accumulators are read back with tcgen05.ld by all dequantizing warps.  When K is split, the CTAs of a tile
 //     add their partial tiles in split order through distributed shared memory, each finishing one contiguous slice.
@@ -32,27 +36,29 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA raises the kernels object's status word, skips to the
 // TMEM release and returns.
+#include <cuda.h>
 #include <stdlib.h>
 
 #include "lc_internal.h"
 
 namespace {
 
-constexpr int TILE_ROWS = 128;   // weight rows per accumulator (UMMA M)
+constexpr int TILE_ROWS = 128;   // weight rows per accumulator tile (UMMA M)
 constexpr int NB = 64;           // batch columns (UMMA N)
-constexpr int KT = 64;           // k per operand stage
-constexpr int NBAR = 16;         // stage-release barriers, one per stage index mod 16
-constexpr int NLOAD = 2;         // activation loader warps
-constexpr int NISS = 4;          // MMA-issuing warps, one accumulator each (see below)
+constexpr int KT = 64;           // k per operand tile (one 128-byte swizzled row)
+constexpr int STEP_TILES = 2;    // operand tiles per pipeline step (128 k)
+constexpr int NBAR = 8;          // step-release barriers, one per step index mod 8
+constexpr int NISS = 4;          // MMA-issuing warps, one accumulator each
 constexpr int TMEM_COLS = NISS * NB;   // 256
 // Operand tiles are K-major with the 128-byte swizzle: a row is its 64 k values (128 bytes, eight 16-byte chunks),
 // rows follow each other at 128 bytes, and chunk c of row r sits at chunk position c ^ (r % 8) of the row.  Tiles
 // start on 1024-byte boundaries (eight rows: the swizzle pattern's period).
 constexpr int ROW_BYTES = KT * 2;            // 128
-constexpr int A_TILE = TILE_ROWS * ROW_BYTES;   // one 128-row operand tile of one stage: 16 KB
-constexpr int B_STAGE = NB * ROW_BYTES;         // 8 KB
+constexpr int A_TILE = TILE_ROWS * ROW_BYTES;   // one 128-row operand tile: 16 KB
+constexpr int B_TILE = NB * ROW_BYTES;          // 8 KB
+constexpr int B_SLOT = STEP_TILES * B_TILE;     // activations of one step
 constexpr int BB = 66;           // bytes per TQ2_0 block
-constexpr int MAX_TILES = 12;    // stages per CTA (three blocks of 256 k)
+constexpr int MAX_STEPS = 12;    // steps per CTA (six blocks of 256 k)
 constexpr int MAX_GROUPS = 3;
 constexpr int MAX_KS = 8;        // portable cluster size
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -62,24 +68,16 @@ struct TcdParams {
     __half *out[MAX_GROUPS];
     int n[MAX_GROUPS], tile_end[MAX_GROUPS];
     int ngroups;
-    const __half *x;
     int m, K, nb;        // nb = blocks per weight row
     int ks, bps;         // split-K: grid.z = cluster size = ks, bps = blocks per split
     int raw_rs;          // bytes reserved per row of raw blocks (odd multiple of 16)
-    int sa, sb;          // operand stages in shared memory: weights (a ring) / activations (all stages of a CTA)
-    int geglu;           // 1 (two accumulators): w[0] = gate, w[1] = up, out[0] = gelu(gate) * up
+    int sa, sb;          // operand slots (one step each) in shared memory: weights / activations
+    int geglu;           // 1: operand rows 0-63 are gate rows, 64-127 the same rows of the up matrix; out[0] = gelu(gate) * up
     int *status;
     uint32_t wait_limit;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
 __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
 }
@@ -171,45 +169,59 @@ __device__ __forceinline__ uint2 pack4(float a, float b, float c, float d) {
     return make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
 }
 
-// MT accumulators of 128 weight rows per CTA: 1 for a plain (grouped) projection, 2 for GeGLU.
-template <int MT>
-__global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_kernel(const TcdParams p) {
-    constexpr int ROWS = TILE_ROWS * MT, NDQ = 8 * MT, NT = (NDQ + NLOAD + NISS) * 32;
-    constexpr int A_STAGE = MT * A_TILE;
+// One box of the activation tensor map (64 k x 64 rows, 128-byte swizzle) -> shared memory, completion on `mbar`.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(mbar)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(addr), "r"(bytes) : "memory");
+}
+
+constexpr int NDQ = 8;                       // dequantizing warps (also the epilogue warps)
+constexpr int NT = (NDQ + 1 + NISS) * 32;    // + activation loader warp + MMA issuers
+constexpr int A_SLOT = STEP_TILES * A_TILE;  // weights of one step
+
+__global__ void __launch_bounds__(NT, 1)
+qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CUtensorMap x_map) {
+    constexpr int ROWS = TILE_ROWS;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // operand tiles start on 1024-byte boundaries
-    const int SA = p.sa, SB = p.sb;   // SB = the CTA's stage count: every activation stage has its own slot
-    uint8_t *a_s = smem;                                   // [SA][A_STAGE]; reused for the split-K exchange
-    uint8_t *b_s = a_s + SA * A_STAGE;                     // [SB][B_STAGE]
-    uint8_t *raw = b_s + SB * B_STAGE;                     // [ROWS][raw_rs]
+    const int SA = p.sa, SB = p.sb;
+    uint8_t *a_s = smem;                                   // [SA][A_SLOT]; reused for the split-K exchange
+    uint8_t *b_s = a_s + SA * A_SLOT;                      // [SB][B_SLOT]
+    uint8_t *raw = b_s + SB * B_SLOT;                      // [ROWS][raw_rs]
     uint64_t *bars = reinterpret_cast<uint64_t *>(raw + ROWS * p.raw_rs);
     uint64_t *raw_full = bars;                             // 1
-    uint64_t *a_full = bars + 1;                           // [MAX_TILES] (SA used)
-    uint64_t *b_all = a_full + MAX_TILES;                  // 1
-    uint64_t *mma_done = b_all + 1;                        // [NBAR]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(mma_done + NBAR);
+    uint64_t *a_full = bars + 1;                           // [MAX_STEPS] (SA used)
+    uint64_t *b_full = a_full + MAX_STEPS;                 // [MAX_STEPS] (SB used)
+    uint64_t *step_done = b_full + MAX_STEPS;              // [NBAR]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(step_done + NBAR);
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     lc_pdl_trigger();
     int grp = 0;
-    if (MT == 1) while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
-    const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * TILE_ROWS;   // first output row of this tile
+    while (grp + 1 < p.ngroups && (int)blockIdx.x >= p.tile_end[grp]) grp++;
+    const int rows_out = p.geglu ? TILE_ROWS / 2 : TILE_ROWS;                          // output rows of a tile
+    const int n0 = ((int)blockIdx.x - (grp ? p.tile_end[grp - 1] : 0)) * rows_out;    // first output row of this tile
     const int n_rows = p.n[grp];
     const size_t rb = (size_t)p.nb * BB, w_bytes = rb * (size_t)n_rows;
     const int kbs = (int)blockIdx.z * p.bps, kbe = min(p.nb, kbs + p.bps), nblk = max(kbe - kbs, 0);
     const int seg = nblk * BB;
-    const int total_tiles = nblk * 4;                      // 64-k stages of this CTA
-    // Step i of this CTA works on stage tile_of(i): pairs of stages (one 32-byte half block of codes) are walked
-    // from a starting pair that differs from CTA to CTA.
-    const int npairs = total_tiles >> 1, pair0 = npairs ? (int)((blockIdx.x * 5u + blockIdx.z) % (unsigned)npairs) : 0;
-    auto tile_of = [&](int i) -> int {
-        int pi = (i >> 1) + pair0;
-        if (pi >= npairs) pi -= npairs;
-        return 2 * pi + (i & 1);
+    const int total_steps = nblk * 2;                      // 128-k steps of this CTA
+    // Step i of this CTA works on half block half_of(i) (block half_of(i) / 2 of the CTA's range, half % 2 of it);
+    // the walk starts at a half block that differs from CTA to CTA.
+    const int start = total_steps ? (int)((blockIdx.x * 5u + blockIdx.z) % (unsigned)total_steps) : 0;
+    auto half_of = [&](int i) -> int {
+        int hb = i + start;
+        if (hb >= total_steps) hb -= total_steps;
+        return hb;
     };
-    // operand row r of the CTA -> weight matrix (accumulator r / 128) and row of it
-    auto wmat_of = [&](int r) -> const uint8_t * { return MT == 2 ? p.w[r >> 7] : p.w[grp]; };
+    // operand row r of the CTA -> weight matrix and row of it
+    auto wmat_of = [&](int r) -> const uint8_t * { return p.geglu ? p.w[r >> 6] : p.w[grp]; };
+    auto wrow_of = [&](int r) -> int { return n0 + (p.geglu ? (r & 63) : r); };
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
@@ -219,9 +231,9 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
     }
     if (tid == 0) {
         mbar_init(smem_u32(raw_full), ROWS);
-        for (int i = 0; i < MAX_TILES; i++) mbar_init(smem_u32(&a_full[i]), NDQ);
-        mbar_init(smem_u32(b_all), NLOAD);
-        for (int i = 0; i < NBAR; i++) mbar_init(smem_u32(&mma_done[i]), NISS);
+        for (int i = 0; i < MAX_STEPS; i++) mbar_init(smem_u32(&a_full[i]), NDQ);
+        for (int i = 0; i < MAX_STEPS; i++) mbar_init(smem_u32(&b_full[i]), 1);
+        for (int i = 0; i < NBAR; i++) mbar_init(smem_u32(&step_done[i]), NISS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -237,7 +249,7 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
         //      16-byte range (rows are only 2-byte aligned) ----
         if (tid < ROWS) {
             const uint8_t *wm = wmat_of(tid);
-            const int row = n0 + (tid & (TILE_ROWS - 1));
+            const int row = wrow_of(tid);
             const uint32_t bar = smem_u32(raw_full);
             bool counted = false;
             if (row < n_rows && nblk > 0) {
@@ -261,47 +273,40 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { *abort_flag = 1; dead = true; }
         }
-        // This thread's share of every stage: operand row 32 (warp & 3) + lane of accumulator (warp >> 3), the 16 code
-        // bytes 16 bq .. + 15 (bq = (warp >> 2) & 1) of the stage's 32-byte half block, two of their four bit pairs.
-        const int acc = warp >> 3, r = 32 * (warp & 3) + lane, bq = (warp >> 2) & 1;
-        const int row = n0 + r;
+        // This thread's share of every step: operand row 32 (warp & 3) + lane, the 16 code bytes 16 bq .. + 15
+        // (bq = warp >> 2) of the step's 32-byte half block: 64 weights.
+        const int r = 32 * (warp & 3) + lane, bq = warp >> 2;
+        const int row = wrow_of(r);
         const bool rvalid = row < n_rows;
         const size_t g0 = (size_t)row * rb + (size_t)kbs * BB;
-        const uint8_t *rrow = raw + (acc * TILE_ROWS + r) * p.raw_rs + (int)(g0 & 15);
-        const uint32_t dst0 = smem_u32(a_s) + (uint32_t)(acc * A_TILE + r * ROW_BYTES);
+        const uint8_t *rrow = raw + r * p.raw_rs + (int)(g0 & 15);
+        const uint32_t dst0 = smem_u32(a_s) + (uint32_t)(r * ROW_BYTES);
         const uint32_t swz = (uint32_t)(r & 7);
-        uint32_t lut_lo = 0, lut_hi = 0, cw[4] = {0, 0, 0, 0};
-        for (int i = 0; i < total_tiles && !dead; i++) {
-            const int t = tile_of(i), s = i % SA, blk = t >> 2, h = (t >> 1) & 1, lp = t & 1;
-            if (i >= SA) {   // the MMAs that read this stage SA steps ago have completed
+        for (int i = 0; i < total_steps && !dead; i++) {
+            const int hb = half_of(i), s = i % SA, blk = hb >> 1, h = hb & 1;
+            if (i >= SA) {   // the MMAs that read this slot SA steps ago have completed
                 uint32_t ok = 1;
                 const int u = i - SA;
-                if (lane == 0) ok = mbar_wait(smem_u32(&mma_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) ? 1u : 0u;
+                if (lane == 0) ok = mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) ? 1u : 0u;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
             }
-            if (lp == 0) {
-                // The four weights a code can mean, (q - 1) d, as a byte table for prmt: lut_lo / lut_hi hold the low /
-                // high bytes of {-d, 0, d, 2d}; a selector nibble pair (q, q + 4) then assembles one f16.
-                const __half d = rvalid ? *reinterpret_cast<const __half *>(rrow + blk * BB + 64) : __float2half(0.0f);
-                const uint32_t p01 = (uint32_t)__half_as_ushort(__hneg(d));
-                const uint32_t p23 = (uint32_t)__half_as_ushort(d) | ((uint32_t)__half_as_ushort(__hadd(d, d)) << 16);
-                lut_lo = __byte_perm(p01, p23, 0x6420);
-                lut_hi = __byte_perm(p01, p23, 0x7531);
-                // 16 code bytes, 2-byte aligned: five aligned words, funnel-shifted into place
-                const uint32_t ca = smem_u32(rrow + blk * BB + 32 * h + 16 * bq), sh = (ca & 3u) * 8u, wa = ca & ~3u;
-                const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8), w3 = lds32(wa + 12), w4 = sh ? lds32(wa + 16) : 0u;
-                cw[0] = __funnelshift_r(w0, w1, sh);
-                cw[1] = __funnelshift_r(w1, w2, sh);
-                cw[2] = __funnelshift_r(w2, w3, sh);
-                cw[3] = __funnelshift_r(w3, w4, sh);
-            }
-            // element k = 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j; this stage holds
-            // l = 2 lp, 2 lp + 1; chunk 4 (l & 1) + 2 bq + {0, 1} of the row takes bytes j = 16 bq + {0..7, 8..15}
-            const uint32_t dst = dst0 + (uint32_t)(s * A_STAGE);
+            // The four weights a code can mean, (q - 1) d, as a byte table for prmt: lut_lo / lut_hi hold the low /
+            // high bytes of {-d, 0, d, 2d}; a selector nibble pair (q, q + 4) then assembles one f16.
+            const __half d = rvalid ? *reinterpret_cast<const __half *>(rrow + blk * BB + 64) : __float2half(0.0f);
+            const uint32_t p01 = (uint32_t)__half_as_ushort(__hneg(d));
+            const uint32_t p23 = (uint32_t)__half_as_ushort(d) | ((uint32_t)__half_as_ushort(__hadd(d, d)) << 16);
+            const uint32_t lut_lo = __byte_perm(p01, p23, 0x6420), lut_hi = __byte_perm(p01, p23, 0x7531);
+            // 16 code bytes, 2-byte aligned: five aligned words, funnel-shifted into place
+            const uint32_t ca = smem_u32(rrow + blk * BB + 32 * h + 16 * bq), sh = (ca & 3u) * 8u, wa = ca & ~3u;
+            const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8), w3 = lds32(wa + 12), w4 = sh ? lds32(wa + 16) : 0u;
+            const uint32_t cw[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                                    __funnelshift_r(w3, w4, sh)};
+            // element k = 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j.  Operand tile l >> 1 of
+            // the step takes l; chunk 4 (l & 1) + 2 bq + {0, 1} of the row takes bytes j = 16 bq + {0..7, 8..15}.
+            const uint32_t dst = dst0 + (uint32_t)(s * A_SLOT);
 #pragma unroll
-            for (int li = 0; li < 2; li++) {
-                const int l = 2 * lp + li;
+            for (int l = 0; l < 4; l++) {
                 uint32_t v[8];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
@@ -309,8 +314,8 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
                     v[2 * q] = __byte_perm(lut_lo, lut_hi, sel);
                     v[2 * q + 1] = __byte_perm(lut_lo, lut_hi, sel >> 16);
                 }
-                const uint32_t c0 = (uint32_t)(4 * li + 2 * bq);
-                const uint32_t da = dst + (((c0 ^ swz) << 4)), db = dst + ((((c0 + 1) ^ swz) << 4));
+                const uint32_t c0 = (uint32_t)(4 * (l & 1) + 2 * bq), dt = dst + (uint32_t)((l >> 1) * A_TILE);
+                const uint32_t da = dt + (((c0 ^ swz) << 4)), db = dt + ((((c0 + 1) ^ swz) << 4));
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(da), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(db), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
             }
@@ -318,61 +323,54 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&a_full[s]));
         }
-    } else if (warp < NDQ + NLOAD) {
-        // =========================== activation loaders (two warps) ===========================
-        // Stage t holds x[0..64, k0 + 64 t .. + 63]: 64 rows of 128 bytes, chunks swizzled as above.  Every stage of the
-        // CTA has its own slot and all are requested at once; loader w takes the steps i with i % 2 == w, each lane
-        // copies 16 pieces of 16 bytes per stage.  The loaders report once, when everything has landed.
-        const int lw = warp - NDQ;
-        lc_pdl_wait();   // the activations are the predecessor's output
-        const __half *xk = p.x + (size_t)kbs * 256;
-        for (int i = lw; i < total_tiles; i += NLOAD) {
-            const int t = tile_of(i);
-            const uint32_t base = smem_u32(b_s) + (uint32_t)(i * B_STAGE);
-#pragma unroll
-            for (int e = 0; e < 16; e++) {
-                const int pc = lane + 32 * e, rowb = pc >> 3, c = pc & 7;   // 8 consecutive lanes: 128 contiguous bytes of a row
-                const bool ok = rowb < p.m;
-                cp_async16(base + (uint32_t)(rowb * ROW_BYTES + ((c ^ (rowb & 7)) << 4)),
-                           ok ? (const void *)(xk + (size_t)rowb * p.K + t * KT + c * 8) : (const void *)p.x, ok ? 16u : 0u);
+    } else if (warp == NDQ) {
+        // =========================== activation loader (one thread) ===========================
+        // Step i needs x[0..64, k .. k + 127], k = 256 (kbs + half / 2) + 128 (half % 2): two boxes of the tensor map.
+        if (lane == 0) {
+            lc_pdl_wait();   // the activations are the predecessor's output
+            bool dead = false;
+            for (int i = 0; i < total_steps && !dead; i++) {
+                if (i >= SB) {   // its slot was last read by the MMAs of step i - SB
+                    const int u = i - SB;
+                    if (!mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+                }
+                const int hb = half_of(i), k0 = (kbs + (hb >> 1)) * 256 + (hb & 1) * 128;
+                const uint32_t bar = smem_u32(&b_full[i % SB]), dst = smem_u32(b_s) + (uint32_t)((i % SB) * B_SLOT);
+                mbar_expect_tx(bar, (uint32_t)B_SLOT);
+                tma_load_2d(dst, &x_map, k0, 0, bar);
+                tma_load_2d(dst + B_TILE, &x_map, k0 + KT, 0, bar);
             }
+            if (dead) *abort_flag = 1;
         }
-        cp_async_commit();
-        cp_async_wait<0>();
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(b_all));
     } else {
         // =========================== MMA issue (four warps, one thread each) ===========================
-        // Issuer iw owns TMEM accumulator iw (columns 64 iw ..).  One accumulator tile per CTA: issuer iw takes K = 16
-        // step iw of every stage.  Two (GeGLU): issuers 0, 1 take steps {0, 1}, {2, 3} of the gate tile, issuers 2, 3
-        // the same of the up tile.
-        const int iw = warp - NDQ - NLOAD;
-        const int mt = MT == 2 ? (iw >> 1) : 0, k_first = MT == 2 ? 2 * (iw & 1) : iw, k_count = MT == 2 ? 2 : 1;
+        // Issuer iw owns TMEM accumulator iw (columns 64 iw ..) and takes K = 16 slice iw of both 64-k operand tiles of
+        // every step.
         // One thread per issuer runs the loop: every instruction in it (barrier test, MMA, commit) costs its thread on
         // the order of a hundred cycles or more, so nothing warp-wide is added.
+        const int iw = warp - NDQ - 1;
         if (lane == 0) {
-            const uint64_t adesc0 = make_desc(smem_u32(a_s) + (uint32_t)(mt * A_TILE + k_first * 32));
-            const uint64_t bdesc0 = make_desc(smem_u32(b_s) + (uint32_t)(k_first * 32));
+            const uint64_t adesc0 = make_desc(smem_u32(a_s) + (uint32_t)(iw * 32));
+            const uint64_t bdesc0 = make_desc(smem_u32(b_s) + (uint32_t)(iw * 32));
             const uint32_t tmem_acc = tmem_base + (uint32_t)(iw * NB);
-            bool dead = !mbar_wait(smem_u32(b_all), 0u, p.wait_limit);   // all activations of this CTA have landed
-            for (int i = 0; i < total_tiles && !dead; i++) {
-                if (!mbar_wait(smem_u32(&a_full[i % SA]), (uint32_t)((i / SA) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+            bool dead = false;
+            for (int i = 0; i < total_steps && !dead; i++) {
+                if (!mbar_wait(smem_u32(&a_full[i % SA]), (uint32_t)((i / SA) & 1), p.wait_limit) ||
+                    !mbar_wait(smem_u32(&b_full[i % SB]), (uint32_t)((i / SB) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
                 tc_fence_after();
-                uint64_t ad = adesc0 + (uint64_t)((uint32_t)((i % SA) * A_STAGE) >> 4);
-                uint64_t bd = bdesc0 + (uint64_t)((uint32_t)(i * B_STAGE) >> 4);
 #pragma unroll
-                for (int j = 0; j < k_count; j++) {
-                    umma_f16(tmem_acc, ad, bd, idesc, (i > 0 || j > 0) ? 1u : 0u);
-                    ad += (uint64_t)(32 >> 4);   // the next K = 16 step: 32 bytes along the row
-                    bd += (uint64_t)(32 >> 4);
+                for (int lp = 0; lp < STEP_TILES; lp++) {
+                    const uint64_t ad = adesc0 + (uint64_t)((uint32_t)((i % SA) * A_SLOT + lp * A_TILE) >> 4);
+                    const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)((i % SB) * B_SLOT + lp * B_TILE) >> 4);
+                    umma_f16(tmem_acc, ad, bd, idesc, (i > 0 || lp > 0) ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&mma_done[i % NBAR]));
+                umma_commit(smem_u32(&step_done[i % NBAR]));
             }
-            // drain: the last stage's barrier completes when all four issuers' MMAs are done
-            if (!dead && total_tiles > 0) {
-                const int last = total_tiles - 1;
-                dead = !mbar_wait(smem_u32(&mma_done[last % NBAR]), (uint32_t)((last / NBAR) & 1), p.wait_limit);
+            // drain: the last step's barrier completes when all four issuers' MMAs are done
+            if (!dead && total_steps > 0) {
+                const int last = total_steps - 1;
+                dead = !mbar_wait(smem_u32(&step_done[last % NBAR]), (uint32_t)((last / NBAR) & 1), p.wait_limit);
             }
             if (dead) *abort_flag = 1;
         }
@@ -383,80 +381,77 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
     tc_fence_after();
     const bool failed = *abort_flag != 0;
 
-    // ---- results.  Dequantizing warp w reads TMEM lanes 32 (w & 3) .. + 31 (one weight row per thread) and CW batch
-    //      columns starting at CW (w >> 2), of every accumulator ----
-    constexpr int CW = NB / (NDQ / 4);                      // 32 (one accumulator) or 16 (two)
-    float *red = reinterpret_cast<float *>(a_s);            // [MT][NB cols][128 rows] f32 (split K only)
+    // ---- results.  Dequantizing warp w reads TMEM lanes 32 (w & 3) .. + 31 (one operand row per thread) and the 32
+    //      batch columns starting at 32 (w >> 2); the four partial accumulators are added as (0 + 1) + (2 + 3) ----
+    float *red = reinterpret_cast<float *>(a_s);            // staging, reuses the weight slots: [NB cols][128 rows] f32
     __half *out = p.out[grp];
+    const int lrow = 32 * (warp & 3) + lane, c0 = 32 * (warp >> 2);
+    float v[32];
     if (warp < NDQ) {
-        const int lrow = 32 * (warp & 3) + lane, c0 = CW * (warp >> 2);
 #pragma unroll
-        for (int cc = 0; cc < CW; cc += 16) {
-            // the four partial accumulators, added in a fixed order: (0 + 1) + (2 + 3) for one tile; gate = 0 + 1 and
-            // up = 2 + 3 for two
-            float v[MT][16];
-#pragma unroll
-            for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-                for (int j = 0; j < 16; j++) v[mt][j] = 0.f;
-            if (!failed && total_tiles > 0) {
+        for (int cc = 0; cc < 32; cc += 16) {
+            if (!failed && total_steps > 0) {
                 const uint32_t ta = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(c0 + cc);
                 uint32_t a0[16], a1[16];
                 tmem_ld16(ta, a0);
                 tmem_ld16(ta + NB, a1);
 #pragma unroll
-                for (int j = 0; j < 16; j++) v[0][j] = __uint_as_float(a0[j]) + __uint_as_float(a1[j]);
+                for (int j = 0; j < 16; j++) v[cc + j] = __uint_as_float(a0[j]) + __uint_as_float(a1[j]);
                 tmem_ld16(ta + 2 * NB, a0);
                 tmem_ld16(ta + 3 * NB, a1);
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const float hi = __uint_as_float(a0[j]) + __uint_as_float(a1[j]);
-                    if (MT == 2) v[MT - 1][j] = hi; else v[0][j] += hi;
-                }
+                for (int j = 0; j < 16; j++) v[cc + j] += __uint_as_float(a0[j]) + __uint_as_float(a1[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[cc + j] = 0.f;
             }
-            if (p.ks > 1) {
+        }
+        if (p.ks > 1 || (p.geglu && lrow >= 64)) {   // partial tiles of a split, or the up half of a GeGLU tile
 #pragma unroll
-                for (int mt = 0; mt < MT; mt++)
+            for (int j = 0; j < 32; j++) red[(c0 + j) * TILE_ROWS + lrow] = v[j];
+        } else if (!p.geglu && n0 + lrow < n_rows && !failed) {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) red[(mt * NB + c0 + cc + j) * TILE_ROWS + lrow] = v[mt][j];
-            } else if (n0 + lrow < n_rows && !failed) {
+            for (int j = 0; j < 32; j++)
+                if (c0 + j < p.m) out[(size_t)(c0 + j) * n_rows + n0 + lrow] = __float2half_rn(v[j]);
+        }
+    }
+    if (p.ks == 1 && p.geglu) {
+        // gate rows (operand rows 0-63) meet their up rows (64-127) through shared memory
+        __syncthreads();
+        if (warp < NDQ && lrow < 64 && n0 + lrow < n_rows && !failed) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int col = c0 + cc + j;
-                    float r = v[0][j];
-                    if (MT == 2) r = geglu_f(r, v[MT - 1][j]);
-                    if (col < p.m) out[(size_t)col * n_rows + n0 + lrow] = __float2half_rn(r);
-                }
-            }
+            for (int j = 0; j < 32; j++)
+                if (c0 + j < p.m)
+                    out[(size_t)(c0 + j) * n_rows + n0 + lrow] = __float2half_rn(geglu_f(v[j], red[(c0 + j) * TILE_ROWS + 64 + lrow]));
         }
     }
     if (p.ks > 1) {
-        // The ks CTAs of this tile are one cluster.  An item is four consecutive rows of one batch column; CTA `rank`
-        // finishes the items [rank, rank + 1) * per: adds the ks partials in split order and stores.  Consecutive
+        // The ks CTAs of this tile are one cluster.  An item is four consecutive output rows of one batch column; CTA
+        // `rank` finishes the items [rank, rank + 1) * per: adds the ks partials in split order and stores.  Consecutive
         // threads take consecutive items: consecutive 16-byte pieces of the peers' shared memory, consecutive rows out.
         cluster_sync();
         const int rank = (int)blockIdx.z;
         const uint32_t red_a = smem_u32(red);
-        auto gather = [&](int mt, int col, int r4) {
-            const uint32_t la = red_a + (uint32_t)(((mt * NB + col) * TILE_ROWS + r4) * 4);
-            float4 v[MAX_KS];
+        auto gather = [&](int col, int r4) {
+            const uint32_t la = red_a + (uint32_t)((col * TILE_ROWS + r4) * 4);
+            float4 pv[MAX_KS];
 #pragma unroll
-            for (int sp = 0; sp < MAX_KS; sp++) v[sp] = sp < p.ks ? ld_dsmem_f4(la, (uint32_t)sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp = 0; sp < MAX_KS; sp++) pv[sp] = sp < p.ks ? ld_dsmem_f4(la, (uint32_t)sp) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int sp = 0; sp < MAX_KS; sp++) {
-                acc.x += v[sp].x; acc.y += v[sp].y; acc.z += v[sp].z; acc.w += v[sp].w;
+                acc.x += pv[sp].x; acc.y += pv[sp].y; acc.z += pv[sp].z; acc.w += pv[sp].w;
             }
             return acc;
         };
-        const int items = p.m * (TILE_ROWS / 4), per = (items + p.ks - 1) / p.ks;
+        const int items = p.m * (rows_out / 4), per = (items + p.ks - 1) / p.ks;
         const int it_end = min(items, (rank + 1) * per);
         if (!failed) {
             for (int it = rank * per + tid; it < it_end; it += NT) {
-                const int col = it / (TILE_ROWS / 4), r4 = (it - col * (TILE_ROWS / 4)) * 4;
-                float4 a = gather(0, col, r4);
-                if (MT == 2) {
-                    const float4 u = gather(MT - 1, col, r4);
+                const int col = it / (rows_out / 4), r4 = (it - col * (rows_out / 4)) * 4;
+                float4 a = gather(col, r4);
+                if (p.geglu) {
+                    const float4 u = gather(col, r4 + 64);
                     a = make_float4(geglu_f(a.x, u.x), geglu_f(a.y, u.y), geglu_f(a.z, u.z), geglu_f(a.w, u.w));
                 }
                 __half *dst = out + (size_t)col * n_rows + n0 + r4;
@@ -479,14 +474,43 @@ __global__ void __launch_bounds__((8 * MT + NLOAD + NISS) * 32, 1) qgemm_tcd_ker
     }
 }
 
-template <int MT>
-int launch_tcd(lc_batch *b, const TcdParams &p, int tiles, size_t smem) {
-    auto kern = qgemm_tcd_kernel<MT>;
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link-time dependency on the driver).
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_tiled_fn encode_tiled() {
+    static encode_tiled_fn fn = []() -> encode_tiled_fn {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<encode_tiled_fn>(ptr);
+    }();
+    return fn;
+}
+
+// The activations x[m, K] (f16, row-major) as a 2-D tensor map: boxes of 64 k x 64 rows land as 64 rows of 128 bytes
+// with the 128-byte swizzle; rows beyond m read as zero.
+int make_x_map(CUtensorMap *map, const void *x, uint32_t m, uint32_t kk) {
+    encode_tiled_fn fn = encode_tiled();
+    if (!fn) return lc_fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {kk, m};
+    const cuuint64_t strides[1] = {(cuuint64_t)kk * 2};
+    const cuuint32_t box[2] = {KT, NB};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return lc_fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return LC_OK;
+}
+
+int launch_tcd(lc_batch *b, const TcdParams &p, const CUtensorMap &x_map, int tiles, size_t smem) {
     static lc_smem_optin optin;
-    LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
+    LC_CUDA_TRY(lc_ensure_smem(qgemm_tcd_kernel, optin, b->ctx, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, 1, p.ks);
-    cfg.blockDim = dim3((8 * MT + NLOAD + NISS) * 32);
+    cfg.blockDim = dim3(NT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = b->stream;
     cudaLaunchAttribute attr[2];
@@ -505,7 +529,7 @@ int launch_tcd(lc_batch *b, const TcdParams &p, int tiles, size_t smem) {
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    LC_LAUNCH_CHECKED(cudaLaunchKernelEx(&cfg, kern, p));
+    LC_LAUNCH_CHECKED(cudaLaunchKernelEx(&cfg, qgemm_tcd_kernel, p, x_map));
     b->dispatch_count++;
     return LC_OK;
 }
@@ -520,7 +544,6 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     if (m <= 8 || m > NB || ng < 1 || ng > MAX_GROUPS || kk % 256 != 0 || !lc_aligned(input->dptr, 16)) return -1;
     if (geglu && (ng != 2 || ns[0] != ns[1])) return -1;
     TcdParams p;
-    p.x = (const __half *)input->dptr;
     p.m = (int)m;
     p.K = (int)kk;
     p.nb = (int)(kk / 256);
@@ -533,14 +556,15 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
         p.w[g] = (const uint8_t *)weights[gi]->dptr;
         p.out[g] = (__half *)outputs[gi]->dptr;
         p.n[g] = (int)ns[gi];
-        if (g < ng && !(geglu && g > 0)) tiles += ((int)ns[g] + TILE_ROWS - 1) / TILE_ROWS;
+        const int rows_out = geglu ? TILE_ROWS / 2 : TILE_ROWS;
+        if (g < ng && !(geglu && g > 0)) tiles += ((int)ns[g] + rows_out - 1) / rows_out;
         p.tile_end[g] = tiles;
     }
     if (tiles < 1) return -1;
-    const int mt = geglu ? 2 : 1, rows = TILE_ROWS * mt;
+    const int rows = TILE_ROWS;
     // One wave: split K over a cluster of at most 8 CTAs while the CTA count stays within about 7/8 of the SM count
     // (a cluster needs all its SMs in one GPC, so the last few SMs cannot always be used; a launch that does not fit
-    // runs a second wave and takes twice as long), and no CTA takes more than MAX_TILES stages (three blocks per row).
+    // runs a second wave and takes twice as long), and no CTA takes more than MAX_STEPS steps (six blocks per row).
     static const int ks_cap = []() { const char *e = getenv("LOCAL_CUDA_TCD_KS"); const int v = e ? atoi(e) : 0; return v > 0 ? v : MAX_KS; }();
     int ks = (k->ctx->sm_count * 7 / 8) / tiles;
     if (ks > ks_cap) ks = ks_cap;
@@ -548,7 +572,7 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     if (ks > p.nb) ks = p.nb;
     if (ks < 1) ks = 1;
     int bps = (p.nb + ks - 1) / ks;
-    if (bps > MAX_TILES / 4) bps = MAX_TILES / 4;
+    if (bps > MAX_STEPS / 2) bps = MAX_STEPS / 2;
     ks = (p.nb + bps - 1) / bps;
     if (ks > MAX_KS) return -1;   // K too long for one cluster of this kernel
     p.ks = ks;
@@ -557,18 +581,23 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     if ((p.raw_rs / 16) % 2 == 0) p.raw_rs += 16;
     p.status = k->dev_status;
     p.wait_limit = WAIT_LIMIT;
-    // shared memory: all activation stages of the CTA when they fit, then as many weight stages as the rest holds
-    const int total = 4 * bps;
-    const size_t fixed = (size_t)rows * p.raw_rs + (2 + MAX_TILES + NBAR) * 8 + 16 + 1024;   // + 1024: tile alignment slack
-    const size_t budget = k->ctx->smem_optin > 8192 ? k->ctx->smem_optin - 4096 : 0;
-    const size_t a_stage = (size_t)mt * A_TILE;
-    const int sb = total;
-    if (fixed + (size_t)sb * B_STAGE + 2 * a_stage > budget) return -1;
-    int sa = (int)((budget - fixed - (size_t)sb * B_STAGE) / a_stage);
+    // Shared memory: up to three activation slots, then as many weight slots as the rest holds (at least two; with
+    // split K the partial-tile exchange reuses them and must fit).
+    const int total = 2 * bps;
+    const size_t fixed = (size_t)rows * p.raw_rs + (1 + 2 * MAX_STEPS + NBAR) * 8 + 16 + 1024;   // + 1024: tile alignment slack
+    const size_t budget = k->ctx->smem_optin > 2048 ? k->ctx->smem_optin - 1024 : 0;
+    const size_t a_slot = (size_t)A_SLOT;
+    int sb = total < 3 ? total : 3;
+    while (sb > 2 && fixed + (size_t)sb * B_SLOT + 2 * a_slot > budget) sb--;
+    if (fixed + (size_t)sb * B_SLOT + (total < 2 ? total : 2) * a_slot > budget) return -1;
+    int sa = (int)((budget - fixed - (size_t)sb * B_SLOT) / a_slot);
     if (sa > total) sa = total;
-    if (ks > 1 && (size_t)sa * a_stage < (size_t)mt * NB * TILE_ROWS * 4) return -1;   // the split-K exchange reuses the weight stages
+    if ((ks > 1 || geglu) && (size_t)sa * a_slot < (size_t)NB * TILE_ROWS * 4) return -1;
     p.sa = sa;
     p.sb = sb;
-    const size_t smem = fixed + (size_t)sb * B_STAGE + (size_t)sa * a_stage;
-    return geglu ? launch_tcd<2>(b, p, tiles, smem) : launch_tcd<1>(b, p, tiles, smem);
+    const size_t smem = fixed + (size_t)sb * B_SLOT + (size_t)sa * a_slot;
+    CUtensorMap x_map;
+    int st = make_x_map(&x_map, input->dptr, m, kk);
+    if (st != LC_OK) return st;
+    return launch_tcd(b, p, x_map, tiles, smem);
 }
