@@ -302,6 +302,32 @@ LC_API int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf
                                         uint32_t num_kv_heads, uint32_t window, uint32_t bits,
                                         uint32_t n_lanes, uint32_t ring_capacity, float softmax_scale);
 
+/* Prefill / multi-row verify attention over codes: query row r of the chunk (rq / out f32 [n_rows, n_q, hd]) sits at
+ * absolute position start_pos + r and attends the keys of its own causal window of the ONE cache that already holds
+ * the chunk's rows: exactly a decode call with current_pos = start_pos + r per row.  The second entry point is the
+ * reference's query-tiled kernel; here both run the same launch (rows of a chunk share the cache through L2). */
+LC_API int lc_flash_attention_tq_prefill_into(lc_kernels *k, lc_batch *b, const lc_buf *rq, const lc_buf *k_codes,
+                                              const lc_buf *k_norms, const lc_buf *v_codes, const lc_buf *v_norms,
+                                              const lc_buf *levels, lc_buf *out, uint32_t head_dim, uint32_t kv_len,
+                                              uint32_t start_pos, uint32_t n_rows, uint32_t num_q_heads,
+                                              uint32_t num_kv_heads, uint32_t window, uint32_t bits,
+                                              uint32_t ring_capacity, float softmax_scale);   /* kernels.rs:5259 */
+LC_API int lc_flash_attention_tq_prefill_tiled_into(lc_kernels *k, lc_batch *b, const lc_buf *rq, const lc_buf *k_codes,
+                                                    const lc_buf *k_norms, const lc_buf *v_codes,
+                                                    const lc_buf *v_norms, const lc_buf *levels, lc_buf *out,
+                                                    uint32_t head_dim, uint32_t kv_len, uint32_t start_pos,
+                                                    uint32_t n_rows, uint32_t num_q_heads, uint32_t num_kv_heads,
+                                                    uint32_t window, uint32_t bits, uint32_t ring_capacity,
+                                                    float softmax_scale);                      /* kernels.rs:5345 */
+/* Rotate -> prefill attention -> inverse-rotate for a chunk: q f16 [n_rows, n_q, hd] in, attn_out f16 out
+ * (QuantizedKvCache::fused_attention_batch_into, kv_cache/quant_cache.rs:620-700). */
+LC_API int lc_tq_attention_prefill_into(lc_kernels *k, lc_batch *b, const lc_buf *q, const lc_buf *k_codes,
+                                        const lc_buf *k_norms, const lc_buf *v_codes, const lc_buf *v_norms,
+                                        const lc_buf *levels, const lc_buf *signs, lc_buf *attn_out, uint32_t head_dim,
+                                        uint32_t kv_len, uint32_t start_pos, uint32_t n_rows, uint32_t num_q_heads,
+                                        uint32_t num_kv_heads, uint32_t window, uint32_t bits, uint32_t ring_capacity,
+                                        float softmax_scale);
+
 /* No counterpart in the reference.  lc_tq_attention_into for callers that must not
  * allocate device memory when they run attention (an HBM budget fully handed to the KV
  * pool, or a latency-critical serving loop that cannot take cudaMalloc's stall): the split-K
@@ -448,6 +474,68 @@ LC_API int lc_model_reset_lane(lc_model *m, uint32_t lane);         /* quant_uni
 LC_API int lc_model_decode_batch_step_into(lc_model *m, lc_batch *b, const lc_buf *tokens,
                                            const lc_buf *positions, uint32_t n_lanes, uint32_t want_logits,
                                            lc_buf *next_tokens);                    /* batched.rs:271 */
+
+/* ------------------------------------------------------------ KV containers -- */
+/* QuantizedKvCache (local-engine/src/kv_cache/quant_cache.rs:73-91): the TurboQuant cache of one layer of one
+ * sequence -- packed K / V codes [rows, n_kv, code_bytes], f16 norms [rows, n_kv], and the codec's levels / signs
+ * (TurboQuant::new with LC_TQ_SEED).  physical_positions < max_positions makes it a sliding-window ring (logical
+ * position p in row p % physical_positions); the constructor's checks are the reference's: bits in 2..=4, head_dim a
+ * power of two <= 512, ring >= sliding_window + 255 (room for a 256-row prefill chunk, quant_cache.rs:191-209). */
+typedef struct lc_kv_cache lc_kv_cache;
+LC_API int lc_kv_cache_create(lc_ctx *ctx, uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_positions,
+                              uint32_t physical_positions, uint32_t sliding_window, uint32_t bits,
+                              lc_kv_cache **out);                                   /* quant_cache.rs:182-228 */
+LC_API void lc_kv_cache_destroy(lc_kv_cache *cache);
+LC_API uint32_t lc_kv_cache_physical_positions(const lc_kv_cache *cache);           /* quant_cache.rs:243-246 */
+LC_API uint32_t lc_kv_cache_ring_capacity(const lc_kv_cache *cache);                /* quant_cache.rs:258-266 */
+LC_API size_t lc_kv_cache_code_bytes(const lc_kv_cache *cache);                     /* quant_cache.rs:278-280 */
+/* The owned buffers (borrowed; any out pointer may be NULL). */
+LC_API int lc_kv_cache_buffers(lc_kv_cache *cache, lc_buf **keys_q, lc_buf **key_norms, lc_buf **values_q,
+                               lc_buf **value_norms, lc_buf **levels, lc_buf **signs); /* quant_cache.rs:283-300 */
+LC_API int lc_kv_cache_reset(lc_kv_cache *cache);                                   /* quant_cache.rs:364-380 */
+/* k_src / v_src: f16 [n_rows, n_kv_heads, head_dim]; position + n_rows <= max_positions. */
+LC_API int lc_kv_cache_write_kv_gpu_into(lc_kv_cache *cache, lc_batch *b, lc_kernels *k, const lc_buf *k_src,
+                                         const lc_buf *v_src, uint32_t position, uint32_t n_rows); /* quant_cache.rs:391-444 */
+/* q, attn_out: f16 [n_q_heads, head_dim].  The reference's rq / vacc scratch arguments are gone: rotate, attend and
+ * rotate back run as one fused call.  softmax_scale: 1.0 for the reference's behaviour. */
+LC_API int lc_kv_cache_fused_attention_into(lc_kv_cache *cache, lc_batch *b, lc_kernels *k, const lc_buf *q,
+                                            lc_buf *attn_out, uint32_t seq_len, uint32_t current_pos,
+                                            uint32_t n_q_heads, uint32_t window, float softmax_scale); /* quant_cache.rs:548-598 */
+/* q, attn_out: f16 [n_rows, n_q_heads, head_dim]; row r at position start_pos + r. */
+LC_API int lc_kv_cache_fused_attention_batch_into(lc_kv_cache *cache, lc_batch *b, lc_kernels *k, const lc_buf *q,
+                                                  lc_buf *attn_out, uint32_t kv_len, uint32_t start_pos,
+                                                  uint32_t n_rows, uint32_t n_q_heads, uint32_t window,
+                                                  float softmax_scale);             /* quant_cache.rs:620-700 */
+/* Prefix snapshots for prompt reuse: rows [0, positions) of the four buffers to / from host memory; `positions` is
+ * clamped to lc_kv_cache_max_snapshot_positions (the ring capacity for a ringed cache). */
+LC_API uint32_t lc_kv_cache_max_snapshot_positions(const lc_kv_cache *cache);       /* quant_cache.rs:311-318 */
+LC_API int lc_kv_cache_snapshot_prefix(const lc_kv_cache *cache, uint32_t positions, void *keys_q, void *values_q,
+                                       void *key_norms, void *value_norms);         /* quant_cache.rs:327-340 */
+LC_API int lc_kv_cache_restore_prefix(lc_kv_cache *cache, uint32_t positions, const void *keys_q,
+                                      const void *values_q, const void *key_norms,
+                                      const void *value_norms);                     /* quant_cache.rs:343-362 */
+
+/* The lane admit / recycle loop of batched decode (Pipeline::run_batched_to_completion,
+ * local-engine/src/pipeline/runner.rs:123-214) over the per-lane pools of an lc_model: more requests than lanes is the
+ * normal case; as lanes finish they are zeroed (lc_model_reset_lane) and the next queued request is admitted.  A round
+ * is: lc_lane_sched_prepare (finalize, admit, fill the host arrays tokens / positions [n_lanes]; idle lanes carry token 0
+ * at position 0), upload + lc_model_decode_batch_step_into with next_tokens, download, lc_lane_sched_consume.  An
+ * admitted lane is fed its prompt one token per step through the same decode step (outputs discarded until the last
+ * prompt token); the reference runs a separate prefill pipeline for that.  `model` may be NULL (no pools to zero). */
+typedef struct lc_lane_sched lc_lane_sched;
+typedef enum lc_stop_reason { LC_STOP_NONE = 0, LC_STOP_EOS = 1, LC_STOP_MAX_TOKENS = 2, LC_STOP_CAPACITY = 3 } lc_stop_reason;
+LC_API int lc_lane_sched_create(lc_model *model, uint32_t n_lanes, uint32_t lane_capacity, uint32_t eos_token,
+                                lc_lane_sched **out);
+LC_API void lc_lane_sched_destroy(lc_lane_sched *s);
+LC_API int lc_lane_sched_submit(lc_lane_sched *s, uint64_t id, const uint32_t *prompt, uint32_t prompt_len,
+                                uint32_t max_new_tokens);
+LC_API int lc_lane_sched_prepare(lc_lane_sched *s, uint32_t *tokens, uint32_t *positions, uint32_t *n_active);
+LC_API int lc_lane_sched_consume(lc_lane_sched *s, const uint32_t *next_tokens);    /* runner.rs:196-208, 100-109 */
+/* Pop one completed request in completion order; *n_out = 0 and *reason = 0 when none is ready.  With out_tokens NULL
+ * only *n_out / *reason / *id are reported and the request stays queued. */
+LC_API int lc_lane_sched_pop_finished(lc_lane_sched *s, uint64_t *id, uint32_t *out_tokens, uint32_t capacity,
+                                      uint32_t *n_out, int *reason);
+LC_API uint32_t lc_lane_sched_pending(const lc_lane_sched *s);   /* queued + running requests */
 
 #ifdef __cplusplus
 }

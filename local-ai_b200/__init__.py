@@ -26,3 +26,4 @@ from . import synth  # noqa: F401
 from . import model  # noqa: F401
 from . import sharding  # noqa: F401
 from .model import DecodeModel, ModelConfig, e2b_like_config  # noqa: F401
+from .containers import LaneScheduler, QuantizedKvCache  # noqa: F401

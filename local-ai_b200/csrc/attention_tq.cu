@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(NT) tq_attn_split_kernel(const TqAttnParams p)
             if (p.status && threadIdx.x == 0) atomicExch(p.status, LC_DEV_STATUS_POSITION);
         }
     } else {
-        pos = p.current_pos;
+        pos = p.current_pos + (p.row_positions ? lane_idx : 0u);
         seq_len = min(p.kv_len, pos + 1u);
     }
     const uint32_t win_start = (p.window > 0u && pos + 1u > p.window) ? (pos + 1u - p.window) : 0u;
@@ -320,7 +320,10 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
                  const lc_buf *kc, const lc_buf *kn, const lc_buf *vc, const lc_buf *vn, const lc_buf *levels,
                  const lc_buf *signs, lc_buf *out, const lc_buf *positions, uint32_t hd, uint32_t kv_len,
                  uint32_t current_pos, uint32_t lane_capacity, uint32_t n_q, uint32_t n_kv, uint32_t window,
-                 uint32_t bits, uint32_t n_lanes, uint32_t ring, float scale) {
+                 uint32_t bits, uint32_t n_lanes, uint32_t ring, float scale, uint32_t n_rows = 0) {
+    // n_rows != 0: prefill / multi-row verify over one cache: row r at position current_pos + r (n_lanes is ignored)
+    const bool prefill = n_rows != 0;
+    if (prefill) n_lanes = n_rows;
     if (!k || !b || !rq_or_q || !kc || !kn || !vc || !vn || !levels || !out || (fused && !signs))
         return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     if (bits < 2 || bits > 4) return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: bits %u not in 2..=4", name, bits);
@@ -344,9 +347,10 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
         rows = (size_t)n_lanes * lane_capacity;
         len_max = ring ? ring : lane_capacity;
     } else {
-        const uint32_t seq_len = kv_len < current_pos + 1 ? kv_len : current_pos + 1;
+        const uint32_t last_pos = current_pos + (prefill ? n_rows - 1 : 0);   // the row that sees the most keys
+        const uint32_t seq_len = kv_len < last_pos + 1 ? kv_len : last_pos + 1;
         rows = ring ? (ring < seq_len ? ring : seq_len) : seq_len;
-        const uint32_t ws = (window > 0 && current_pos + 1 > window) ? current_pos + 1 - window : 0;
+        const uint32_t ws = (window > 0 && last_pos + 1 > window) ? last_pos + 1 - window : 0;
         len_max = seq_len > ws ? seq_len - ws : 0;
         lane_capacity = 0;
     }
@@ -424,6 +428,7 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     p.positions = positions ? (const uint32_t *)positions->dptr : nullptr;
     p.kv_len = kv_len;
     p.current_pos = current_pos;
+    p.row_positions = prefill ? 1 : 0;
     p.lane_capacity = lane_capacity;
     p.n_q = n_q;
     p.n_kv = n_kv;
@@ -491,6 +496,48 @@ int lc_tq_attention_into(lc_kernels *k, lc_batch *b, const lc_buf *q, const lc_b
     return tq_attention("tq_attention", k, b, q, true, k_codes, k_norms, v_codes, v_norms, levels, signs, attn_out,
                         nullptr, head_dim, kv_len, current_pos, 0, num_q_heads, num_kv_heads, window, bits, 1,
                         ring_capacity, softmax_scale);
+}
+
+// Prefill / multi-row verify over codes (shaders/attention_flash_tq.metal:290-556, kernels.rs:5259-5420): row r of the
+// chunk is a decode query at position start_pos + r over the one cache that already holds the chunk's rows.  Here both
+// reference kernels map onto the decode kernels with the chunk's rows as the grid's third dimension: the tensor-core
+// kernel already reads every K/V row once for all q-heads of a kv-head, and the rows of a chunk re-read the cache from
+// L2, which is what the reference's query-tiled kernel buys with its threadgroup tiles.  So the "tiled" entry point
+// is the same launch; it keeps the reference's name and argument list so callers can switch either way.
+int lc_flash_attention_tq_prefill_into(lc_kernels *k, lc_batch *b, const lc_buf *rq, const lc_buf *k_codes,
+                                       const lc_buf *k_norms, const lc_buf *v_codes, const lc_buf *v_norms,
+                                       const lc_buf *levels, lc_buf *out, uint32_t head_dim, uint32_t kv_len,
+                                       uint32_t start_pos, uint32_t n_rows, uint32_t num_q_heads, uint32_t num_kv_heads,
+                                       uint32_t window, uint32_t bits, uint32_t ring_capacity, float softmax_scale) {
+    if (n_rows == 0) return LC_OK;
+    return tq_attention("flash_attention_tq_prefill", k, b, rq, false, k_codes, k_norms, v_codes, v_norms, levels, nullptr,
+                        out, nullptr, head_dim, kv_len, start_pos, 0, num_q_heads, num_kv_heads, window, bits, 1,
+                        ring_capacity, softmax_scale, n_rows);
+}
+
+int lc_flash_attention_tq_prefill_tiled_into(lc_kernels *k, lc_batch *b, const lc_buf *rq, const lc_buf *k_codes,
+                                             const lc_buf *k_norms, const lc_buf *v_codes, const lc_buf *v_norms,
+                                             const lc_buf *levels, lc_buf *out, uint32_t head_dim, uint32_t kv_len,
+                                             uint32_t start_pos, uint32_t n_rows, uint32_t num_q_heads,
+                                             uint32_t num_kv_heads, uint32_t window, uint32_t bits,
+                                             uint32_t ring_capacity, float softmax_scale) {
+    if (n_rows == 0) return LC_OK;
+    return tq_attention("flash_attention_tq_prefill_tiled", k, b, rq, false, k_codes, k_norms, v_codes, v_norms, levels,
+                        nullptr, out, nullptr, head_dim, kv_len, start_pos, 0, num_q_heads, num_kv_heads, window, bits, 1,
+                        ring_capacity, softmax_scale, n_rows);
+}
+
+// The three dispatches QuantizedKvCache::fused_attention_batch_into issues (kv_cache/quant_cache.rs:620-700) in one
+// call: q f16 [n_rows, n_q, hd] in, attn_out f16 out.
+int lc_tq_attention_prefill_into(lc_kernels *k, lc_batch *b, const lc_buf *q, const lc_buf *k_codes, const lc_buf *k_norms,
+                                 const lc_buf *v_codes, const lc_buf *v_norms, const lc_buf *levels, const lc_buf *signs,
+                                 lc_buf *attn_out, uint32_t head_dim, uint32_t kv_len, uint32_t start_pos, uint32_t n_rows,
+                                 uint32_t num_q_heads, uint32_t num_kv_heads, uint32_t window, uint32_t bits,
+                                 uint32_t ring_capacity, float softmax_scale) {
+    if (n_rows == 0) return LC_OK;
+    return tq_attention("tq_attention_prefill", k, b, q, true, k_codes, k_norms, v_codes, v_norms, levels, signs, attn_out,
+                        nullptr, head_dim, kv_len, start_pos, 0, num_q_heads, num_kv_heads, window, bits, 1, ring_capacity,
+                        softmax_scale, n_rows);
 }
 
 int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *q, const lc_buf *k_codes,
@@ -633,6 +680,7 @@ extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const 
     p.positions = nullptr;
     p.kv_len = kv_len;
     p.current_pos = current_pos;
+    p.row_positions = 0;
     p.lane_capacity = 0;
     p.n_q = num_q_heads;
     p.n_kv = num_kv_heads;

@@ -13,6 +13,9 @@ struct TqAttnParams {
     float *partial;       // [lanes * n_q * n_splits] x (2 + HD) floats
     const uint32_t *positions;  // per-lane positions, or NULL for the single-sequence form
     uint32_t kv_len, current_pos;
+    // row_positions (prefill / multi-row verify): the grid's z index is a query ROW of one sequence, row r at position
+    // current_pos + r; all rows read the same cache (lane_capacity = 0) and row r sees min(kv_len, its position + 1) keys.
+    uint32_t row_positions;
     uint32_t lane_capacity, n_q, n_kv, window, ring, n_splits, group;  // group = n_q / n_kv
     uint32_t fused_q, direct_out;
     float scale;

@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
             if (p.status && threadIdx.x == 0) atomicExch(p.status, LC_DEV_STATUS_POSITION);
         }
     } else {
-        pos = p.current_pos;
+        pos = p.current_pos + (p.row_positions ? lane_idx : 0u);
         seq_len = min(p.kv_len, pos + 1u);
     }
     const uint32_t win_start = (p.window > 0u && pos + 1u > p.window) ? (pos + 1u - p.window) : 0u;

@@ -199,6 +199,17 @@ def flash_attention_tq_batched(rq, kc, kn, vc, vn, levels, positions, hd, lane_c
     return out
 
 
+def flash_attention_tq_prefill(rq, kc, kn, vc, vn, levels, hd, kv_len, start_pos, n_rows, n_q, n_kv, window, bits, ring,
+                               scale=1.0, tiled=False) -> np.ndarray:
+    """[n_rows, n_q, hd] f32; `tiled` selects the f16-tile arithmetic of the query-tiled shader."""
+    out = np.empty(n_rows * n_q * hd, dtype=np.float32)
+    fn = lib().orc_flash_attention_tq_prefill_tiled if tiled else lib().orc_flash_attention_tq_prefill
+    fn(_p(_c(rq, np.float32)), _p(_c(kc, np.uint8)), _p(_h(kn)), _p(_c(vc, np.uint8)), _p(_h(vn)),
+       _p(_c(levels, np.float32)), _p(out), _u(hd), _u(kv_len), _u(start_pos), _u(n_rows), _u(n_q), _u(n_kv), _u(window),
+       _u(bits), _u(ring), _f(scale))
+    return out
+
+
 def tq_attention_fused(q, kc, kn, vc, vn, levels, signs, positions, hd, lane_capacity, n_q, n_kv, window, bits,
                        n_lanes, ring, scale=1.0, kv_len=0, current_pos=0) -> np.ndarray:
     out = np.empty(n_lanes * n_q * hd, dtype=np.uint16)

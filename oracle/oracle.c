@@ -523,6 +523,83 @@ ORC_API void orc_flash_attention_tq_batched(const float *rq, const uint8_t *kc,
         }
 }
 
+/* Prefill / multi-row verify attention over codes, shaders/attention_flash_tq.metal:290-423
+ * (flash_attention_tq_prefill): query row r sits at absolute position start_pos + r, attends
+ * t in [win_start(r), min(kv_len, start_pos + r + 1)) of ONE cache (slot = (t % ring) * n_kv +
+ * kv_head), i.e. exactly the single-position kernel with current_pos = start_pos + r.
+ * rq, out: [n_rows, n_q, hd] f32. */
+ORC_API void orc_flash_attention_tq_prefill(const float *rq, const uint8_t *kc, const uint16_t *kn,
+                                            const uint8_t *vc, const uint16_t *vn,
+                                            const float *levels, float *out, unsigned hd,
+                                            unsigned kv_len, unsigned start_pos, unsigned n_rows,
+                                            unsigned n_q, unsigned n_kv, unsigned window,
+                                            unsigned bits, unsigned ring, float scale) {
+#pragma omp parallel for schedule(dynamic) collapse(2)
+    for (int r = 0; r < (int)n_rows; r++)
+        for (int qh = 0; qh < (int)n_q; qh++) {
+            unsigned pos = start_pos + (unsigned)r;
+            unsigned seq_len = kv_len < pos + 1 ? kv_len : pos + 1;
+            unsigned win_start = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+            size_t qb = ((size_t)r * n_q + (size_t)qh) * hd;
+            attn_codes_one(rq + qb, kc, kn, vc, vn, levels, out + qb, hd, bits, 0, n_kv,
+                           (unsigned)qh / (n_q / n_kv), win_start, seq_len, ring, scale);
+        }
+}
+
+/* The query-tiled variant, shaders/attention_flash_tq.metal:425-556
+ * (flash_attention_tq_prefill_tiled): same rows and windows, but every K / V element is first
+ * rounded to half as `half(norm * levels[code])` (:497-498) and the dot products run over those
+ * rounded tiles; the shader's own test holds it to 5e-3 of the non-tiled kernel
+ * (local-metal/src/kernels.rs:10287-10448).  Evaluated in f64 over the f16-rounded elements. */
+ORC_API void orc_flash_attention_tq_prefill_tiled(const float *rq, const uint8_t *kc,
+                                                  const uint16_t *kn, const uint8_t *vc,
+                                                  const uint16_t *vn, const float *levels,
+                                                  float *out, unsigned hd, unsigned kv_len,
+                                                  unsigned start_pos, unsigned n_rows, unsigned n_q,
+                                                  unsigned n_kv, unsigned window, unsigned bits,
+                                                  unsigned ring, float scale) {
+    size_t cb = orc_tq_code_bytes(hd, bits);
+#pragma omp parallel for schedule(dynamic) collapse(2)
+    for (int r = 0; r < (int)n_rows; r++)
+        for (int qh = 0; qh < (int)n_q; qh++) {
+            unsigned pos = start_pos + (unsigned)r, kvh = (unsigned)qh / (n_q / n_kv);
+            unsigned seq_len = kv_len < pos + 1 ? kv_len : pos + 1;
+            unsigned win_start = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+            size_t qb = ((size_t)r * n_q + (size_t)qh) * hd;
+            float *o = out + qb;
+            for (unsigned d = 0; d < hd; d++) o[d] = 0.0f;
+            if (seq_len <= win_start) continue;
+            unsigned n = seq_len - win_start;
+            double *logit = (double *)malloc(sizeof(double) * n);
+            double *acc = (double *)calloc(hd, sizeof(double));
+            double mx = -INFINITY, sum = 0.0;
+            for (unsigned t = win_start; t < seq_len; t++) {
+                size_t slot = (size_t)(ring ? t % ring : t) * n_kv + kvh;
+                const uint8_t *c = kc + slot * cb;
+                float nk = h2f(kn[slot]);
+                double dot = 0.0;
+                for (unsigned d = 0; d < hd; d++)
+                    dot += (double)rq[qb + d] * (double)h2f(f2h(nk * levels[unpack_code(c, d, bits)]));
+                dot *= (double)scale;
+                logit[t - win_start] = dot;
+                if (dot > mx) mx = dot;
+            }
+            for (unsigned t = win_start; t < seq_len; t++) {
+                size_t slot = (size_t)(ring ? t % ring : t) * n_kv + kvh;
+                const uint8_t *c = vc + slot * cb;
+                float nv = h2f(vn[slot]);
+                double w = exp(logit[t - win_start] - mx);
+                sum += w;
+                for (unsigned d = 0; d < hd; d++)
+                    acc[d] += w * (double)h2f(f2h(nv * levels[unpack_code(c, d, bits)]));
+            }
+            double inv = sum > 0.0 ? 1.0 / sum : 0.0;
+            for (unsigned d = 0; d < hd; d++) o[d] = (float)(acc[d] * inv);
+            free(acc);
+            free(logit);
+        }
+}
+
 /* The call sequence the KV containers always issue around the code-space
  * kernel (local-engine/src/kv_cache/quant_cache.rs:565-596,
  * quant_unified_pool.rs:218-256): rq = R(q) from f16 q, attention in rotated
