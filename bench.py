@@ -82,13 +82,13 @@ class QuantMatvec:
     (the reference's own microbenchmark cycles 35 distinct weight sets so each read is cold,
     local-metal/src/kernels.rs:8898-8902).  One step = one pass over all copies."""
 
-    def __init__(self, la, ctx, kernels, fmt: str, rows: int, cols: int, m: int = 1):
+    def __init__(self, la, ctx, kernels, fmt: str, rows: int, cols: int, m: int = 1, min_copies: int = 8):
         self.la, self.ctx, self.k, self.fmt, self.rows, self.cols, self.m = la, ctx, kernels, fmt, rows, cols, m
         l2 = ctx.caps()["l2_bytes"]
         gen = la.synth.q4_0_weights if fmt == "q4_0" else la.synth.tq2_0_weights
         w0 = gen(rows, cols, seed=1)
         self.wbytes = w0.size
-        self.copies = max(8, int(np.ceil(2.2 * l2 / self.wbytes)))
+        self.copies = max(min_copies, int(np.ceil(2.2 * l2 / self.wbytes)))
         self.weights = []
         for c in range(self.copies):
             w = w0 if c == 0 else np.roll(w0, c * 4099 * (18 if fmt == "q4_0" else 66))  # distinct rows order, same blocks
@@ -154,8 +154,16 @@ class QuantMatvec:
         launch_ms = ms_per_step / self.launches_per_step
         achieved = self.alg_bytes_per_launch / (launch_ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_kind": peak_kind, "kernel": "qgemv_kernel",
+                "traffic": None, "peak_kind": peak_kind, "kernel": self.kernel_name(),
+                "us_per_launch": launch_ms * 1e3, "algorithmic_bytes_per_launch": self.alg_bytes_per_launch,
                 "frac_of_nominal_8tbs": achieved / 8000.0}
+
+    def kernel_name(self) -> str:
+        if self.m == 1:
+            return "qgemv_mma_stream_kernel" if self.rows >= 18944 else "qgemv_kernel"
+        if self.fmt == "tq2_0" and 8 < self.m <= 64:
+            return "qgemm_tcd_kernel (tcgen05)"
+        return "qgemm_mma_kernel" if self.m <= 64 else "qgemm_tc_kernel (tcgen05)"
 
     def value(self, ms_per_step: float) -> float:
         return self.alg_bytes_per_launch * self.units_per_step / (ms_per_step * 1e-3) / 1e9
@@ -173,6 +181,125 @@ class QuantMatvec:
         return dt / reps, self.alg_bytes_per_launch / (dt / reps) / 1e9, f"{reps} passes over one {self.rows}x{self.cols} matrix"
 
 
+class TqAttention:
+    """Config 3: fused decode attention over tq2 codes (8 q heads, 1 kv head, head_dim 256, softmax scale 1/16) for
+    `lanes` sequences at `context` cached positions each, every lane attending context + 1 keys.  A step is one
+    pass over `pools` distinct KV pools (together larger than L2 twice over), one fused call each (query rotation,
+    split-K attention over codes, merge, inverse rotation; f16 query in, f16 out), launched from one CUDA graph.
+    Pools hold seeded random codes and norms ~ |N(0, I_256)|; the cost does not depend on the values."""
+
+    def __init__(self, la, ctx, kernels, lanes: int, context: int):
+        self.la, self.ctx, self.k, self.lanes, self.context = la, ctx, kernels, lanes, context
+        self.hd, self.n_q, self.n_kv, self.bits = 256, 8, 1, 2
+        cb = la.tq_code_bytes(self.hd, self.bits)
+        self.cap = context + 1
+        rows = lanes * self.cap
+        self.alg_bytes_per_launch = rows * self.n_kv * (2 * cb + 4) + 2 * lanes * self.n_q * self.hd * 2
+        l2 = ctx.caps()["l2_bytes"]
+        self.pools_n = max(3, int(np.ceil(2.2 * l2 / self.alg_bytes_per_launch)))
+        self.levels = la.CudaBuffer.from_slice(ctx, la.tq_levels(self.hd, self.bits))
+        self.signs = la.CudaBuffer.from_slice(ctx, la.tq_signs(self.hd, la.TQ_SEED))
+        self.q_host = la.synth.normal_f16((lanes, self.n_q, self.hd), 3)
+        self.q = la.CudaBuffer.from_slice(ctx, self.q_host)
+        self.out = la.CudaBuffer.empty(ctx, lanes * self.n_q * self.hd * 2)
+        self.positions = la.CudaBuffer.from_slice(ctx, np.full(lanes, context, np.uint32))
+        self.pools = []
+        codes = la.synth.splitmix64(4242, rows * cb // 8).view(np.uint8)
+        norms = (16.0 * la.synth.uniform(4243, rows, 0.9, 1.1)).astype(np.float16)
+        for i in range(self.pools_n):
+            # the same bytes at a different rotation per pool: distinct addresses, any code values
+            kc = la.CudaBuffer.from_slice(ctx, np.roll(codes, 64 * (i + 1)))
+            vc = la.CudaBuffer.from_slice(ctx, np.roll(codes, 64 * (i + 7)))
+            kn = la.CudaBuffer.from_slice(ctx, np.roll(norms, i))
+            vn = la.CudaBuffer.from_slice(ctx, np.roll(norms, i + 3))
+            self.pools.append((kc, kn, vc, vn))
+        self.name = f"fused tq2 decode attention, {lanes} lane(s) x {context + 1} keys, 8 q heads / 1 kv head of 256"
+        self.units_per_step = self.pools_n
+        self.graph, self.launches_per_step = None, None
+
+    def _enqueue(self, b, i):
+        kc, kn, vc, vn = self.pools[i]
+        self.k.tq_attention_batched_into(b, self.q, kc, kn, vc, vn, self.levels, self.signs, self.out, self.positions,
+                                         self.hd, self.cap, self.n_q, self.n_kv, 0, self.bits, self.lanes, 0, 1.0 / 16.0)
+
+    def prepare(self):
+        b = self.la.CommandBatch.new(self.ctx)
+        for i in range(self.pools_n):
+            self._enqueue(b, i)
+        self.launches_per_step = b.dispatch_count()
+        b.commit_and_wait()
+        b = self.la.CommandBatch.capture(self.ctx)
+        for i in range(self.pools_n):
+            self._enqueue(b, i)
+        self.graph = b.end_capture()
+
+    def step(self):
+        self.graph.launch()
+
+    def check(self, orc):
+        """Lane 0 of the last pool against the oracle's fused attention (2e-3 of max(|want|, 1): f16 output)."""
+        kc, kn, vc, vn = self.pools[-1]
+        cb = self.la.tq_code_bytes(self.hd, self.bits)
+        n = self.cap
+        want = orc.tq_attention_fused(self.q_host[:1], kc.as_slice(np.uint8, n * cb), kn.as_slice(np.float16, n),
+                                      vc.as_slice(np.uint8, n * cb), vn.as_slice(np.float16, n),
+                                      self.la.tq_levels(self.hd, self.bits), self.la.tq_signs(self.hd, self.la.TQ_SEED),
+                                      np.array([self.context], np.uint32), self.hd, self.cap, self.n_q, self.n_kv, 0,
+                                      self.bits, 1, 0, 1.0 / 16.0).astype(np.float32).reshape(-1)
+        got = self.out.as_slice(np.float16, self.n_q * self.hd).astype(np.float32)
+        assert np.all(np.abs(got - want) <= 2e-3 * np.maximum(np.abs(want), 1.0)), "attention differs from the oracle"
+
+    def prepare_e2e(self):
+        nb = self.lanes * self.n_q * self.hd * 2
+        self.hq, self.ho = self.la.PinnedHost(nb), self.la.PinnedHost(nb)
+        self.hq.array[:] = self.q_host.view(np.uint8).reshape(-1)
+        self.h2d, self.d2h = nb * self.pools_n, nb * self.pools_n
+
+    def step_e2e(self):
+        b = self.la.CommandBatch.new(self.ctx)
+        for i in range(self.pools_n):
+            b.upload(self.q, 0, self.hq.ptr, self.hq.nbytes)
+            self._enqueue(b, i)
+            b.download(self.out, 0, self.ho.ptr, self.ho.nbytes)
+        b.commit_and_wait()
+
+    def metric(self):
+        return "tq_decode_attention_hbm_gbs", "GB/s"
+
+    def l2_note(self):
+        return (f"inputs larger than L2 ({self.pools_n} distinct KV pools, "
+                f"{self.pools_n * self.alg_bytes_per_launch / 1e6:.0f} MB per pass)")
+
+    def value(self, ms_per_step: float) -> float:
+        return self.alg_bytes_per_launch * self.units_per_step / (ms_per_step * 1e-3) / 1e9
+
+    def roofline(self, ms_per_step: float, peak: float, peak_kind: str, timed):
+        us = ms_per_step * 1e3 / self.pools_n
+        achieved = self.alg_bytes_per_launch / (us * 1e-6) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_kind": peak_kind,
+                "kernel": "tq2_attn_mma_kernel + tq_attn_merge_kernel (one fused call)", "us_per_launch": us,
+                "algorithmic_bytes_per_launch": self.alg_bytes_per_launch, "frac_of_nominal_8tbs": achieved / 8000.0}
+
+    def cpu_sample(self, orc, threads: int):
+        kc, kn, vc, vn = self.pools[0]
+        cb = self.la.tq_code_bytes(self.hd, self.bits)
+        n = self.cap
+        args = (self.q_host[:1], kc.as_slice(np.uint8, n * cb), kn.as_slice(np.float16, n), vc.as_slice(np.uint8, n * cb),
+                vn.as_slice(np.float16, n), self.la.tq_levels(self.hd, self.bits),
+                self.la.tq_signs(self.hd, self.la.TQ_SEED), np.array([self.context], np.uint32), self.hd, self.cap,
+                self.n_q, self.n_kv, 0, self.bits, 1, 0, 1.0 / 16.0)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            orc.tq_attention_fused(*args)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > 3.0 or reps >= 50:
+                break
+        per = dt / reps
+        return per, n * (2 * cb + 4) / per / 1e9, f"{reps} passes over one lane of {n} keys (oracle, all host threads)"
+
+
 class DecodeStep:
     """Config 4: one decode step of the synthetic Gemma-4-E2B-like dense decoder (35 layers, hidden 1536,
     8 q heads / 1 kv head of 256, GeGLU 6144, 4:1 SWA(512):full, TQ2_0 projections, Q4_0 tied 262144-row
@@ -182,17 +309,21 @@ class DecodeStep:
     on the device, the whole step in one CUDA graph."""
 
     def __init__(self, la, ctx, kernels, lanes: int = 64, context: int = 8192, n_layers: int = 35,
-                 vocab: int = 262144):
+                 vocab: int = 262144, share: "DecodeStep | None" = None):
+        """`share`: another DecodeStep of the same architecture whose host-side weights are reused (the synthetic
+        tensors depend on the layer shapes and the seed only)."""
         self.la, self.ctx, self.k, self.lanes, self.context = la, ctx, kernels, lanes, context
         self.cfg = la.e2b_like_config(max_lanes=lanes, max_context=context + 512, n_layers=n_layers, vocab=vocab)
         cfg = self.cfg
         self.model = la.DecodeModel(ctx, kernels, cfg)
+        if share is not None:
+            assert (share.cfg.n_layers, share.cfg.vocab) == (n_layers, vocab)
         self.host_layers = []
         for i in range(n_layers):
-            t = la.model.synth_layer(cfg, i, seed=4)
+            t = share.host_layers[i] if share is not None else la.model.synth_layer(cfg, i, seed=4)
             self.model.set_layer(i, t)
             self.host_layers.append(t)
-        self.emb, self.fnorm = la.model.synth_embedding(cfg, seed=4)
+        self.emb, self.fnorm = (share.emb, share.fnorm) if share is not None else la.model.synth_embedding(cfg, seed=4)
         self.model.set_embedding(self.emb, self.fnorm)
         self.geo = []
         self.kv_bytes = 0
@@ -241,13 +372,42 @@ class DecodeStep:
                 "read per step")
 
     def check(self, orc):
-        """Size-independent checks at full size: tokens in range, lane isolation (duplicate lanes agree)."""
-        nt = self.next_tokens.as_slice(np.uint32)
-        assert np.all(nt < self.cfg.vocab), "argmax out of range"
+        """At full size: the first lanes' logits against the oracle's step on the same weights, tokens, positions
+        and KV pools (the rule of the decode-step tests: 2e-3 of the logit scale when the rows written by the step
+        come out byte-identical, the reference's 0.15 envelope otherwise, pipeline/batched.rs:471-477); tokens in
+        range; the device argmax against its own logits."""
+        la, cfg = self.la, self.cfg
         nl = min(2, self.lanes)
-        logits = self.model.logits_buffer().as_slice(np.float32, nl * self.cfg.vocab).reshape(nl, -1)
-        assert np.all(np.isfinite(logits)), "non-finite logits"
-        assert all(nt[i] == int(np.argmax(logits[i])) for i in range(nl)), "argmax kernel disagrees"
+        self.tokens.copy_from_bytes(self.tokens_host.view(np.uint8))          # the end-to-end loop fed tokens back
+        self.positions.copy_from_bytes(self.positions_host.view(np.uint8))
+        om_cfg = la.e2b_like_config(max_lanes=nl, max_context=cfg.max_context, n_layers=cfg.n_layers, vocab=cfg.vocab)
+        om = orc.OracleModel(om_cfg, self.host_layers, self.emb, self.fnorm, self.geo)
+        cb = la.tq_code_bytes(cfg.head_dim, cfg.kv_bits)
+
+        def lanes_of(i):   # the first nl lanes of layer i's device pools: (name, bytes)
+            kv = self.model.kv_buffers(i)
+            rows = nl * kv["lane_rows"] * cfg.n_kv_heads
+            return [(n, kv[n].as_slice(np.uint8, rows * (cb if n.endswith("codes") else 2))) for n in
+                    ("k_codes", "v_codes", "k_norms", "v_norms")]
+        for i, pool in enumerate(om.pools):
+            for name, dev in lanes_of(i):
+                pool[name].view(np.uint8)[:] = dev
+        want, _ = om.decode_batch_step(self.tokens_host[:nl], self.positions_host[:nl])
+        b = la.CommandBatch.new(self.ctx)
+        self.model.decode_batch_step_into(b, self.tokens, self.positions, self.lanes, True, self.next_tokens)
+        b.commit_and_wait()
+        nt = self.next_tokens.as_slice(np.uint32, self.lanes)
+        assert np.all(nt < cfg.vocab), "argmax out of range"
+        got = self.model.logits_buffer().as_slice(np.float32, nl * cfg.vocab).reshape(nl, -1)
+        assert np.all(np.isfinite(got)), "non-finite logits"
+        assert all(nt[i] == int(np.argmax(got[i])) for i in range(nl)), "argmax kernel disagrees with its logits"
+        mism = sum(int(np.sum(dev != pool[name].view(np.uint8))) for i, pool in enumerate(om.pools)
+                   for name, dev in lanes_of(i))
+        scale = max(1.0, float(np.abs(want).max()))
+        err = float(np.abs(got - want).max()) / scale
+        tol = 2e-3 if mism == 0 else 0.15
+        assert err <= tol, f"logits differ from the oracle by {err:.3e} of scale ({mism} differing KV bytes)"
+        self.parity = {"lanes_checked": nl, "max_err_of_logit_scale": err, "kv_bytes_differing": mism, "tolerance": tol}
 
     def prepare_e2e(self):
         self.h_in = self.la.PinnedHost(2 * self.lanes * 4, dtype=np.uint32)
@@ -278,12 +438,13 @@ class DecodeStep:
     def value(self, ms_per_step: float) -> float:
         return self.lanes / (ms_per_step * 1e-3)
 
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, mean over one GeGLU and one down
-    # launch of an ncu capture of the 5-layer workload (5.12 MB and 3.27 MB, cold cache; summary committed with the profiles).
-    FFN_TRAFFIC_BYTES = 4194800
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel: mean over one GeGLU and one down
+    # launch of an ncu capture (cold cache) of the 5-layer workload, whose launches have the full model's shapes.
+    FFN_TRAFFIC = {"bytes": None, "profile": "profiles/qgemm_tcd_tq2_0_m64.md",
+                   "captured_on": "bench.py --workload decode_b64_small (same launch shapes as decode_b64)"}
 
     def roofline(self, ms_per_step: float, peak: float, peak_kind: str, timed):
-        """The dominant kernel by time is the decode matmul (qgemm_mma_kernel, TQ2_0, m = lanes): its two largest
+        """The dominant kernel by time is the decode matmul (qgemm_tcd_kernel, TQ2_0, m = lanes): its two largest
         launch shapes, the fused GeGLU projection and the down projection of every layer, are run alone here (one
         graph, every layer's own weights, 2 x n_layers launches) and timed with CUDA events.  Algorithmic bytes per
         launch = rows * row_bytes + m * cols * 2 + m * rows * 2.  The whole-step figures are reported beside it."""
@@ -316,24 +477,32 @@ class DecodeStep:
         achieved = per_launch / (us * 1e-6) / 1e9
         whole = self.alg_bytes_per_step / (ms_per_step * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": self.FFN_TRAFFIC_BYTES if m == 64 else None, "peak_kind": peak_kind,
-                "kernel": (f"{'qgemm_mma_kernel' if m <= 64 else 'qgemm_tc_kernel (tcgen05) + gelu_mul'}<TQ2_0, m={m}>: GeGLU + down "
-                           f"projections of {cfg.n_layers} layers, {n_launch} launches"),
+                "traffic": self.FFN_TRAFFIC["bytes"] if m == 64 else None,
+                "traffic_source": self.FFN_TRAFFIC if m == 64 else None, "peak_kind": peak_kind,
+                "kernel": (f"{'qgemv_kernel' if m <= 8 else 'qgemm_tcd_kernel (tcgen05)' if m <= 64 else 'qgemm_tc_kernel (tcgen05) + gelu_mul'}"
+                           f"<TQ2_0, m={m}>: GeGLU + down projections of {cfg.n_layers} layers, {n_launch} launches"),
                 "us_per_launch": us, "algorithmic_bytes_per_launch": per_launch,
                 "launches_timed_alone_share_of_step": ms / ms_per_step,
                 "whole_step": {"achieved": whole, "frac": whole / peak, "algorithmic_bytes_per_step": self.alg_bytes_per_step,
                                "bound_tok_s": self.lanes / (self.alg_bytes_per_step / (peak * 1e9))}}
 
     def cpu_sample(self, orc, threads: int):
-        lanes = 2
-        om = orc.OracleModel(self.cfg, self.host_layers, self.emb, self.fnorm, self.geo)
-        # the oracle's pools start empty; attention cost is what matters, so mark rows as present via positions
+        lanes = min(2, self.lanes)
+        cfg = self.la.e2b_like_config(max_lanes=lanes, max_context=self.cfg.max_context, n_layers=self.cfg.n_layers,
+                                      vocab=self.cfg.vocab)
+        om = orc.OracleModel(cfg, self.host_layers, self.emb, self.fnorm, self.geo)
+        # the oracle's pools start empty (zero rows); the attention's cost does not depend on the values
         tok = self.tokens_host[:lanes].copy()
         pos = self.positions_host[:lanes].copy()
-        t0 = time.perf_counter()
-        om.decode_batch_step(tok, pos)
-        dt = time.perf_counter() - t0
-        return dt, lanes / dt, f"1 step of {lanes} lanes at context {self.context} (f64-accumulating oracle, all host threads)"
+        orc.set_step_baseline_matmul(True)      # projections as the CPU baseline computes them: f16 weights, f32 dot
+        try:
+            t0 = time.perf_counter()
+            om.decode_batch_step(tok, pos)
+            dt = time.perf_counter() - t0
+        finally:
+            orc.set_step_baseline_matmul(False)
+        return dt, lanes / dt, (f"1 step of {lanes} lane(s) at context {self.context}, all {self.cfg.n_layers} layers + "
+                                "vocabulary projection (dequant to f16 + f32 dot, all host threads)")
 
 
 class RaggedDecode(DecodeStep):
@@ -347,7 +516,7 @@ class RaggedDecode(DecodeStep):
     One step = one token for every one of the 512 sequences; value = 512 / step time (strong scaling)."""
 
     def __init__(self, la, ctx, kernels, rank: int, world: int, vocab_mode: str = "replicated", total: int = 512,
-                 n_layers: int = 35, vocab: int = 262144, max_ctx: int = 131072):
+                 n_layers: int = 35, vocab: int = 262144, max_ctx: int = 131072, share: "DecodeStep | None" = None):
         self.la, self.ctx, self.k = la, ctx, kernels
         self.rank, self.world, self.vocab_mode, self.total = rank, world, vocab_mode, total
         ctxs = la.synth.lognormal_contexts(total, seed=55, hi=max_ctx)
@@ -360,9 +529,9 @@ class RaggedDecode(DecodeStep):
         self.model = la.DecodeModel(ctx, kernels, cfg)
         self.host_layers = []
         for i in range(n_layers):
-            t = la.model.synth_layer(cfg, i, seed=4)
+            t = share.host_layers[i] if share is not None else la.model.synth_layer(cfg, i, seed=4)
             self.model.set_layer(i, t)
-        self.emb, self.fnorm = la.model.synth_embedding(cfg, seed=4)
+        self.emb, self.fnorm = (share.emb, share.fnorm) if share is not None else la.model.synth_embedding(cfg, seed=4)
         self.emb_buf = la.CudaBuffer.from_slice(ctx, self.emb)
         self.model.set_embedding(self.emb_buf, self.fnorm)
         self.emb = None
@@ -507,10 +676,15 @@ WORKLOADS = {
     "matvec_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 6144, 1536, 1),
     "matmul_tq2_0_m16": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 16),
     "matmul_tq2_0_m64": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 64),
-    "matvec_vocab_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 262144, 1536, 1),
+    "matmul_tq2_0_m256": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 256),
+    "matvec_vocab_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 262144, 1536, 1, min_copies=3),
     "decode_b64": lambda la, ctx, k: DecodeStep(la, ctx, k, 64, 8192),
     "decode_b1": lambda la, ctx, k: DecodeStep(la, ctx, k, 1, 8192),
     "decode_b64_small": lambda la, ctx, k: DecodeStep(la, ctx, k, 64, 2048, n_layers=5, vocab=32768),
+    "attention_32768x1": lambda la, ctx, k: TqAttention(la, ctx, k, 1, 32767),
+    "attention_131072x1": lambda la, ctx, k: TqAttention(la, ctx, k, 1, 131071),
+    "attention_8193x64": lambda la, ctx, k: TqAttention(la, ctx, k, 64, 8192),
+    "attention_2049x64": lambda la, ctx, k: TqAttention(la, ctx, k, 64, 2048),
     "ragged512": None, "ragged512_allgather": None, "ragged64_small": None, "ragged64_small_allgather": None,
 }
 DEFAULT_WORKLOAD = "decode_b64"
@@ -528,6 +702,88 @@ def _load_module(name: str, path: Path):
     return mod
 
 
+def run_extras(la, ctx, kernels, headline, timed_local, orc, peak: float, peak_kind: str, device: int) -> dict:
+    """The other halves of the metric, measured in the same process after the headline (rank 0 only, no
+    collective): batch-1 decode, the fused-dequant matvec / matmul configurations and decode attention at the
+    configured contexts.  Each entry has its own CUDA-event time over about half a second of back-to-back steps,
+    its own clock sample, its algorithmic bytes and its check against the oracle."""
+    import gc
+    out = {}
+
+    def measure(key, make):
+        try:
+            wl = make()
+            wl.prepare()
+            ms1 = timed_local(wl.step, 3, 3)
+            steps = int(min(2000, max(5, 0.5e3 / max(ms1, 1e-3))))
+            sampler = ClockSampler(device)
+            sampler.start()
+            time.sleep(0.3)
+            ms = timed_local(wl.step, steps, 3)
+            clocks = sampler.stop()
+            wl.check(orc)
+            metric, unit = wl.metric()
+            r = wl.roofline(ms, peak, peak_kind, timed_local)
+            rec = {"metric": metric, "value": wl.value(ms), "unit": unit, "ms_per_step": ms, "steps": steps,
+                   "workload": wl.name, "l2_policy": wl.l2_note(), "kernel": r["kernel"], "clocks": clocks}
+            if isinstance(wl, DecodeStep):
+                w = r["whole_step"]
+                rec.update({"hbm_gbs": w["achieved"], "frac": w["frac"], "algorithmic_bytes_per_step": w["algorithmic_bytes_per_step"],
+                            "gpu_launches_per_step": wl.launches_per_step, "parity": getattr(wl, "parity", None)})
+            else:
+                rec.update({"hbm_gbs": r["achieved"], "frac": r["frac"], "us_per_launch": r["us_per_launch"],
+                            "algorithmic_bytes_per_launch": r["algorithmic_bytes_per_launch"]})
+            rec["peak_kind"] = peak_kind
+            out[key] = rec
+            del wl
+        except Exception as e:   # an extra must not take the headline down with it
+            out[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        gc.collect()
+
+    measure("decode_b1", lambda: DecodeStep(la, ctx, kernels, 1, 8192, share=headline))
+    measure("matvec_q4_0", lambda: QuantMatvec(la, ctx, kernels, "q4_0", 6144, 1536, 1))
+    for m in (1, 16, 64):
+        measure(f"matvec_tq2_0_m{m}", lambda m=m: QuantMatvec(la, ctx, kernels, "tq2_0", 8192, 1536, m))
+    measure("matvec_vocab_q4_0", lambda: QuantMatvec(la, ctx, kernels, "q4_0", 262144, 1536, 1, min_copies=3))
+    measure("attention_32768x1", lambda: TqAttention(la, ctx, kernels, 1, 32767))
+    measure("attention_131072x1", lambda: TqAttention(la, ctx, kernels, 1, 131071))
+    measure("attention_8193x64", lambda: TqAttention(la, ctx, kernels, 64, 8192))
+    return out
+
+
+def run_ragged_extras(la, ctx, kernels, headline, timed, rank: int, world: int, small: bool) -> dict:
+    """Config 5 on `world` GPUs (every rank calls this): 512 ragged sequences sharded by request, vocabulary
+    replicated (no collective) and row-split with the NCCL all-gather of f32 logits; for the latter the two
+    all-gathers are also timed alone, so that the collective's share of the step is a measurement."""
+    import torch
+    kw = dict(total=64, n_layers=5, vocab=32768, max_ctx=8192) if small else {}
+    out = {}
+    wl = RaggedDecode(la, ctx, kernels, rank, world, "replicated", share=headline, **kw)
+    wl.prepare()
+    ms = timed(wl.step, 5, 3)
+    out["ragged512_replicated" if not small else "ragged64_small_replicated"] = {
+        "metric": wl.metric()[0], "value": wl.total / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "n_gpus": world,
+        "workload": wl.name.replace("vocabulary replicated", "vocabulary replicated (no collective)"),
+        "lanes_on_rank0": wl.lanes, "gpu_launches_per_step": wl.launches_per_step}
+    if wl.total % world == 0:
+        wl.vocab_mode = "allgather"
+        wl.prepare()
+        ms = timed(wl.step, 5, 3)
+
+        def gathers():
+            with torch.cuda.stream(wl.t_stream):
+                if world > 1:
+                    wl.dist.all_gather_into_tensor(wl.t_hidden_all, wl.t_hidden_all[rank * wl.lanes:(rank + 1) * wl.lanes].clone())
+                    wl.dist.all_gather_into_tensor(wl.t_logits_all, wl.t_logits_slice)
+        ms_ag = timed(gathers, 5, 3)
+        out["ragged512_allgather" if not small else "ragged64_small_allgather"] = {
+            "metric": wl.metric()[0], "value": wl.total / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "n_gpus": world,
+            "workload": wl.name.replace("vocabulary replicated", "vocabulary row-split + NCCL all-gather of f32 logits"),
+            "allgather_ms_alone": ms_ag, "allgather_bytes_per_step": wl.total * wl.vocab_ * 4 + wl.total * wl.cfg.hidden * 2,
+            "gpu_launches_per_step": wl.launches_per_step}
+    return out
+
+
 def run_reference(args, rank: int, world: int) -> None:
     """The reference's CPU path for this workload on the host cores (rank 0 only): the reference is Rust +
     Metal and cannot be built or run here, so this arm times the oracle's restatement of what the reference
@@ -537,6 +793,7 @@ def run_reference(args, rank: int, world: int) -> None:
     orc = entry.load_oracle()
     synth = _load_module("la_synth", ROOT / "local-ai_b200" / "synth.py")
     name = args.workload
+    orc.set_num_threads(orc.host_threads())   # torch.distributed.run exports OMP_NUM_THREADS=1 to every rank
     threads = orc.num_threads()
     note = ("CPU restatement of the reference's arithmetic (oracle/); the reference's Metal path is unavailable on "
             "this box and its Rust toolchain is absent")
@@ -564,6 +821,7 @@ def run_reference(args, rank: int, world: int) -> None:
         om = orc.OracleModel(cfg, layers, emb, fnorm, geo)
         tok = (synth.splitmix64(7, sample_lanes) % np.uint64(vocab)).astype(np.uint32)
         pos = np.full(sample_lanes, context, np.uint32)
+        orc.set_step_baseline_matmul(True)   # projections as a CPU would run them: weights to f16, naive f32 dot
         for _ in range(min(args.warmup, 1)):
             om.decode_batch_step(tok, pos)
         t0 = time.perf_counter()
@@ -574,14 +832,33 @@ def run_reference(args, rank: int, world: int) -> None:
         metric, unit = (f"decode_tok_s_ragged{lanes_full}" if ragged else f"decode_tok_s_batch{lanes_full}"), "tok/s"
         sample = (f"each step = {sample_lanes} of the {lanes_full} lanes, one token each at context {context}"
                   f"{' (the median of the lognormal contexts)' if ragged else ''}, all {n_layers} "
-                  f"layers + vocabulary projection, {threads} OpenMP threads")
+                  f"layers + vocabulary projection (dequant to f16 + f32 dot), {threads} OpenMP threads")
         wl_name = (f"ragged decode, {lanes_full} sequences (lognormal contexts, median 2048) of the E2B-like decoder" if ragged else
                    f"decode step, E2B-like dense decoder {n_layers} layers, batch {lanes_full}, context {context}, "
                    f"TQ2_0 weights + Q4_0 vocab {vocab}, tq2 KV")
+    elif name.startswith("attention"):
+        keys, lanes_full = {"attention_32768x1": (32768, 1), "attention_131072x1": (131072, 1),
+                            "attention_8193x64": (8193, 64), "attention_2049x64": (2049, 64)}[name]
+        hd, n_q, n_kv, bits, cb = 256, 8, 1, 2, 64
+        codes = synth.splitmix64(4242, keys * cb // 8).view(np.uint8)
+        norms = (16.0 * synth.uniform(4243, keys, 0.9, 1.1)).astype(np.float16)
+        q = synth.normal_f16((1, n_q, hd), 3)
+        a = (q, codes, norms, np.roll(codes, 64 * 7), np.roll(norms, 3), orc.tq_levels(hd, bits), orc.tq_signs(hd, 0x7459C0DE),
+             np.array([keys - 1], np.uint32), hd, keys, n_q, n_kv, 0, bits, 1, 0, 1.0 / 16.0)
+        for _ in range(min(args.warmup, 2)):
+            orc.tq_attention_fused(*a)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            orc.tq_attention_fused(*a)
+        dt = (time.perf_counter() - t0) / args.steps
+        val = keys * (2 * cb + 4) / dt / 1e9
+        metric, unit = "tq_decode_attention_hbm_gbs", "GB/s"
+        sample = f"each step = one of the {lanes_full} lane(s), {keys} keys (fused code-space attention), {threads} OpenMP threads"
+        wl_name = f"fused tq2 decode attention, {lanes_full} lane(s) x {keys} keys, 8 q heads / 1 kv head of 256"
     else:
         shapes = {"matvec_tq2_0": ("tq2_0", 8192, 1536, 1), "matvec_q4_0": ("q4_0", 6144, 1536, 1),
                   "matmul_tq2_0_m16": ("tq2_0", 8192, 1536, 16), "matmul_tq2_0_m64": ("tq2_0", 8192, 1536, 64),
-                  "matvec_vocab_q4_0": ("q4_0", 262144, 1536, 1)}
+                  "matmul_tq2_0_m256": ("tq2_0", 8192, 1536, 256), "matvec_vocab_q4_0": ("q4_0", 262144, 1536, 1)}
         fmt, rows, cols, m = shapes[name]
         w = (synth.q4_0_weights if fmt == "q4_0" else synth.tq2_0_weights)(rows, cols, seed=1)
         x = synth.normal_f16((m, cols), seed=2)
@@ -596,12 +873,13 @@ def run_reference(args, rank: int, world: int) -> None:
         val = alg / dt / 1e9
         metric, unit = "fused_quant_matvec_hbm_gbs", "GB/s"
         sample = f"each step = one {rows}x{cols} {fmt} matrix (dequant to f16 + naive f32 dot), {threads} OpenMP threads"
-        wl_name = name
+        wl_name = f"{fmt} fused dequant mat{'vec' if m == 1 else 'mul'} {rows}x{cols} batch {m}"
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl_name, "note": note},
+        "config": {"workload": wl_name, "l2_policy": "host memory: no device cache involved", "launch": "host threads (OpenMP)",
+                   "replicas": 1, "note": note},
         "cpu_baseline": {"value": val, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -615,6 +893,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra record (the metric's other halves)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()
@@ -679,12 +958,20 @@ def main() -> None:
     clocks = sampler.stop() if rank == 0 else None
     wl.prepare_e2e()
     ms_e2e = timed(wl.step_e2e, max(3, args.steps // 4), 3)
+    extra = {}
+    with_extra = not args.no_extra and args.workload in ("decode_b64", "decode_b64_small")
+    if with_extra and world > 1:
+        try:
+            extra.update(run_ragged_extras(la, ctx, kernels, wl, timed, rank, world, small=args.workload.endswith("small")))
+        except Exception as e:
+            extra["ragged"] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     orc = entry.load_oracle()
+    orc.set_num_threads(orc.host_threads())   # a launcher may have exported OMP_NUM_THREADS=1 to every rank
     wl.check(orc)
     peak, peak_kind = measured_peaks()
     metric, unit = wl.metric()
@@ -701,11 +988,17 @@ def main() -> None:
         "gpu_launches": wl.launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if getattr(wl, "parity", None):
+        line["parity"] = wl.parity
     if not args.no_cpu_baseline:
         threads = orc.num_threads()
         sec, gbs, desc = wl.cpu_sample(orc, 0)
         line["cpu_baseline"] = {"value": gbs, "unit": unit, "cores": threads, "kind": "port",
                                 "sample": desc + f"; {sec * 1e3:.2f} ms"}
+    if with_extra and args.workload == "decode_b64":
+        extra.update(run_extras(la, ctx, kernels, wl, timed_local, orc, peak, peak_kind, local_rank))
+    if extra:
+        line["extra"] = extra
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

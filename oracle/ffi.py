@@ -293,6 +293,26 @@ def num_threads() -> int:
     return lib().orc_num_threads()
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads for every later call (a launcher may have exported OMP_NUM_THREADS=1)."""
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
+def host_threads() -> int:
+    """The host threads this process may use: its affinity mask, else the CPU count."""
+    import os
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def set_step_baseline_matmul(on: bool) -> None:
+    """Decode-step projections in the CPU baseline's arithmetic (weights rounded to f16, f32 dot) instead of the
+    checker's f64 accumulation."""
+    lib().orc_set_step_baseline_matmul(C.c_int(1 if on else 0))
+
+
 # ---- decode step (composition) ----
 class _OrcLayer(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "attn_norm", "q_norm", "k_norm",

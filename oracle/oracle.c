@@ -809,6 +809,16 @@ typedef struct {
     const orc_layer *layers;
 } orc_model;
 
+/* Which arithmetic the decode step's projections use: 0 = the f64-accumulating checker (orc_matmul_nt_quant),
+ * 1 = the CPU baseline's (orc_baseline_matmul_nt: weights rounded to f16, naive f32 dot), which is what the
+ * reference would run on a CPU and what the bench times. */
+static int g_step_baseline_matmul = 0;
+ORC_API void orc_set_step_baseline_matmul(int on) { g_step_baseline_matmul = on; }
+static void step_matmul(int fmt, const uint16_t *a, const uint8_t *w, size_t m, size_t k, size_t n, float *c) {
+    if (g_step_baseline_matmul) orc_baseline_matmul_nt(fmt, a, w, m, k, n, c, 0);
+    else orc_matmul_nt_quant(fmt, a, w, m, k, n, c);
+}
+
 static void f32_to_f16_vec(const float *s, uint16_t *d, size_t n) {
     for (size_t i = 0; i < n; i++) d[i] = f2h(s[i]);
 }
@@ -843,13 +853,13 @@ ORC_API void orc_decode_batch_step(const orc_model *m, const uint32_t *tokens,
     for (unsigned li = 0; li < m->n_layers; li++) {
         const orc_layer *L = &m->layers[li];
         orc_rms_norm(x, L->attn_norm, NULL, normed, H, n, m->eps);
-        orc_matmul_nt_quant(ORC_TQ2_0, normed, L->wq, n, H, qd, tmp);
+        step_matmul(ORC_TQ2_0, normed, L->wq, n, H, qd, tmp);
         f32_to_f16_vec(tmp, q, n * qd);
         orc_qk_norm(q, L->q_norm, HD, n * NQ, m->eps);
         orc_rope(q, positions, m->rope_theta, HD, NQ, n, 1.0f);
-        orc_matmul_nt_quant(ORC_TQ2_0, normed, L->wk, n, H, kd, tmp);
+        step_matmul(ORC_TQ2_0, normed, L->wk, n, H, kd, tmp);
         f32_to_f16_vec(tmp, k, n * kd);
-        orc_matmul_nt_quant(ORC_TQ2_0, normed, L->wv, n, H, kd, tmp);
+        step_matmul(ORC_TQ2_0, normed, L->wv, n, H, kd, tmp);
         f32_to_f16_vec(tmp, v, n * kd);
         orc_qk_norm(k, L->k_norm, HD, n * NKV, m->eps);
         orc_rms_norm(v, ones, NULL, v, HD, n * NKV, m->eps);
@@ -861,24 +871,26 @@ ORC_API void orc_decode_batch_step(const orc_model *m, const uint32_t *tokens,
         orc_tq_attention_fused(q, L->k_codes, L->k_norms, L->v_codes, L->v_norms, m->levels,
                                m->signs, attn, positions, HD, L->lane_rows, NQ, NKV, L->window,
                                m->bits, n, L->ring, m->softmax_scale, 0, 0);
-        orc_matmul_nt_quant(ORC_TQ2_0, attn, L->wo, n, qd, H, tmp);
+        step_matmul(ORC_TQ2_0, attn, L->wo, n, qd, H, tmp);
         f32_to_f16_vec(tmp, ffn, (size_t)n * H);
         orc_rms_norm(ffn, L->post_attn_norm, x, resid, H, n, m->eps);
         orc_rms_norm(resid, L->ffn_norm, NULL, normed, H, n, m->eps);
-        orc_matmul_nt_quant(ORC_TQ2_0, normed, L->wgate, n, H, I, tmp);
+        step_matmul(ORC_TQ2_0, normed, L->wgate, n, H, I, tmp);
         f32_to_f16_vec(tmp, gate, (size_t)n * I);
-        orc_matmul_nt_quant(ORC_TQ2_0, normed, L->wup, n, H, I, tmp);
+        step_matmul(ORC_TQ2_0, normed, L->wup, n, H, I, tmp);
         f32_to_f16_vec(tmp, up, (size_t)n * I);
         orc_gelu_mul(gate, up, gate, (size_t)n * I);
-        orc_matmul_nt_quant(ORC_TQ2_0, gate, L->wdown, n, I, H, tmp);
+        step_matmul(ORC_TQ2_0, gate, L->wdown, n, I, H, tmp);
         f32_to_f16_vec(tmp, ffn, (size_t)n * H);
         orc_rms_norm(ffn, L->post_ffn_norm, resid, x, H, n, m->eps);
     }
     orc_rms_norm(x, m->final_norm, NULL, normed, H, n, m->eps);
     if (hidden_out) memcpy(hidden_out, normed, 2 * (size_t)n * H);
-    if (logits) orc_matmul_nt_quant(ORC_Q4_0, normed, m->embed, n, H, m->vocab, logits);
+    if (logits) step_matmul(ORC_Q4_0, normed, m->embed, n, H, m->vocab, logits);
     free(x); free(normed); free(q); free(k); free(v); free(attn); free(resid);
     free(gate); free(up); free(ffn); free(ones); free(tmp);
 }
 
 ORC_API int orc_num_threads(void) { return omp_get_max_threads(); }
+/* The bench sets the thread count itself (a launcher may export OMP_NUM_THREADS=1 to every rank). */
+ORC_API void orc_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
