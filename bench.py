@@ -512,12 +512,17 @@ class RaggedDecode(DecodeStep):
       replicated  every rank projects its own lanes against the whole table; no collective (default);
       allgather   the table is row-split; hidden rows are all-gathered (1.5 MB), every rank projects its rows for
                   all 512 lanes and the f32 logit slices are all-gathered over NCCL (537 MB per step), as the
-                  configuration states; greedy tokens are then taken on every rank.
+                  configuration states; greedy tokens are then taken on every rank (per-shard records + merge);
+      pairs       as allgather up to the projection; then every rank reduces its slice to (max, first index) per
+                  lane on the device and only those 8 bytes per lane are all-gathered and merged with the
+                  first-maximum rule (local-engine/src/sampler.rs:148-158).
+    The collectives go through the C ABI (lc_comm_*), enqueued on the step's stream.
     One step = one token for every one of the 512 sequences; value = 512 / step time (strong scaling)."""
 
     def __init__(self, la, ctx, kernels, rank: int, world: int, vocab_mode: str = "replicated", total: int = 512,
-                 n_layers: int = 35, vocab: int = 262144, max_ctx: int = 131072, share: "DecodeStep | None" = None):
-        self.la, self.ctx, self.k = la, ctx, kernels
+                 n_layers: int = 35, vocab: int = 262144, max_ctx: int = 131072, share: "DecodeStep | None" = None,
+                 comm=None):
+        self.la, self.ctx, self.k, self.comm = la, ctx, kernels, comm
         self.rank, self.world, self.vocab_mode, self.total = rank, world, vocab_mode, total
         ctxs = la.synth.lognormal_contexts(total, seed=55, hi=max_ctx)
         self.shards = la.sharding.shard_lanes(ctxs, world)
@@ -579,48 +584,70 @@ class RaggedDecode(DecodeStep):
                                           self.next_tokens if local_vocab else None)
         self.graph = b.end_capture()
         if not local_vocab:
-            assert self.total % self.world == 0, "the all-gather variant needs equal shards"
-            dev = torch.device("cuda", ctx.device)
-            self.t_stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+            assert self.total % self.world == 0, "the row-split variants need equal shards"
+            assert self.world == 1 or self.comm is not None, "the row-split variants need a communicator"
             lo, hi = la.sharding.vocab_rows(self.vocab_, self.world, self.rank)
-            self.rows = hi - lo
+            self.rows, self.lo = hi - lo, lo
             rb = cfg.hidden // 32 * 18
             self.table_slice = la.CudaBuffer.wrap(ctx, self.emb_buf.device_ptr + lo * rb, self.rows * rb)
-            self.t_hidden_all = torch.empty(self.total, cfg.hidden, dtype=torch.float16, device=dev)
-            self.t_logits_slice = torch.empty(self.total, self.rows, dtype=torch.float32, device=dev)
-            self.t_logits_all = torch.empty(self.world, self.total, self.rows, dtype=torch.float32, device=dev)
-            self.hidden_all = la.CudaBuffer.wrap(ctx, self.t_hidden_all.data_ptr(), self.t_hidden_all.numel() * 2)
-            self.logits_slice = la.CudaBuffer.wrap(ctx, self.t_logits_slice.data_ptr(), self.t_logits_slice.numel() * 4)
+            if not hasattr(self, "hidden_all"):
+                self.hidden_all = la.CudaBuffer.empty(ctx, self.total * cfg.hidden * 2)
+                self.logits_slice = la.CudaBuffer.empty(ctx, self.total * self.rows * 4)
+                self.pairs_all = la.CudaBuffer.empty(ctx, self.world * self.total * 8)
+                self.next_all = la.CudaBuffer.empty(ctx, self.total * 4)
+            if self.vocab_mode == "allgather" and not hasattr(self, "logits_all"):
+                self.logits_all = la.CudaBuffer.empty(ctx, self.world * self.total * self.rows * 4)
             self.hidden_local = self.model.hidden_buffer()
-            self.dist = dist
-            self.launches_per_step += 1
+            b = la.CommandBatch.new(ctx)
+            self._enqueue_vocab(b)
+            self.launches_per_step += b.dispatch_count()
+            b.commit_and_wait()
+
+    def _gather(self, b, buf, bytes_per_rank, send=None):
+        """All-gather into `buf` ([world] x bytes_per_rank); `send` = None means in place (this rank's slot of buf)."""
+        if self.world > 1:
+            self.comm.all_gather_into(b, send if send is not None else buf, 0 if send is not None else self.rank * bytes_per_rank,
+                                      buf, bytes_per_rank)
+        elif send is not None:
+            b.blit_buffer_copy(send, 0, buf, 0, bytes_per_rank)
+
+    def _enqueue_vocab(self, b):
+        la, ctx, cfg, n, total = self.la, self.ctx, self.cfg, self.lanes, self.total
+        b.blit_buffer_copy(self.hidden_local, 0, self.hidden_all, self.rank * n * cfg.hidden * 2, n * cfg.hidden * 2)
+        self._gather(b, self.hidden_all, n * cfg.hidden * 2)
+        self.k.matmul_nt_q4_0_f32out_into(b, self.hidden_all, self.table_slice, self.logits_slice, total, cfg.hidden, self.rows)
+        pair_slot = lambda r: la.CudaBuffer.wrap(ctx, self.pairs_all.device_ptr + r * total * 8, total * 8)
+        if self.vocab_mode == "allgather":
+            self._gather(b, self.logits_all, total * self.rows * 4, send=self.logits_slice)
+            for r in range(self.world):
+                sl = la.CudaBuffer.wrap(ctx, self.logits_all.device_ptr + r * total * self.rows * 4, total * self.rows * 4)
+                self.k.argmax_pairs_f32_into(b, sl, pair_slot(r), total, self.rows, r * self.rows)
+        else:
+            self.k.argmax_pairs_f32_into(b, self.logits_slice, pair_slot(self.rank), total, self.rows, self.lo)
+            self._gather(b, self.pairs_all, total * 8)
+        self.k.merge_argmax_pairs_into(b, self.pairs_all, self.next_all, total, self.world)
+
+    def gathers_alone(self):
+        """The variant's collectives without the compute between them (timed alone by the bench)."""
+        b = self.la.CommandBatch.new(self.ctx)
+        self._gather(b, self.hidden_all, self.lanes * self.cfg.hidden * 2)
+        if self.vocab_mode == "allgather":
+            self._gather(b, self.logits_all, self.total * self.rows * 4, send=self.logits_slice)
+        else:
+            self._gather(b, self.pairs_all, self.total * 8)
+        for p in getattr(self, "_pend2", []):
+            p.wait()
+        self._pend2 = [b.commit_async()]
 
     def step(self):
         self.graph.launch()
         if self.vocab_mode == "replicated":
             return
-        import torch
-        la, ctx, cfg = self.la, self.ctx, self.cfg
-        n = self.lanes
-        for p in getattr(self, "_pend", []):   # the previous step's batches (long finished): release their events
+        for p in getattr(self, "_pend", []):   # the previous step's batch (long finished): release its event
             p.wait()
-        with torch.cuda.stream(self.t_stream):
-            b = la.CommandBatch.new(ctx)
-            b.blit_buffer_copy(self.hidden_local, 0, self.hidden_all, self.rank * n * cfg.hidden * 2, n * cfg.hidden * 2)
-            pend = [b.commit_async()]   # enqueued on the context's stream; the collective below orders itself after it
-            mine = self.t_hidden_all[self.rank * n:(self.rank + 1) * n]
-            if self.world > 1:
-                self.dist.all_gather_into_tensor(self.t_hidden_all, mine.clone())
-            b = la.CommandBatch.new(ctx)
-            self.k.matmul_nt_q4_0_f32out_into(b, self.hidden_all, self.table_slice, self.logits_slice, self.total,
-                                              cfg.hidden, self.rows)
-            pend.append(b.commit_async())
-            if self.world > 1:
-                self.dist.all_gather_into_tensor(self.t_logits_all, self.t_logits_slice)
-            else:
-                self.t_logits_all[0].copy_(self.t_logits_slice)
-            self.t_next = la.sharding.greedy_from_logit_slices(self.t_logits_all, self.rows)
-        self._pend = pend
+        b = self.la.CommandBatch.new(self.ctx)
+        self._enqueue_vocab(b)
+        self._pend = [b.commit_async()]
 
     def l2_note(self):
         return (f"inputs larger than L2: {self.weight_bytes / 1e6:.0f} MB of weights + {self.kv_bytes / 1e6:.0f} MB of KV "
@@ -631,7 +658,8 @@ class RaggedDecode(DecodeStep):
             nt = self.next_tokens.as_slice(np.uint32, self.lanes)
             assert np.all(nt < self.cfg.vocab), "argmax out of range"
         else:
-            assert int(self.t_next.max()) < self.cfg.vocab
+            self.ctx.synchronize()
+            assert int(self.next_all.as_slice(np.uint32, self.total).max()) < self.cfg.vocab
 
     def prepare_e2e(self):
         self.h_in = self.la.PinnedHost(2 * self.lanes * 4, dtype=np.uint32)
@@ -654,10 +682,10 @@ class RaggedDecode(DecodeStep):
             b.commit_and_wait()
             self.h_in.array[: self.lanes] = self.h_out.array
         else:
-            self.ctx.synchronize()
-            import torch
-            torch.cuda.synchronize()
-            self.h_in.array[: self.lanes] = self.t_next[self.rank * self.lanes:(self.rank + 1) * self.lanes].cpu().numpy().astype(np.uint32)
+            b = self.la.CommandBatch.new(self.ctx)
+            b.download(self.next_all, self.rank * self.lanes * 4, self.h_out.ptr, self.lanes * 4)
+            b.commit_and_wait()
+            self.h_in.array[: self.lanes] = self.h_out.array
         self.e2e_steps += 1
         self.h_in.array[self.lanes:] = self.e2e_pos0 + (self.e2e_steps % 200)
 
@@ -685,7 +713,8 @@ WORKLOADS = {
     "attention_131072x1": lambda la, ctx, k: TqAttention(la, ctx, k, 1, 131071),
     "attention_8193x64": lambda la, ctx, k: TqAttention(la, ctx, k, 64, 8192),
     "attention_2049x64": lambda la, ctx, k: TqAttention(la, ctx, k, 64, 2048),
-    "ragged512": None, "ragged512_allgather": None, "ragged64_small": None, "ragged64_small_allgather": None,
+    "ragged512": None, "ragged512_allgather": None, "ragged512_pairs": None,
+    "ragged64_small": None, "ragged64_small_allgather": None, "ragged64_small_pairs": None,
 }
 DEFAULT_WORKLOAD = "decode_b64"
 
@@ -751,36 +780,31 @@ def run_extras(la, ctx, kernels, headline, timed_local, orc, peak: float, peak_k
     return out
 
 
-def run_ragged_extras(la, ctx, kernels, headline, timed, rank: int, world: int, small: bool) -> dict:
-    """Config 5 on `world` GPUs (every rank calls this): 512 ragged sequences sharded by request, vocabulary
-    replicated (no collective) and row-split with the NCCL all-gather of f32 logits; for the latter the two
-    all-gathers are also timed alone, so that the collective's share of the step is a measurement."""
-    import torch
+def run_ragged_extras(la, ctx, kernels, headline, timed, rank: int, world: int, comm, small: bool) -> dict:
+    """Config 5 on `world` GPUs (every rank calls this): 512 ragged sequences sharded by request with the vocabulary
+    projection (A) replicated, no collective; (B) row-split with the NCCL all-gather of the f32 logit slices; (C)
+    row-split with per-shard (max, first index) records, 8 bytes per lane gathered and merged on the device.  For B and
+    C the collectives are also timed alone, so that their share of the step is a measurement."""
     kw = dict(total=64, n_layers=5, vocab=32768, max_ctx=8192) if small else {}
-    out = {}
-    wl = RaggedDecode(la, ctx, kernels, rank, world, "replicated", share=headline, **kw)
-    wl.prepare()
-    ms = timed(wl.step, 5, 3)
-    out["ragged512_replicated" if not small else "ragged64_small_replicated"] = {
-        "metric": wl.metric()[0], "value": wl.total / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "n_gpus": world,
-        "workload": wl.name.replace("vocabulary replicated", "vocabulary replicated (no collective)"),
-        "lanes_on_rank0": wl.lanes, "gpu_launches_per_step": wl.launches_per_step}
-    if wl.total % world == 0:
-        wl.vocab_mode = "allgather"
+    out, tag = {}, "ragged64_small" if small else "ragged512"
+    wl = RaggedDecode(la, ctx, kernels, rank, world, "replicated", share=headline, comm=comm, **kw)
+    for mode, label in (("replicated", "vocabulary replicated (no collective)"),
+                        ("allgather", "vocabulary row-split + NCCL all-gather of f32 logits"),
+                        ("pairs", "vocabulary row-split + all-gather of (max, index) records, 8 B per lane")):
+        if mode != "replicated" and wl.total % world != 0:
+            continue
+        wl.vocab_mode = mode
         wl.prepare()
         ms = timed(wl.step, 5, 3)
-
-        def gathers():
-            with torch.cuda.stream(wl.t_stream):
-                if world > 1:
-                    wl.dist.all_gather_into_tensor(wl.t_hidden_all, wl.t_hidden_all[rank * wl.lanes:(rank + 1) * wl.lanes].clone())
-                    wl.dist.all_gather_into_tensor(wl.t_logits_all, wl.t_logits_slice)
-        ms_ag = timed(gathers, 5, 3)
-        out["ragged512_allgather" if not small else "ragged64_small_allgather"] = {
-            "metric": wl.metric()[0], "value": wl.total / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "n_gpus": world,
-            "workload": wl.name.replace("vocabulary replicated", "vocabulary row-split + NCCL all-gather of f32 logits"),
-            "allgather_ms_alone": ms_ag, "allgather_bytes_per_step": wl.total * wl.vocab_ * 4 + wl.total * wl.cfg.hidden * 2,
-            "gpu_launches_per_step": wl.launches_per_step}
+        wl.check(None)
+        rec = {"metric": wl.metric()[0], "value": wl.total / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "n_gpus": world,
+               "workload": wl.name.replace("vocabulary replicated", label), "lanes_on_rank0": wl.lanes,
+               "gpu_launches_per_step": wl.launches_per_step}
+        if mode != "replicated":
+            rec["collectives_ms_alone"] = timed(wl.gathers_alone, 5, 3)
+            rec["collective_bytes_per_rank_per_step"] = wl.total // world * wl.cfg.hidden * 2 + (
+                wl.total * wl.rows * 4 if mode == "allgather" else wl.total * 8)
+        out[f"{tag}_{mode}"] = rec
     return out
 
 
@@ -807,7 +831,8 @@ def run_reference(args, rank: int, world: int) -> None:
         lanes_full, context, n_layers, vocab = {"decode_b64": (64, 8192, 35, 262144), "decode_b1": (1, 8192, 35, 262144),
                                                 "decode_b64_small": (64, 2048, 5, 32768),
                                                 "ragged512": (512, 2048, 35, 262144), "ragged512_allgather": (512, 2048, 35, 262144),
-                                                "ragged64_small": (64, 2048, 5, 32768),
+                                                "ragged512_pairs": (512, 2048, 35, 262144),
+                                                "ragged64_small": (64, 2048, 5, 32768), "ragged64_small_pairs": (64, 2048, 5, 32768),
                                                 "ragged64_small_allgather": (64, 2048, 5, 32768)}[name]
         cfg = Cfg()
         cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.inter = 1536, 8, 1, 256, 6144
@@ -911,12 +936,26 @@ def main() -> None:
     la = entry.load_package()
     ctx = la.CudaContext.new(local_rank)
     kernels = la.Kernels.new(ctx)
+    comm = None
+
+    def communicator():
+        """NCCL through the C ABI; the unique id made on rank 0 travels over the process group."""
+        nonlocal comm
+        if comm is None and world > 1:
+            uid = torch.zeros(la.Communicator.ID_BYTES, dtype=torch.uint8, device="cuda")
+            if rank == 0:
+                uid.copy_(torch.frombuffer(bytearray(la.Communicator.unique_id()), dtype=torch.uint8))
+            dist.broadcast(uid, src=0)
+            comm = la.Communicator(ctx, bytes(uid.cpu().numpy().tobytes()), rank, world)
+        return comm
+
     if args.workload.startswith("ragged"):
-        mode = "allgather" if args.workload.endswith("allgather") else "replicated"
+        mode = "allgather" if args.workload.endswith("allgather") else "pairs" if args.workload.endswith("pairs") else "replicated"
+        c = communicator() if mode != "replicated" else None
         if "small" in args.workload:
-            wl = RaggedDecode(la, ctx, kernels, rank, world, mode, total=64, n_layers=5, vocab=32768, max_ctx=8192)
+            wl = RaggedDecode(la, ctx, kernels, rank, world, mode, total=64, n_layers=5, vocab=32768, max_ctx=8192, comm=c)
         else:
-            wl = RaggedDecode(la, ctx, kernels, rank, world, mode)
+            wl = RaggedDecode(la, ctx, kernels, rank, world, mode, comm=c)
     else:
         wl = WORKLOADS[args.workload](la, ctx, kernels)
     wl.prepare()
@@ -962,7 +1001,8 @@ def main() -> None:
     with_extra = not args.no_extra and args.workload in ("decode_b64", "decode_b64_small")
     if with_extra and world > 1:
         try:
-            extra.update(run_ragged_extras(la, ctx, kernels, wl, timed, rank, world, small=args.workload.endswith("small")))
+            extra.update(run_ragged_extras(la, ctx, kernels, wl, timed, rank, world, communicator(),
+                                           small=args.workload.endswith("small")))
         except Exception as e:
             extra["ragged"] = {"error": f"{type(e).__name__}: {e}"[:300]}
 

@@ -435,6 +435,33 @@ LC_API int lc_embed_rows_q4_0_into(lc_kernels *k, lc_batch *b, const lc_buf *tab
 LC_API int lc_argmax_rows_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc_buf *out_index,
                                    uint32_t rows, uint32_t cols);
 
+/* Row-split vocabulary projection (the 262144-row table split across GPUs, one process per GPU): per-shard greedy
+ * argmax as pairs {f32 max, u32 first index + index_offset} and their merge over shards laid out [shards][rows] in
+ * index order, with the first-maximum rule of local-engine/src/sampler.rs:148-158 (strict '>' in index order; an
+ * all -inf / NaN row yields the first shard's first index).  8 bytes per lane cross the links instead of a logit slice. */
+LC_API int lc_argmax_pairs_f32_into(lc_kernels *k, lc_batch *b, const lc_buf *values, lc_buf *pairs, uint32_t rows,
+                                    uint32_t cols, uint32_t index_offset);
+LC_API int lc_merge_argmax_pairs_into(lc_kernels *k, lc_batch *b, const lc_buf *pairs_all, lc_buf *out_index,
+                                      uint32_t rows, uint32_t shards);
+
+/* ------------------------------------------------------------- multi-GPU -- */
+/* NCCL behind the ABI, for the all-gather of the row-split vocabulary projection.  The reference is single-GPU; these
+ * entry points exist for the sharded configuration only.  libnccl is loaded at run time (LOCAL_CUDA_NCCL_LIB, else the
+ * loader's libnccl.so.2): without it every call returns LC_ERR_NCCL, as does any NCCL error.  lc_comm_unique_id runs on
+ * one rank; the host carries the 128 bytes to the others; every rank then calls lc_comm_create (collective, blocking).
+ * lc_comm_all_gather_into enqueues on the batch's stream: bytes_per_rank bytes at send + send_offset go to
+ * recv + rank * bytes_per_rank on every rank (send may be recv itself: in place). */
+#define LC_COMM_ID_BYTES 128
+typedef struct lc_comm lc_comm;
+LC_API int lc_comm_available(void);
+LC_API int lc_comm_unique_id(uint8_t *id);                      /* out: LC_COMM_ID_BYTES bytes */
+LC_API int lc_comm_create(lc_ctx *ctx, const uint8_t *id, uint32_t rank, uint32_t world, lc_comm **out);
+LC_API void lc_comm_destroy(lc_comm *c);
+LC_API uint32_t lc_comm_rank(const lc_comm *c);
+LC_API uint32_t lc_comm_world(const lc_comm *c);
+LC_API int lc_comm_all_gather_into(lc_batch *b, lc_comm *c, const lc_buf *send, size_t send_offset, lc_buf *recv,
+                                   size_t bytes_per_rank);
+
 /* ----------------------------------------------------------- decode step -- */
 /* One batched decode step of the dense decoder in the op order of
  * TransformerLayer::forward_decode_batch_turbo (local-engine/src/layer.rs:731-868) inside

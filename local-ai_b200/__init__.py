@@ -10,6 +10,7 @@ The directory name carries a hyphen, so import it through the loader in
 from .kernels import (  # noqa: F401
     TQ_SEED,
     CommandBatch,
+    Communicator,
     CudaBuffer,
     CudaContext,
     CudaGraph,

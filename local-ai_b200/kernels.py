@@ -248,6 +248,42 @@ class Kernels:
             self._h = None
 
 
+class Communicator:
+    """NCCL behind the C ABI (lc_comm_*): one communicator per process / GPU.  `unique_id()` runs on one rank; the
+    host carries the bytes to the others (a file, a socket, an existing process group); every rank then constructs
+    its Communicator (collective)."""
+
+    ID_BYTES = 128
+
+    @staticmethod
+    def available() -> bool:
+        return _lib.load().lc_comm_available() == 0
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_uint8 * Communicator.ID_BYTES)()
+        _check(_lib.load().lc_comm_unique_id(buf))
+        return bytes(buf)
+
+    def __init__(self, ctx: CudaContext, uid: bytes, rank: int, world: int):
+        assert len(uid) == self.ID_BYTES
+        self._lib = ctx._lib
+        self._ctx = ctx
+        h = C.c_void_p()
+        buf = (C.c_uint8 * self.ID_BYTES).from_buffer_copy(uid)
+        _check(self._lib.lc_comm_create(ctx._h, buf, rank, world, C.byref(h)))
+        self._h = h
+        self.rank, self.world = rank, world
+
+    def all_gather_into(self, batch, send: CudaBuffer, send_offset: int, recv: CudaBuffer, bytes_per_rank: int) -> None:
+        _check(self._lib.lc_comm_all_gather_into(batch._h, self._h, send._h, send_offset, recv._h, bytes_per_rank))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.lc_comm_destroy(self._h)
+            self._h = None
+
+
 def _make_method(cname: str, restype, argnames):
     def method(self, *args):
         if len(args) != len(argnames) - 1:

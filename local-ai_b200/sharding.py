@@ -53,6 +53,37 @@ def merge_argmax(values: np.ndarray, indices: np.ndarray) -> np.ndarray:
     return tok.astype(np.uint32)
 
 
+PAIR_DTYPE = np.dtype([("value", np.float32), ("index", np.uint32)])   # what lc_argmax_pairs_f32_into writes
+
+
+def argmax_pairs(logits: np.ndarray, index_offset: int) -> np.ndarray:
+    """Host twin of lc_argmax_pairs_f32_into: per row (max, first index + offset) with a strict '>' scan; an all
+    -inf / NaN row reports (-inf, offset)."""
+    logits = np.asarray(logits, dtype=np.float32)
+    out = np.empty(logits.shape[0], dtype=PAIR_DTYPE)
+    for r, row in enumerate(logits):
+        bv, bi = np.float32(-np.inf), 0
+        for i, x in enumerate(row):
+            if x > bv:
+                bv, bi = x, i
+        out[r] = (bv, bi + index_offset)
+    return out
+
+
+def merge_argmax_pairs(pairs_all: np.ndarray) -> np.ndarray:
+    """Host twin of lc_merge_argmax_pairs_into: pairs_all is [shards, rows] of PAIR_DTYPE, shards in index order.
+    A later shard wins only with a strictly larger value, so equal maxima go to the lowest index; a row whose every
+    shard reports -inf keeps the first shard's index."""
+    pairs_all = np.asarray(pairs_all, dtype=PAIR_DTYPE)
+    tok = pairs_all[0]["index"].copy()
+    best = np.full(pairs_all.shape[1], -np.inf, np.float32)
+    for s in range(pairs_all.shape[0]):
+        better = pairs_all[s]["value"] > best
+        tok = np.where(better, pairs_all[s]["index"], tok)
+        best = np.where(better, pairs_all[s]["value"], best)
+    return tok.astype(np.uint32)
+
+
 def greedy_from_logit_slices(logits_all, rows: int):
     """The row-split vocabulary variant after the all-gather: `logits_all` is a torch tensor [world, lanes, rows]
     (shard r holds table rows [r * rows, (r + 1) * rows) for every lane).  Returns the greedy token per lane with the

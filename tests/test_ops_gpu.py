@@ -126,6 +126,37 @@ def test_embed_rows_and_argmax(la, orc, ctx, kernels):
     assert got[1] == 1000 and got[2] == 0 and got[3] == n - 1
 
 
+def test_argmax_pairs_and_merge(la, orc, ctx, kernels):
+    """Row-split greedy choice: per-shard (max, first index) records and their merge equal one first-maximum scan of
+    the whole row (sampler.rs:148-158), and each record equals its host twin bit for bit."""
+    rows, vocab, shards = 9, 8192, 4
+    v = la.synth.normal(31, rows * vocab).astype(np.float32).reshape(rows, vocab)
+    v[1, 100] = v[1, 7000] = 50.0          # tie across shards: the lower shard keeps it
+    v[2, 3000] = v[2, 3001] = 50.0         # tie inside a shard
+    v[3, :] = -np.inf
+    v[4, 17] = np.nan
+    v[5, vocab - 1] = 60.0
+    per = vocab // shards
+    pairs_all = Guarded(la, ctx, shards * rows * 8)
+    b = la.CommandBatch.new(ctx)
+    keep = []
+    for s in range(shards):
+        sl = dev(la, ctx, np.ascontiguousarray(v[:, s * per:(s + 1) * per]))
+        keep.append(sl)
+        dst = la.CudaBuffer.wrap(ctx, pairs_all.view.device_ptr + s * rows * 8, rows * 8)
+        kernels.argmax_pairs_f32_into(b, sl, dst, rows, per, s * per)
+    tok = Guarded(la, ctx, rows * 4)
+    kernels.merge_argmax_pairs_into(b, pairs_all.view, tok.view, rows, shards)
+    b.commit_and_wait()
+    got_pairs = pairs_all.read(np.uint8).view(la.sharding.PAIR_DTYPE).reshape(shards, rows)
+    want_pairs = np.stack([la.sharding.argmax_pairs(v[:, s * per:(s + 1) * per], s * per) for s in range(shards)])
+    assert np.array_equal(got_pairs.view(np.uint8), want_pairs.view(np.uint8))
+    got = tok.read(np.uint32)
+    assert got.tolist() == la.sharding.merge_argmax_pairs(want_pairs).tolist()
+    assert got.tolist() == [orc.argmax(v[r]) for r in range(rows)]
+    assert got[1] == 100 and got[2] == 3000 and got[3] == 0 and got[5] == vocab - 1
+
+
 # ---- fused forms: must equal the unfused sequence (same f16 rounding points) ----
 def test_qk_norm_rope_fused(la, orc, ctx, kernels):
     hd, heads, rows, theta = 256, 8, 5, 1e6

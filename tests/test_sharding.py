@@ -67,6 +67,31 @@ def test_greedy_from_logit_slices_equals_first_max_scan(la, orc):
     assert got.tolist() == [orc.argmax(logits[i]) for i in range(lanes)]
 
 
+def test_pair_twins_equal_first_max_scan(la, orc):
+    """The (max, index) records the device kernels exchange, merged shard by shard, give the single first-maximum
+    scan (sampler.rs:148-158): ties across and inside shards, an all -inf row, a row with NaNs."""
+    rng = np.random.default_rng(6)
+    lanes, vocab, world = 7, 1024, 4
+    logits = rng.standard_normal((lanes, vocab)).astype(np.float32)
+    logits[1, 100] = logits[1, 900] = 9.0
+    logits[2, 300] = logits[2, 301] = 9.0
+    logits[3, :] = -np.inf
+    logits[4, 5] = np.nan
+    logits[4, 700] = 8.0
+    rows = vocab // world
+    pairs = np.stack([la.sharding.argmax_pairs(logits[:, r * rows:(r + 1) * rows], r * rows) for r in range(world)])
+    got = la.sharding.merge_argmax_pairs(pairs)
+    assert got.tolist() == [orc.argmax(logits[i]) for i in range(lanes)]
+    assert got.tolist() == la.sharding.merge_argmax(pairs["value"], pairs["index"]).tolist()
+
+
+def test_comm_entry_points_report_instead_of_failing_to_load(la):
+    """NCCL is loaded at run time: the library itself loads without it, and lc_comm_available says which case holds."""
+    lib = la._lib.load()
+    assert lib.lc_comm_available() in (0, 11)   # LC_OK or LC_ERR_NCCL
+    assert lib.lc_comm_rank(None) == 0 and lib.lc_comm_world(None) == 0
+
+
 RANK_SCRIPT = textwrap.dedent('''
     import os, sys, numpy as np
     sys.path.insert(0, os.environ["REPO_ROOT"])
@@ -102,6 +127,12 @@ RANK_SCRIPT = textwrap.dedent('''
     dist.all_gather(pairs, pair)
     vals = np.stack([p[0].numpy() for p in pairs]); idxs = np.stack([p[1].numpy().astype(np.int64) for p in pairs])
     tok = sharding.merge_argmax(vals, idxs)
+    # the same exchange in the device kernels' record format (8 bytes per lane and shard), merged by their host twin
+    rec = sharding.argmax_pairs(logits, lo)
+    recs = [torch.zeros(lanes, 8, dtype=torch.uint8) for _ in range(world)]
+    dist.all_gather(recs, torch.from_numpy(rec.view(np.uint8).reshape(lanes, 8).copy()))
+    tok_rec = sharding.merge_argmax_pairs(np.stack([r.numpy().reshape(-1).view(sharding.PAIR_DTYPE) for r in recs]))
+    assert tok_rec.tolist() == tok.tolist()
     full = np.stack([synth.normal(100 + int(l), hidden) for l in order]).astype(np.float32) @ table.T
     assert tok.tolist() == full.argmax(axis=1).tolist(), (tok, full.argmax(axis=1))
     # the variant that all-gathers the f32 logit slices themselves (equal slices: all_gather_into_tensor)
