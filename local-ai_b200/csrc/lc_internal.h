@@ -50,7 +50,8 @@ struct lc_kernels {
     bool batchm = true;  // LOCAL_AI_BATCHM: register-resident small-M path
     bool smallm = true;  // LOCAL_AI_SMALLM
     bool mma = true;     // LOCAL_AI_MMA: tensor-core path for larger M
-    bool decode_tc = true;   // LOCAL_CUDA_DECODE_TC: lean tcgen05 kernel for TQ2_0 at 8 < M <= 64
+    bool decode_tc = true;   // LOCAL_CUDA_DECODE_TC: lean tcgen05 kernel for TQ2_0 at small_m < M <= 64
+    uint32_t small_m = 0;    // LOCAL_CUDA_SMALL_M (0..8): TQ2_0 matmuls of up to this many rows keep the CUDA-core kernel
     bool decode_mma = true;  // LOCAL_CUDA_DECODE_MMA: register-direct mma.sync path for 8 < M <= 64 (0: tcgen05 there too)
     int kv_norm_mode = 0;  // LOCAL_CUDA_TQ_NORM: 0 sequential (Rust codec order), 1 tree (Metal order)
     // Library-owned scratch for split-K partials (grown outside graph capture).

@@ -2,11 +2,14 @@
 // stand-in for Kernels::matmul_nt_q4_0_into / matmul_nt_tq2_0_into
 // (local-metal/src/kernels.rs:6459-6563).  The reference picks between four
 // Metal kernels by m (batchm <= 4, smallm <= 8, simdgroup MMA, scalar tile);
-// here: the register-resident CUDA-core path that streams the weights once for
-// up to 16 rows (qmatvec.cu, m <= 8); for decode batches (8 < m <= 64) the lean
-// tcgen05 kernel (qmatmul_tcd.cu: TQ2_0, f16 out) or the register-direct
-// mma.sync kernel (qmatmul_mma.cu: Q4_0, f32 out, shapes the former declines);
-// and the large-tile tcgen05 kernel for larger m (qmatmul_tc.cu).
+// here: for TQ2_0 with f16 output and m <= 64 the lean tcgen05 kernel
+// (qmatmul_tcd.cu; it is also the faster launch at m <= 8, LOCAL_CUDA_SMALL_M=8
+// keeps those on the CUDA-core kernel); otherwise the register-resident CUDA-core
+// path that streams the weights once for up to 16 rows (qmatvec.cu, m <= 8), the
+// register-direct mma.sync kernel for decode batches 8 < m <= 64 (qmatmul_mma.cu:
+// Q4_0, f32 out, shapes the tcgen05 kernel declines), and the large-tile tcgen05
+// kernel for larger m (qmatmul_tc.cu).  The matvec entry points (lc_matvec_*) stay
+// on the CUDA-core kernels.
 // LOCAL_AI_MMA=0 forces the CUDA-core path for every m, as it forces the non-MMA
 // kernels in the reference; LOCAL_CUDA_DECODE_TC=0 / LOCAL_CUDA_DECODE_MMA=0
 // switch the two decode kernels off (with both off, 8 < m <= 64 runs on
@@ -37,15 +40,15 @@ static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch
     int st = lc_check_qargs(fmt, name, k, b, weight, input, output, m, kk, n, f32out ? 4 : 2);
     if (st != LC_OK) return st;
     if (n == 0) return LC_OK;
+    const lc_buf *ws[1] = {weight};
+    lc_buf *os[1] = {output};
+    const uint32_t ns[1] = {n};
+    if (k->mma && k->decode_tc && fmt == 1 && !f32out && m > k->small_m && m <= 64) {
+        st = lc_qgemm_tcd_launch(k, b, input, 1, ws, os, ns, m, kk, false);
+        if (st >= 0) return st;
+    }
     if (k->mma && m > 8) {
         if (m <= 64) {
-            const lc_buf *ws[1] = {weight};
-            lc_buf *os[1] = {output};
-            const uint32_t ns[1] = {n};
-            if (k->decode_tc && fmt == 1 && !f32out) {
-                st = lc_qgemm_tcd_launch(k, b, input, 1, ws, os, ns, m, kk, false);
-                if (st >= 0) return st;
-            }
             if (k->decode_mma) {
                 st = lc_qgemm_mma_grouped(fmt, f32out, k, b, input, 1, ws, os, ns, m, kk);
                 if (st >= 0) return st;
@@ -69,10 +72,13 @@ int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, 
         int st = lc_check_qargs(1, "matmul_nt_tq2_0", k, b, weights[g], input, outputs[g], m, kk, ns[g], 2);
         if (st != LC_OK) return st;
     }
+    if (k->mma && k->decode_tc && m > k->small_m && m <= 64) {
+        const int st = lc_qgemm_tcd_launch(k, b, input, ng, weights, outputs, ns, m, kk, false);
+        if (st >= 0) return st;
+    }
     if (k->mma && m > 8) {
         int st = -1;
-        if (k->decode_tc && m <= 64) st = lc_qgemm_tcd_launch(k, b, input, ng, weights, outputs, ns, m, kk, false);
-        if (st < 0 && k->decode_mma && m <= 64) st = lc_qgemm_mma_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
+        if (k->decode_mma && m <= 64) st = lc_qgemm_mma_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
         if (st < 0) st = lc_qgemm_tcgen05_grouped(1, false, k, b, input, ng, weights, outputs, ns, m, kk);
         if (st >= 0) return st;
     }
@@ -101,7 +107,7 @@ int lc_matmul_nt_tq2_0_geglu_into(lc_kernels *k, lc_batch *b, const lc_buf *inpu
     if (st != LC_OK) return st;
     if (n == 0 || m == 0) return LC_OK;
     static const bool fused_ok = []() { const char *e = getenv("LOCAL_CUDA_GEGLU_FUSED"); return !(e && e[0] == '0'); }();
-    if (fused_ok && k->mma && m > 8 && m <= 64) {
+    if (fused_ok && k->mma && m > k->small_m && m <= 64) {
         if (k->decode_tc) {
             const lc_buf *ws[2] = {w_gate, w_up};
             lc_buf *os[2] = {output, output};
@@ -109,7 +115,7 @@ int lc_matmul_nt_tq2_0_geglu_into(lc_kernels *k, lc_batch *b, const lc_buf *inpu
             st = lc_qgemm_tcd_launch(k, b, input, 2, ws, os, ns, m, kk, true);
             if (st >= 0) return st;
         }
-        if (k->decode_mma) {
+        if (k->decode_mma && m > 8) {
             st = lc_qgemm_mma_geglu(k, b, input, w_gate, w_up, output, m, kk, n);
             if (st >= 0) return st;
         }

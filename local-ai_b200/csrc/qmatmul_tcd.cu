@@ -541,7 +541,7 @@ int launch_tcd(lc_batch *b, const TcdParams &p, const CUtensorMap &x_map, int ti
 // launch, a positive status on error, or -1 when the shape is outside what this kernel covers.
 int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
                         lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk, bool geglu) {
-    if (m <= 8 || m > NB || ng < 1 || ng > MAX_GROUPS || kk % 256 != 0 || !lc_aligned(input->dptr, 16)) return -1;
+    if (m < 1 || m > NB || ng < 1 || ng > MAX_GROUPS || kk % 256 != 0 || !lc_aligned(input->dptr, 16)) return -1;
     if (geglu && (ng != 2 || ns[0] != ns[1])) return -1;
     TcdParams p;
     p.m = (int)m;
@@ -587,7 +587,8 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     const size_t fixed = (size_t)rows * p.raw_rs + (1 + 2 * MAX_STEPS + NBAR) * 8 + 16 + 1024;   // + 1024: tile alignment slack
     const size_t budget = k->ctx->smem_optin > 2048 ? k->ctx->smem_optin - 1024 : 0;
     const size_t a_slot = (size_t)A_SLOT;
-    int sb = total < 3 ? total : 3;
+    static const int sb_cap = []() { const char *e = getenv("LOCAL_CUDA_TCD_SB"); const int v = e ? atoi(e) : 0; return v >= 2 && v <= NBAR ? v : 3; }();
+    int sb = total < sb_cap ? total : sb_cap;
     while (sb > 2 && fixed + (size_t)sb * B_SLOT + 2 * a_slot > budget) sb--;
     if (fixed + (size_t)sb * B_SLOT + (total < 2 ? total : 2) * a_slot > budget) return -1;
     int sa = (int)((budget - fixed - (size_t)sb * B_SLOT) / a_slot);
