@@ -106,7 +106,6 @@ __device__ __forceinline__ int rq_index(int h, int d) {
 
 __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) {
     lc_pdl_trigger();
-    lc_pdl_wait();
     extern __shared__ __align__(16) uint8_t smem[];
     uint2 *lut = reinterpret_cast<uint2 *>(smem);                       // [256 bytes][16 copies] x 4 f16
     float *rq_s = reinterpret_cast<float *>(smem + LUT_BYTES);          // [16 s][32 lanes][4] rotated, scaled query
@@ -124,8 +123,67 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     const int gvalid = min((int)G, (int)(p.group - gchunk * G));
     const uint32_t qh0 = kv_head * p.group + gchunk * G;
 
-    // Every global load of the prologue leaves first, so their latencies overlap.
+    // ---- before the dependency wait: everything that depends on the codec's levels only (a constant operand): the
+    //      gamma search and the byte table.  A CTA that becomes resident while its predecessor drains does this
+    //      part for free. ----
     const float lv0 = p.levels[0], lv1 = p.levels[1], lv2 = p.levels[2], lv3 = p.levels[3];
+    // ---- prologue 1: gamma such that every level / gamma is (almost) exactly an f16 ----
+    const float ref = fmaxf(fmaxf(fabsf(lv0), fabsf(lv1)), fmaxf(fabsf(lv2), fabsf(lv3)));
+    {
+        const float ia0 = lv0 != 0.f ? 1.0f / fabsf(lv0) : 0.f, ia1 = lv1 != 0.f ? 1.0f / fabsf(lv1) : 0.f;
+        const float ia2 = lv2 != 0.f ? 1.0f / fabsf(lv2) : 0.f, ia3 = lv3 != 0.f ? 1.0f / fabsf(lv3) : 0.f;
+        float best = INFINITY;
+        int besti = 0;
+#pragma unroll
+        for (int it = 0; it < 1024 / NT; it++) {
+            const int j = threadIdx.x + it * NT;
+            const float gm = ref > 0.f ? ref / (1.0f + (float)j * (1.0f / 1024.0f)) : 1.0f;  // largest level -> [1, 2)
+            const float inv = __frcp_rn(gm);
+            float e = fabsf(__half2float(__float2half_rn(lv0 * inv)) * gm - lv0) * ia0;
+            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv1 * inv)) * gm - lv1) * ia1);
+            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv2 * inv)) * gm - lv2) * ia2);
+            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv3 * inv)) * gm - lv3) * ia3);
+            if (e < best) { best = e; besti = j; }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {   // arg-min inside the warp, lowest index on ties
+            const float oe = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, off);
+            if (oe < best || (oe == best && oi < besti)) { best = oe; besti = oi; }
+        }
+        if (lane == 0) { cand_err[warp] = best; cand_idx[warp] = besti; }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b2 = cand_err[0];
+        int bi = cand_idx[0];
+        for (int i = 1; i < NW; i++)
+            if (cand_err[i] < b2 || (cand_err[i] == b2 && cand_idx[i] < bi)) { b2 = cand_err[i]; bi = cand_idx[i]; }
+        gamma_s = ref > 0.f ? ref / (1.0f + (float)bi * (1.0f / 1024.0f)) : 1.0f;
+    }
+    __syncthreads();
+    const float gamma = gamma_s;
+    // ---- prologue 3: byte -> four f16 levels table; one copy first, then one copy per lane ----
+    {
+        const int byte = threadIdx.x;   // NT == 256
+        const float inv_levels[4] = {lv0 / gamma, lv1 / gamma, lv2 / gamma, lv3 / gamma};
+        float e4[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int c = (byte >> (2 * q)) & 3;
+            e4[q] = c == 0 ? inv_levels[0] : (c == 1 ? inv_levels[1] : (c == 2 ? inv_levels[2] : inv_levels[3]));
+        }
+        uint2 v;
+        v.x = pack_h2(e4[0], e4[1]);
+        v.y = pack_h2(e4[2], e4[3]);
+        ent_s[byte] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int e = threadIdx.x; e < 256 * LUT_COPIES; e += NT) lut[e] = ent_s[e / LUT_COPIES];
+
+    lc_pdl_wait();
+    // ---- after the wait: the query, the positions and the first tiles of codes; their loads leave first ----
     const size_t q_row = ((size_t)lane_idx * p.n_q + qh0 + warp) * HD + 8 * lane;   // warp w owns head w
     uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
     float4 q_s0 = make_float4(0.f, 0.f, 0.f, 0.f), q_s1 = q_s0;
@@ -197,32 +255,6 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         t_issue += NW * KT;
     }
 
-    // ---- prologue 1: gamma such that every level / gamma is (almost) exactly an f16 ----
-    const float ref = fmaxf(fmaxf(fabsf(lv0), fabsf(lv1)), fmaxf(fabsf(lv2), fabsf(lv3)));
-    {
-        const float ia0 = lv0 != 0.f ? 1.0f / fabsf(lv0) : 0.f, ia1 = lv1 != 0.f ? 1.0f / fabsf(lv1) : 0.f;
-        const float ia2 = lv2 != 0.f ? 1.0f / fabsf(lv2) : 0.f, ia3 = lv3 != 0.f ? 1.0f / fabsf(lv3) : 0.f;
-        float best = INFINITY;
-        int besti = 0;
-#pragma unroll
-        for (int it = 0; it < 1024 / NT; it++) {
-            const int j = threadIdx.x + it * NT;
-            const float gm = ref > 0.f ? ref / (1.0f + (float)j * (1.0f / 1024.0f)) : 1.0f;  // largest level -> [1, 2)
-            const float inv = __frcp_rn(gm);
-            float e = fabsf(__half2float(__float2half_rn(lv0 * inv)) * gm - lv0) * ia0;
-            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv1 * inv)) * gm - lv1) * ia1);
-            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv2 * inv)) * gm - lv2) * ia2);
-            e = fmaxf(e, fabsf(__half2float(__float2half_rn(lv3 * inv)) * gm - lv3) * ia3);
-            if (e < best) { best = e; besti = j; }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {   // arg-min inside the warp, lowest index on ties
-            const float oe = __shfl_xor_sync(0xffffffffu, best, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, besti, off);
-            if (oe < best || (oe == best && oi < besti)) { best = oe; besti = oi; }
-        }
-        if (lane == 0) { cand_err[warp] = best; cand_idx[warp] = besti; }
-    }
     // ---- prologue 2 (independent of gamma): rotated, scaled query; warp w owns head w ----
     {
         const int h = warp;   // NW == G
@@ -273,14 +305,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         *reinterpret_cast<float4 *>(rq_s + rq_index(h, 8 * lane)) = make_float4(x[0], x[1], x[2], x[3]);
         *reinterpret_cast<float4 *>(rq_s + rq_index(h, 8 * lane + 4)) = make_float4(x[4], x[5], x[6], x[7]);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float b2 = cand_err[0];
-        int bi = cand_idx[0];
-        for (int i = 1; i < NW; i++)
-            if (cand_err[i] < b2 || (cand_err[i] == b2 && cand_idx[i] < bi)) { b2 = cand_err[i]; bi = cand_idx[i]; }
-        gamma_s = ref > 0.f ? ref / (1.0f + (float)bi * (1.0f / 1024.0f)) : 1.0f;
-    }
+    __syncthreads();   // the rotated query is in place; so is every copy of the table
     // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15
     // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
     // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
@@ -300,27 +325,6 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         bql[s][0] = pack_h2(lo[0], lo[1]);
         bql[s][1] = pack_h2(lo[2], lo[3]);
     }
-    __syncthreads();
-    const float gamma = gamma_s;
-    // ---- prologue 3: byte -> four f16 levels table; one copy first, then one copy per lane ----
-    {
-        const int byte = threadIdx.x;   // NT == 256
-        const float inv_levels[4] = {lv0 / gamma, lv1 / gamma, lv2 / gamma, lv3 / gamma};
-        float e4[4];
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int c = (byte >> (2 * q)) & 3;
-            e4[q] = c == 0 ? inv_levels[0] : (c == 1 ? inv_levels[1] : (c == 2 ? inv_levels[2] : inv_levels[3]));
-        }
-        uint2 v;
-        v.x = pack_h2(e4[0], e4[1]);
-        v.y = pack_h2(e4[2], e4[3]);
-        ent_s[byte] = v;
-    }
-    __syncthreads();
-#pragma unroll 8
-    for (int e = threadIdx.x; e < 256 * LUT_COPIES; e += NT) lut[e] = ent_s[e / LUT_COPIES];
-    __syncthreads();
     const uint2 *lut_lane = lut + (lane & (LUT_COPIES - 1));
 
     // ---- main loop: each warp takes every 8th 16-key tile of this split ----
