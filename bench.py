@@ -82,8 +82,12 @@ class QuantMatvec:
     (the reference's own microbenchmark cycles 35 distinct weight sets so each read is cold,
     local-metal/src/kernels.rs:8898-8902).  One step = one pass over all copies."""
 
-    def __init__(self, la, ctx, kernels, fmt: str, rows: int, cols: int, m: int = 1, min_copies: int = 8):
+    def __init__(self, la, ctx, kernels, fmt: str, rows: int, cols: int, m: int = 1, min_copies: int = 8,
+                 grouped: bool = False):
+        """grouped: the copies go through lc_matvec_*_group_into, up to 96 matrices per launch (the decode-time
+        access pattern: many same-shape matrices against one vector), instead of one launch per matrix."""
         self.la, self.ctx, self.k, self.fmt, self.rows, self.cols, self.m = la, ctx, kernels, fmt, rows, cols, m
+        self.grouped = grouped and m == 1
         l2 = ctx.caps()["l2_bytes"]
         gen = la.synth.q4_0_weights if fmt == "q4_0" else la.synth.tq2_0_weights
         w0 = gen(rows, cols, seed=1)
@@ -100,8 +104,10 @@ class QuantMatvec:
         self.alg_bytes_per_launch = self.wbytes + m * cols * 2 + m * rows * 2
         self.units_per_step = self.copies
         self.name = f"{fmt} fused dequant mat{'vec' if m == 1 else 'mul'} {rows}x{cols} batch {m}"
+        if self.grouped:
+            self.name += f", {min(96, self.copies)} matrices per launch"
         self.graph = None
-        self.launches_per_step = self.copies
+        self.launches_per_step = self.copies if not self.grouped else -(-self.copies // 96)
 
     def _enqueue(self, b, c):
         if self.m == 1:
@@ -111,13 +117,22 @@ class QuantMatvec:
             fn = self.k.matmul_nt_q4_0_into if self.fmt == "q4_0" else self.k.matmul_nt_tq2_0_into
             fn(b, self.x, self.weights[c], self.out[c], self.m, self.cols, self.rows)
 
+    def _enqueue_all(self, b):
+        if not self.grouped:
+            for c in range(self.copies):
+                self._enqueue(b, c)
+            return
+        fn = self.k.matvec_q4_0_group_into if self.fmt == "q4_0" else self.k.matvec_tq2_0_group_into
+        for c0 in range(0, self.copies, 96):
+            c1 = min(self.copies, c0 + 96)
+            fn(b, self.weights[c0:c1], c1 - c0, self.x, self.out[c0:c1], self.rows, self.cols)
+
     def prepare(self):
         b = self.la.CommandBatch.new(self.ctx)
-        self._enqueue(b, 0)
+        self._enqueue_all(b)
         b.commit_and_wait()
         b = self.la.CommandBatch.capture(self.ctx)
-        for c in range(self.copies):
-            self._enqueue(b, c)
+        self._enqueue_all(b)
         self.graph = b.end_capture()
 
     def step(self):
@@ -151,7 +166,7 @@ class QuantMatvec:
         return f"inputs larger than L2 ({self.copies} distinct weight copies, {self.copies * self.wbytes / 1e6:.0f} MB per pass)"
 
     def roofline(self, ms_per_step: float, peak: float, peak_kind: str, timed):
-        launch_ms = ms_per_step / self.launches_per_step
+        launch_ms = ms_per_step / self.copies    # per matrix (a grouped launch covers several)
         achieved = self.alg_bytes_per_launch / (launch_ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_kind": peak_kind, "kernel": self.kernel_name(),
@@ -159,6 +174,8 @@ class QuantMatvec:
                 "frac_of_nominal_8tbs": achieved / 8000.0}
 
     def kernel_name(self) -> str:
+        if self.grouped:
+            return "qgemv_mma_stream_kernel (grouped)"
         if self.m == 1:
             return "qgemv_mma_stream_kernel" if self.rows >= 18944 else "qgemv_kernel"
         if self.fmt == "tq2_0" and 8 < self.m <= 64:
@@ -701,6 +718,8 @@ class RaggedDecode(DecodeStep):
 
 WORKLOADS = {
     "matvec_tq2_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 1),
+    "matvec_tq2_0_grouped": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 1, grouped=True),
+    "matvec_q4_0_grouped": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 6144, 1536, 1, grouped=True),
     "matvec_q4_0": lambda la, ctx, k: QuantMatvec(la, ctx, k, "q4_0", 6144, 1536, 1),
     "matmul_tq2_0_m16": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 16),
     "matmul_tq2_0_m64": lambda la, ctx, k: QuantMatvec(la, ctx, k, "tq2_0", 8192, 1536, 64),
@@ -771,6 +790,8 @@ def run_extras(la, ctx, kernels, headline, timed_local, orc, peak: float, peak_k
 
     measure("decode_b1", lambda: DecodeStep(la, ctx, kernels, 1, 8192, share=headline))
     measure("matvec_q4_0", lambda: QuantMatvec(la, ctx, kernels, "q4_0", 6144, 1536, 1))
+    measure("matvec_q4_0_grouped", lambda: QuantMatvec(la, ctx, kernels, "q4_0", 6144, 1536, 1, grouped=True))
+    measure("matvec_tq2_0_m1_grouped", lambda: QuantMatvec(la, ctx, kernels, "tq2_0", 8192, 1536, 1, grouped=True))
     for m in (1, 16, 64):
         measure(f"matvec_tq2_0_m{m}", lambda m=m: QuantMatvec(la, ctx, kernels, "tq2_0", 8192, 1536, m))
     measure("matvec_vocab_q4_0", lambda: QuantMatvec(la, ctx, kernels, "q4_0", 262144, 1536, 1, min_copies=3))
@@ -882,6 +903,7 @@ def run_reference(args, rank: int, world: int) -> None:
         wl_name = f"fused tq2 decode attention, {lanes_full} lane(s) x {keys} keys, 8 q heads / 1 kv head of 256"
     else:
         shapes = {"matvec_tq2_0": ("tq2_0", 8192, 1536, 1), "matvec_q4_0": ("q4_0", 6144, 1536, 1),
+                  "matvec_tq2_0_grouped": ("tq2_0", 8192, 1536, 1), "matvec_q4_0_grouped": ("q4_0", 6144, 1536, 1),
                   "matmul_tq2_0_m16": ("tq2_0", 8192, 1536, 16), "matmul_tq2_0_m64": ("tq2_0", 8192, 1536, 64),
                   "matmul_tq2_0_m256": ("tq2_0", 8192, 1536, 256), "matvec_vocab_q4_0": ("q4_0", 262144, 1536, 1)}
         fmt, rows, cols, m = shapes[name]

@@ -172,6 +172,15 @@ LC_API int lc_matvec_tq2_0_f32out(lc_kernels *k, lc_ctx *ctx, const lc_buf *matr
 LC_API int lc_matvec_tq2_0_f32out_into(lc_kernels *k, lc_batch *b, const lc_buf *matrix,
                                        const lc_buf *vector, lc_buf *output, uint32_t rows,
                                        uint32_t cols);                              /* kernels.rs:6011 */
+/* Grouped form: `count` (1..=96) matrices of one shape [rows, cols] against the same vector, output i = matrix i x
+ * vector, f16 out.  One launch when the streaming kernel applies (it walks the matrices as one run of 64-row groups,
+ * so a set of small projections streams at the rate of one large matrix), else one launch per matrix.  The decode-time
+ * access pattern the reference's own microbenchmark models with 35 distinct weight sets
+ * (local-metal/src/kernels.rs:8886-9136). */
+LC_API int lc_matvec_q4_0_group_into(lc_kernels *k, lc_batch *b, const lc_buf *const *matrices, uint32_t count,
+                                     const lc_buf *vector, lc_buf *const *outputs, uint32_t rows, uint32_t cols);
+LC_API int lc_matvec_tq2_0_group_into(lc_kernels *k, lc_batch *b, const lc_buf *const *matrices, uint32_t count,
+                                      const lc_buf *vector, lc_buf *const *outputs, uint32_t rows, uint32_t cols);
 /* SoA TQ2_0: qs = rows*blocks*64 bytes, scales = rows*blocks f16. */
 LC_API int lc_matvec_tq2_0_soa_into(lc_kernels *k, lc_batch *b, const lc_buf *qs,
                                     const lc_buf *scales, const lc_buf *vector, lc_buf *output,

@@ -278,6 +278,8 @@ static int check_qargs(const char *name, lc_kernels *k, lc_batch *b, const lc_bu
 // returns -1 for everything else.
 int lc_qgemv_mma_stream(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
                         lc_buf *output, uint32_t m, uint32_t kk, uint32_t n);
+int lc_qgemv_mma_stream_group(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int count,
+                              const lc_buf *const *weights, lc_buf *const *outputs, uint32_t m, uint32_t kk, uint32_t n);
 
 int lc_qgemm_cuda_core(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input,
                        const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
@@ -314,6 +316,31 @@ extern "C" {
             return NAME##_into(k, b, matrix, vector, output, rows, cols);                                  \
         });                                                                                                \
     }
+
+// Several matrices of one shape against the same vector, one output each, in one launch when the streaming
+// tensor-core kernel applies (it treats them as one long run of 64-row groups), else one launch per matrix.
+#define LC_MATVEC_GROUP(NAME, FMT)                                                                                \
+    int NAME(lc_kernels *k, lc_batch *b, const lc_buf *const *matrices, uint32_t count, const lc_buf *vector,        \
+             lc_buf *const *outputs, uint32_t rows, uint32_t cols) {                                                 \
+        if (!matrices || !outputs) return lc_fail(LC_ERR_INVALID_ARGUMENT, #NAME ": NULL argument");                 \
+        LC_REQUIRE(count >= 1 && count <= 96, #NAME ": count %u not in 1..=96", count);                             \
+        for (uint32_t i = 0; i < count; i++) {                                                                       \
+            int st = check_qargs<FMT>(#NAME, k, b, matrices[i], vector, outputs[i], 1, cols, rows, 2);              \
+            if (st != LC_OK) return st;                                                                              \
+        }                                                                                                            \
+        if (rows == 0) return LC_OK;                                                                                 \
+        if (k->mma && k->decode_mma) {                                                                               \
+            const int st = lc_qgemv_mma_stream_group(FMT, false, k, b, vector, (int)count, matrices, outputs, 1, cols, rows); \
+            if (st >= 0) return st;                                                                                  \
+        }                                                                                                            \
+        for (uint32_t i = 0; i < count; i++) {                                                                       \
+            int st = lc_qgemm_cuda_core(FMT, false, k, b, vector, matrices[i], outputs[i], 1, cols, rows);          \
+            if (st != LC_OK) return st;                                                                              \
+        }                                                                                                            \
+        return LC_OK;                                                                                                \
+    }
+LC_MATVEC_GROUP(lc_matvec_q4_0_group_into, FMT_Q4_0)
+LC_MATVEC_GROUP(lc_matvec_tq2_0_group_into, FMT_TQ2_0)
 
 LC_MATVEC_PAIR(lc_matvec_q4_0, FMT_Q4_0, false)
 LC_MATVEC_PAIR(lc_matvec_q4_0_f32out, FMT_Q4_0, true)

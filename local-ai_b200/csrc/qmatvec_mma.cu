@@ -26,12 +26,15 @@ constexpr int GROUP_ROWS = 64;       // rows per ring slot: 4 row groups of 16
 constexpr int SLOTS = 3;
 constexpr int UNIT_K = 128;          // K is split over the four warp quarters in units of 128 k
 
+constexpr int MAX_MATRICES = 96;     // matrices of one shape streamed by one launch (lc_matvec_*_group_into)
+
 struct StreamParams {
-    const uint8_t *w;
-    void *out;
+    const uint8_t *w[MAX_MATRICES];   // n_mat matrices of n rows each, all read against the same activations
+    void *out[MAX_MATRICES];
     const __half *x;
     int n, m, K, nb;        // nb = blocks per row
-    int groups;             // ceil(n / 64)
+    int gpm;                // 64-row groups per matrix: ceil(n / 64)
+    int groups;             // n_mat * gpm
     int xs;                 // bytes per activation row in shared memory
     int slot_bytes;         // bytes reserved per ring slot
 };
@@ -65,8 +68,9 @@ template <> struct Fmt<FMT_TQ2_0> { static constexpr int bytes = 66; };
 
 // UPQ > 0: the warp's K quarter is UPQ units long and its activation fragments (8 k-steps x 2 registers per unit)
 // stay in registers for the whole launch; UPQ = 0: any length, fragments re-read from shared memory with ldmatrix.
-template <int FMT, typename OutT, int UPQ>
-__global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamParams p) {
+// MULTI: several matrices (group index -> matrix and group of it); otherwise the one matrix p.w[0].
+template <int FMT, typename OutT, int UPQ, bool MULTI>
+__global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const __grid_constant__ StreamParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int BB = Fmt<FMT>::bytes;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -78,9 +82,11 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
     uint8_t *ring = smem + 8 * p.xs + 2 * NW * 32 * 16;               // [SLOTS][slot_bytes]
     const int my_groups = (p.groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
-    // group `it` of this CTA: rows 64 (blockIdx.x + it gridDim.x) ..; one contiguous byte range
+    // group `it` of this CTA: group (blockIdx.x + it gridDim.x) of the launch = rows 64 gi .. of matrix mi; one
+    // contiguous byte range
     auto load_group = [&](int it) {
-        const int grp = (int)blockIdx.x + it * (int)gridDim.x;
+        const int gl = (int)blockIdx.x + it * (int)gridDim.x, mi = MULTI ? gl / p.gpm : 0, grp = gl - mi * p.gpm;
+        const uint8_t *wm = p.w[mi];
         const size_t start = (size_t)grp * GROUP_ROWS * rb;
         const size_t len = (size_t)min(GROUP_ROWS, p.n - grp * GROUP_ROWS) * rb;
         const size_t a0 = start & ~(size_t)15;
@@ -89,9 +95,9 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
         for (int i = tid; i < n16; i += NT) {
             const size_t ga = a0 + ((size_t)i << 4);
             if (ga + 16 <= w_bytes) {
-                cp_async16(smem_u32(slot + ((size_t)i << 4)), p.w + ga);
+                cp_async16(smem_u32(slot + ((size_t)i << 4)), wm + ga);
             } else {
-                for (int b = 0; b < 16; b++) slot[((size_t)i << 4) + b] = (ga + b < w_bytes) ? p.w[ga + b] : 0;
+                for (int b = 0; b < 16; b++) slot[((size_t)i << 4) + b] = (ga + b < w_bytes) ? wm[ga + b] : 0;
             }
         }
     };
@@ -113,7 +119,6 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
     const int u0 = kq * upq, u1 = min(nu, u0 + upq);
     // ldmatrix.x2 lane address: lanes 0-7 rows of the first k half, lanes 8-15 the second
     const uint32_t xl = smem_u32(x_s) + (uint32_t)((lane & 7) * p.xs + ((lane >> 3) & 1) * 16);
-    OutT *out = reinterpret_cast<OutT *>(p.out);
     uint32_t breg[UPQ > 0 ? UPQ * 8 : 1][2];
     if (UPQ > 0) {
         cp_async_wait<1>();
@@ -128,7 +133,8 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
     }
 
     auto reduce_store = [&](int it) {      // warps kq == 0: add the four quarters of group `it` and store
-        const int grp = (int)blockIdx.x + it * (int)gridDim.x;
+        const int gl = (int)blockIdx.x + it * (int)gridDim.x, mi = MULTI ? gl / p.gpm : 0, grp = gl - mi * p.gpm;
+        OutT *out = reinterpret_cast<OutT *>(p.out[mi]);
         const float4 *rp = red + (size_t)(it & 1) * NW * 32;
         float4 v = rp[(0 * 4 + rg) * 32 + lane];
 #pragma unroll
@@ -151,7 +157,7 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
         cp_async_commit();
         if (it > 0 && kq == 0) reduce_store(it - 1);
 
-        const int grp = (int)blockIdx.x + it * (int)gridDim.x;
+        const int gl = (int)blockIdx.x + it * (int)gridDim.x, grp = MULTI ? gl % p.gpm : gl;
         const size_t start = (size_t)grp * GROUP_ROWS * rb;
         const uint8_t *slot = ring + (size_t)(it % SLOTS) * p.slot_bytes + (start & 15);
         const uint8_t *rbase[2];
@@ -256,15 +262,20 @@ __global__ void __launch_bounds__(NT, 1) qgemv_mma_stream_kernel(const StreamPar
     if (my_groups > 0 && kq == 0) reduce_store(my_groups - 1);
 }
 
-template <int FMT, typename OutT, int UPQ>
-int launch_stream_u(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
-    auto kern = qgemv_mma_stream_kernel<FMT, OutT, UPQ>;
+template <int FMT, typename OutT, int UPQ, bool MULTI>
+int launch_stream_um(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
+    auto kern = qgemv_mma_stream_kernel<FMT, OutT, UPQ, MULTI>;
     static lc_smem_optin optin;
     LC_CUDA_TRY(lc_ensure_smem(kern, optin, b->ctx, smem));
     const int grid = p.groups < k->ctx->sm_count ? p.groups : k->ctx->sm_count;
     LC_LAUNCH_CHECKED(lc_launch(kern, dim3(grid), dim3(NT), smem, b, p));
     b->dispatch_count++;
     return LC_OK;
+}
+template <int FMT, typename OutT, int UPQ>
+int launch_stream_u(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem) {
+    return p.groups > p.gpm ? launch_stream_um<FMT, OutT, UPQ, true>(k, b, p, smem)
+                            : launch_stream_um<FMT, OutT, UPQ, false>(k, b, p, smem);
 }
 
 template <int FMT, typename OutT>
@@ -280,21 +291,27 @@ int launch_stream(lc_kernels *k, lc_batch *b, const StreamParams &p, size_t smem
 
 }  // namespace
 
-// m <= 8.  Returns LC_OK after a launch, a positive status on error, or -1 when the shape is outside what this
-// kernel covers or too small for it to pay (the caller then uses the CUDA-core kernel).
-int lc_qgemv_mma_stream(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
-                        lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+// m <= 8; `count` matrices of one shape [n, kk] against the same activations, each with its own output.  Returns
+// LC_OK after a launch, a positive status on error, or -1 when the shape is outside what this kernel covers or too
+// small for it to pay (the caller then uses the CUDA-core kernel).
+int lc_qgemv_mma_stream_group(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, int count,
+                              const lc_buf *const *weights, lc_buf *const *outputs, uint32_t m, uint32_t kk, uint32_t n) {
     const int be = fmt == FMT_Q4_0 ? 32 : 256, bb = fmt == FMT_Q4_0 ? 18 : 66;
-    if (m > 8 || kk % UNIT_K != 0 || kk % be != 0 || !lc_aligned(input->dptr, 16) || !lc_aligned(weight->dptr, 16)) return -1;
+    if (count < 1 || count > MAX_MATRICES || m > 8 || kk % UNIT_K != 0 || kk % be != 0 || !lc_aligned(input->dptr, 16)) return -1;
     StreamParams p;
-    p.w = (const uint8_t *)weight->dptr;
-    p.out = output->dptr;
+    for (int i = 0; i < MAX_MATRICES; i++) {
+        const int j = i < count ? i : count - 1;
+        if (!lc_aligned(weights[j]->dptr, 16)) return -1;
+        p.w[i] = (const uint8_t *)weights[j]->dptr;
+        p.out[i] = outputs[j]->dptr;
+    }
     p.x = (const __half *)input->dptr;
     p.n = (int)n;
     p.m = (int)m;
     p.K = (int)kk;
     p.nb = (int)(kk / be);
-    p.groups = (int)((n + GROUP_ROWS - 1) / GROUP_ROWS);
+    p.gpm = (int)((n + GROUP_ROWS - 1) / GROUP_ROWS);
+    p.groups = p.gpm * count;
     p.xs = (int)kk * 2 + 16;
     const size_t rb = (size_t)p.nb * bb;
     p.slot_bytes = (int)(((size_t)GROUP_ROWS * rb + 15 + 15) / 16 * 16 + 16);
@@ -305,4 +322,11 @@ int lc_qgemv_mma_stream(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const 
     if (fmt == FMT_Q4_0)
         return f32out ? launch_stream<FMT_Q4_0, float>(k, b, p, smem) : launch_stream<FMT_Q4_0, __half>(k, b, p, smem);
     return f32out ? launch_stream<FMT_TQ2_0, float>(k, b, p, smem) : launch_stream<FMT_TQ2_0, __half>(k, b, p, smem);
+}
+
+int lc_qgemv_mma_stream(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight,
+                        lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
+    const lc_buf *ws[1] = {weight};
+    lc_buf *os[1] = {output};
+    return lc_qgemv_mma_stream_group(fmt, f32out, k, b, input, 1, ws, os, m, kk, n);
 }

@@ -288,7 +288,12 @@ def _make_method(cname: str, restype, argnames):
     def method(self, *args):
         if len(args) != len(argnames) - 1:
             raise TypeError(f"{cname[3:]}() takes {len(argnames) - 1} arguments ({', '.join(argnames[1:])}), got {len(args)}")
-        conv = [a._h if hasattr(a, "_h") else a for a in args]
+        conv = []
+        for a in args:
+            if isinstance(a, (list, tuple)):   # an array of handles (const lc_buf *const *)
+                conv.append((C.c_void_p * len(a))(*[x._h for x in a]))
+            else:
+                conv.append(a._h if hasattr(a, "_h") else a)
         r = getattr(self._lib, cname)(self._h, *conv)
         if restype is C.c_int:
             _check(r)

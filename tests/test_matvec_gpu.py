@@ -354,3 +354,32 @@ def test_tq2_0_streaming_small_batch(la, orc, ctx, kernels, m, k, n):
     if m == 1:
         y = run_matvec(la, ctx, kernels, "matvec_tq2_0_f32out", raw, a[0], n, k, True, True)
         rel_close(y, want[0], 2e-4, "matvec_tq2_0_f32out, streaming")
+
+
+@pytest.mark.parametrize("fmt,rows,cols,count", [("tq2_0", 8192, 1536, 6), ("q4_0", 6144, 1536, 5), ("tq2_0", 200, 512, 3),
+                                                 ("q4_0", 4100, 256, 7)])
+def test_matvec_group_equals_single_launches(la, orc, ctx, kernels, fmt, rows, cols, count):
+    """Several matrices of one shape against one vector in one launch (the streaming kernel walks them as one run of
+    64-row groups; small sets fall back to one launch each): every output equals the single-matrix entry point's bit
+    for bit and meets the oracle."""
+    gen = la.synth.q4_0_weights if fmt == "q4_0" else la.synth.tq2_0_weights
+    ws = [gen(rows, cols, 70 + i) for i in range(count)]
+    x = la.synth.normal_f16((1, cols), 69)
+    dx = la.CudaBuffer.from_slice(ctx, x)
+    dws = [la.CudaBuffer.from_slice(ctx, w) for w in ws]
+    outs = [Guarded(la, ctx, rows * 2) for _ in range(count)]
+    b = la.CommandBatch.new(ctx)
+    getattr(kernels, f"matvec_{fmt}_group_into")(b, dws, count, dx, [o.view for o in outs], rows, cols)
+    streamed = rows >= 64 and ((rows + 63) // 64) * count >= 2 * ctx.caps()["sm_count"]
+    assert b.dispatch_count() == (1 if streamed else count)
+    b.commit_and_wait()
+    f = orc.Q4_0 if fmt == "q4_0" else orc.TQ2_0
+    for i in range(count):
+        got = outs[i].read(np.float16)
+        single = la.CudaBuffer.empty(ctx, rows * 2)
+        b = la.CommandBatch.new(ctx)
+        getattr(kernels, f"matvec_{fmt}_into")(b, dws[i], dx, single, rows, cols)
+        b.commit_and_wait()
+        if not streamed:
+            assert np.array_equal(got.view(np.uint16), single.as_slice(np.uint16))
+        rel_close(got, orc.matmul_nt(f, x, ws[i], 1, cols, rows).reshape(-1), 2e-3, f"group matvec {i}")
