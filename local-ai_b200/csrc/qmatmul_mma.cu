@@ -60,6 +60,12 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
+// d = a . b (no accumulator input: the zero operand needs no registers)
+__device__ __forceinline__ void mma16816_zero(float (&d)[4], const uint32_t (&a)[4], const uint32_t b0, const uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t b0, const uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
@@ -86,6 +92,11 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cas
 __device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
 __device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
 __device__ __forceinline__ uint32_t lds_u16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
+__device__ __forceinline__ uint32_t lds_u16s(uint32_t addr) {   // by shared-memory address
+    uint16_t v;
+    asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
 
 template <int FMT> struct Fmt;
 template <> struct Fmt<FMT_Q4_0> { static constexpr int bytes = 18, elems = 32, chunk_blocks = CHUNK_K / 32; };
@@ -472,13 +483,13 @@ __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParam
         const int tile = (int)blockIdx.x + (it / nchunks) * (int)gridDim.x, ch = it % nchunks;
         const uint8_t *st = smem + (it % W_STAGES) * W_STAGE;
         const uint32_t xb = smem_u32(st + W_ROWS * W_RAW_RS) + xl;
-        const uint8_t *rbase[4];
+        uint32_t rbase[4];   // shared-memory addresses
         bool rvalid[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int r = warp * 32 + g + 8 * i, row = tile * W_ROWS + r;
             const size_t g0 = (size_t)row * rb + (size_t)ch * 4 * BB;
-            rbase[i] = st + r * W_RAW_RS + (int)(g0 & 15);
+            rbase[i] = smem_u32(st) + (uint32_t)(r * W_RAW_RS + (int)(g0 & 15));
             rvalid[i] = row < p.n;
         }
 #pragma unroll
@@ -488,9 +499,9 @@ __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParam
             uint32_t a[2][2][4];   // [k half of the block][fragment][register]
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint8_t *bp = rbase[i] + bi * BB;
-                df[i] = rvalid[i] ? __half2float(*reinterpret_cast<const __half *>(bp)) : 0.0f;
-                const uint32_t wq = lds_u16(bp + 2 + 2 * t) | (lds_u16(bp + 10 + 2 * t) << 16);
+                const uint32_t bp = rbase[i] + (uint32_t)(bi * BB);
+                df[i] = rvalid[i] ? __half2float(__ushort_as_half((unsigned short)lds_u16s(bp))) : 0.0f;
+                const uint32_t wq = lds_u16s(bp + 2 + 2 * t) | (lds_u16s(bp + 10 + 2 * t) << 16);
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
                     const uint32_t codes = (wq >> (4 * part)) & 0x0F0F0F0Fu;
@@ -506,12 +517,11 @@ __global__ void __launch_bounds__(W_NT, 1) qgemm_mma_wide_kernel(const WideParam
                 ldmatrix_x4(b[1], xk + (uint32_t)(32 + 8 * j * W_XS));
 #pragma unroll
                 for (int f = 0; f < 2; f++) {
-                    float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int part = 0; part < 2; part++) {
-                        mma16816(t0, a[part][f], b[part][0], b[part][1]);
-                        mma16816(t1, a[part][f], b[part][2], b[part][3]);
-                    }
+                    float t0[4], t1[4];
+                    mma16816_zero(t0, a[0][f], b[0][0], b[0][1]);
+                    mma16816_zero(t1, a[0][f], b[0][2], b[0][3]);
+                    mma16816(t0, a[1][f], b[1][0], b[1][1]);
+                    mma16816(t1, a[1][f], b[1][2], b[1][3]);
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         c[f][j][e] = fmaf(df[2 * f + (e >> 1)], t0[e], c[f][j][e]);
