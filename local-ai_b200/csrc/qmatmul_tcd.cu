@@ -144,8 +144,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
@@ -392,15 +392,15 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
         for (int cc = 0; cc < 32; cc += 16) {
             if (!failed && total_steps > 0) {
                 const uint32_t ta = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(c0 + cc);
-                uint32_t a0[16], a1[16];
+                uint32_t a0[16], a1[16], a2[16], a3[16];   // the four accumulators' loads are in flight together
                 tmem_ld16(ta, a0);
                 tmem_ld16(ta + NB, a1);
+                tmem_ld16(ta + 2 * NB, a2);
+                tmem_ld16(ta + 3 * NB, a3);
+                tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; j++) v[cc + j] = __uint_as_float(a0[j]) + __uint_as_float(a1[j]);
-                tmem_ld16(ta + 2 * NB, a0);
-                tmem_ld16(ta + 3 * NB, a1);
-#pragma unroll
-                for (int j = 0; j < 16; j++) v[cc + j] += __uint_as_float(a0[j]) + __uint_as_float(a1[j]);
+                for (int j = 0; j < 16; j++)
+                    v[cc + j] = (__uint_as_float(a0[j]) + __uint_as_float(a1[j])) + (__uint_as_float(a2[j]) + __uint_as_float(a3[j]));
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[cc + j] = 0.f;
