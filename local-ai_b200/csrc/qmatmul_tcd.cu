@@ -46,19 +46,21 @@ namespace {
 constexpr int TILE_ROWS = 128;   // weight rows per accumulator tile (UMMA M)
 constexpr int NB = 64;           // batch columns (UMMA N)
 constexpr int KT = 64;           // k per operand tile (one 128-byte swizzled row)
-constexpr int STEP_TILES = 2;    // operand tiles per pipeline step (128 k)
+constexpr int STEP_TILES = 4;    // 64-k activation tiles per pipeline step (256 k: one TQ2_0 block per weight row)
 constexpr int NBAR = 8;          // step-release barriers, one per step index mod 8
 constexpr int NISS = 4;          // MMA-issuing warps, one accumulator each
-constexpr int TMEM_COLS = NISS * NB;   // 256
+constexpr int SA = 2;            // weight-operand slots in tensor memory (one step each)
+constexpr int A_COLS = 128;      // columns of one weight slot: 256 k as f16 pairs
+constexpr int A_BASE = NISS * NB;      // the accumulators take columns 0 .. 255
+constexpr int TMEM_COLS = A_BASE + SA * A_COLS;   // 512: all of an SM's tensor memory
 // Operand tiles are K-major with the 128-byte swizzle: a row is its 64 k values (128 bytes, eight 16-byte chunks),
 // rows follow each other at 128 bytes, and chunk c of row r sits at chunk position c ^ (r % 8) of the row.  Tiles
 // start on 1024-byte boundaries (eight rows: the swizzle pattern's period).
 constexpr int ROW_BYTES = KT * 2;            // 128
-constexpr int A_TILE = TILE_ROWS * ROW_BYTES;   // one 128-row operand tile: 16 KB
 constexpr int B_TILE = NB * ROW_BYTES;          // 8 KB
 constexpr int B_SLOT = STEP_TILES * B_TILE;     // activations of one step
 constexpr int BB = 66;           // bytes per TQ2_0 block
-constexpr int MAX_STEPS = 12;    // steps per CTA (six blocks of 256 k)
+constexpr int MAX_STEPS = 6;     // steps per CTA (six blocks of 256 k)
 constexpr int MAX_GROUPS = 3;
 constexpr int MAX_KS = 8;        // portable cluster size
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -124,14 +126,20 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem_d] (+)= A[tmem_a] . B[bdesc]: the weight operand comes from tensor memory (lane = row, one column per two k)
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
         :
-        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// eight columns (16 weights of this thread's row) into tensor memory; taddr = the warp's lane quarter | column
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"r"(taddr), "r"(v[0]), "r"(v[1]),
+                 "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t mbar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
@@ -181,16 +189,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
 
 constexpr int NDQ = 8;                       // dequantizing warps (also the epilogue warps)
 constexpr int NT = (NDQ + 1 + NISS) * 32;    // + activation loader warp + MMA issuers
-constexpr int A_SLOT = STEP_TILES * A_TILE;  // weights of one step
 
 __global__ void __launch_bounds__(NT, 1)
 qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CUtensorMap x_map) {
     constexpr int ROWS = TILE_ROWS;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // operand tiles start on 1024-byte boundaries
-    const int SA = p.sa, SB = p.sb;
-    uint8_t *a_s = smem;                                   // [SA][A_SLOT]; reused for the split-K exchange
-    uint8_t *b_s = a_s + SA * A_SLOT;                      // [SB][B_SLOT]
+    const int SB = p.sb;
+    uint8_t *b_s = smem;                                   // [SB][B_SLOT]; slot 0 is reused for the split-K exchange
     uint8_t *raw = b_s + SB * B_SLOT;                      // [ROWS][raw_rs]
     uint64_t *bars = reinterpret_cast<uint64_t *>(raw + ROWS * p.raw_rs);
     uint64_t *raw_full = bars;                             // 1
@@ -210,14 +216,14 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
     const size_t rb = (size_t)p.nb * BB, w_bytes = rb * (size_t)n_rows;
     const int kbs = (int)blockIdx.z * p.bps, kbe = min(p.nb, kbs + p.bps), nblk = max(kbe - kbs, 0);
     const int seg = nblk * BB;
-    const int total_steps = nblk * 2;                      // 128-k steps of this CTA
-    // Step i of this CTA works on half block half_of(i) (block half_of(i) / 2 of the CTA's range, half % 2 of it);
-    // the walk starts at a half block that differs from CTA to CTA.
+    const int total_steps = nblk;                          // 256-k steps of this CTA: one block per row each
+    // Step i of this CTA works on block block_of(i) of the CTA's range; the walk starts at a block that differs from
+    // CTA to CTA.
     const int start = total_steps ? (int)((blockIdx.x * 5u + blockIdx.z) % (unsigned)total_steps) : 0;
-    auto half_of = [&](int i) -> int {
-        int hb = i + start;
-        if (hb >= total_steps) hb -= total_steps;
-        return hb;
+    auto block_of = [&](int i) -> int {
+        int bl = i + start;
+        if (bl >= total_steps) bl -= total_steps;
+        return bl;
     };
     // operand row r of the CTA -> weight matrix and row of it
     auto wmat_of = [&](int r) -> const uint8_t * { return p.geglu ? p.w[r >> 6] : p.w[grp]; };
@@ -273,23 +279,24 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { *abort_flag = 1; dead = true; }
         }
-        // This thread's share of every step: operand row 32 (warp & 3) + lane, the 16 code bytes 16 bq .. + 15
-        // (bq = warp >> 2) of the step's 32-byte half block: 64 weights.
+        // This thread's share of every step: operand row 32 (warp & 3) + lane and, of each 32-byte half h of the row's
+        // block, the 16 code bytes 16 bq .. + 15 (bq = warp >> 2): 128 weights.
         const int r = 32 * (warp & 3) + lane, bq = warp >> 2;
         const int row = wrow_of(r);
         const bool rvalid = row < n_rows;
         const size_t g0 = (size_t)row * rb + (size_t)kbs * BB;
         const uint8_t *rrow = raw + r * p.raw_rs + (int)(g0 & 15);
-        const uint32_t dst0 = smem_u32(a_s) + (uint32_t)(r * ROW_BYTES);
-        const uint32_t swz = (uint32_t)(r & 7);
+        // tensor-memory address of this warp's lane quarter, first column of the weight slots
+        const uint32_t ta0 = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)A_BASE;
         for (int i = 0; i < total_steps && !dead; i++) {
-            const int hb = half_of(i), s = i % SA, blk = hb >> 1, h = hb & 1;
+            const int blk = block_of(i), s = i % SA;
             if (i >= SA) {   // the MMAs that read this slot SA steps ago have completed
                 uint32_t ok = 1;
                 const int u = i - SA;
                 if (lane == 0) ok = mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) ? 1u : 0u;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
+                tc_fence_after();
             }
             // The four weights a code can mean, (q - 1) d, as a byte table for prmt: lut_lo / lut_hi hold the low /
             // high bytes of {-d, 0, d, 2d}; a selector nibble pair (q, q + 4) then assembles one f16.
@@ -297,35 +304,35 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
             const uint32_t p01 = (uint32_t)__half_as_ushort(__hneg(d));
             const uint32_t p23 = (uint32_t)__half_as_ushort(d) | ((uint32_t)__half_as_ushort(__hadd(d, d)) << 16);
             const uint32_t lut_lo = __byte_perm(p01, p23, 0x6420), lut_hi = __byte_perm(p01, p23, 0x7531);
-            // 16 code bytes, 2-byte aligned: five aligned words, funnel-shifted into place
-            const uint32_t ca = smem_u32(rrow + blk * BB + 32 * h + 16 * bq), sh = (ca & 3u) * 8u, wa = ca & ~3u;
-            const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8), w3 = lds32(wa + 12), w4 = sh ? lds32(wa + 16) : 0u;
-            const uint32_t cw[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
-                                    __funnelshift_r(w3, w4, sh)};
-            // element k = 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j.  Operand tile l >> 1 of
-            // the step takes l; chunk 4 (l & 1) + 2 bq + {0, 1} of the row takes bytes j = 16 bq + {0..7, 8..15}.
-            const uint32_t dst = dst0 + (uint32_t)(s * A_SLOT);
 #pragma unroll
-            for (int l = 0; l < 4; l++) {
-                uint32_t v[8];
+            for (int h = 0; h < 2; h++) {
+                // 16 code bytes, 2-byte aligned: five aligned words, funnel-shifted into place
+                const uint32_t ca = smem_u32(rrow + blk * BB + 32 * h + 16 * bq), sh = (ca & 3u) * 8u, wa = ca & ~3u;
+                const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8), w3 = lds32(wa + 12), w4 = sh ? lds32(wa + 16) : 0u;
+                const uint32_t cw[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                                        __funnelshift_r(w3, w4, sh)};
+                // element k = 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j: for a given l this
+                // thread's bytes j = 16 bq .. + 15 are 16 consecutive k, i.e. the eight columns from (128 h + 32 l + 16 bq) / 2
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const uint32_t sel = ((cw[q] >> (2 * l)) & 0x03030303u) * 0x11u + 0x40404040u;
-                    v[2 * q] = __byte_perm(lut_lo, lut_hi, sel);
-                    v[2 * q + 1] = __byte_perm(lut_lo, lut_hi, sel >> 16);
+                for (int l = 0; l < 4; l++) {
+                    uint32_t v[8];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const uint32_t sel = ((cw[q] >> (2 * l)) & 0x03030303u) * 0x11u + 0x40404040u;
+                        v[2 * q] = __byte_perm(lut_lo, lut_hi, sel);
+                        v[2 * q + 1] = __byte_perm(lut_lo, lut_hi, sel >> 16);
+                    }
+                    tmem_st8(ta0 + (uint32_t)(s * A_COLS + 64 * h + 16 * l + 8 * bq), v);
                 }
-                const uint32_t c0 = (uint32_t)(4 * (l & 1) + 2 * bq), dt = dst + (uint32_t)((l >> 1) * A_TILE);
-                const uint32_t da = dt + (((c0 ^ swz) << 4)), db = dt + ((((c0 + 1) ^ swz) << 4));
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(da), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(db), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&a_full[s]));
         }
     } else if (warp == NDQ) {
         // =========================== activation loader (one thread) ===========================
-        // Step i needs x[0..64, k .. k + 127], k = 256 (kbs + half / 2) + 128 (half % 2): two boxes of the tensor map.
+        // Step i needs x[0..64, k .. k + 255], k = 256 (kbs + block): four boxes of the tensor map.
         if (lane == 0) {
             lc_pdl_wait();   // the activations are the predecessor's output
             bool dead = false;
@@ -334,24 +341,23 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
                     const int u = i - SB;
                     if (!mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
                 }
-                const int hb = half_of(i), k0 = (kbs + (hb >> 1)) * 256 + (hb & 1) * 128;
+                const int k0 = (kbs + block_of(i)) * 256;
                 const uint32_t bar = smem_u32(&b_full[i % SB]), dst = smem_u32(b_s) + (uint32_t)((i % SB) * B_SLOT);
                 mbar_expect_tx(bar, (uint32_t)B_SLOT);
-                tma_load_2d(dst, &x_map, k0, 0, bar);
-                tma_load_2d(dst + B_TILE, &x_map, k0 + KT, 0, bar);
+#pragma unroll
+                for (int lp = 0; lp < STEP_TILES; lp++) tma_load_2d(dst + lp * B_TILE, &x_map, k0 + lp * KT, 0, bar);
             }
             if (dead) *abort_flag = 1;
         }
         __syncwarp();
     } else {
         // =========================== MMA issue (four warps, one thread each) ===========================
-        // Issuer iw owns TMEM accumulator iw (columns 64 iw ..) and takes K = 16 slice iw of both 64-k operand tiles of
-        // every step.
+        // Issuer iw owns TMEM accumulator iw (columns 64 iw ..) and takes K = 16 slice iw of each of the four 64-k tiles of
+        // every step: weights from tensor memory (eight columns per slice), activations from shared memory.
         // One thread per issuer runs the loop: every instruction in it (barrier test, MMA, commit) costs its thread on
         // the order of a hundred cycles or more, so nothing warp-wide is added.
         const int iw = warp - NDQ - 1;
         if (lane == 0) {
-            const uint64_t adesc0 = make_desc(smem_u32(a_s) + (uint32_t)(iw * 32));
             const uint64_t bdesc0 = make_desc(smem_u32(b_s) + (uint32_t)(iw * 32));
             const uint32_t tmem_acc = tmem_base + (uint32_t)(iw * NB);
             bool dead = false;
@@ -361,9 +367,9 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
                 tc_fence_after();
 #pragma unroll
                 for (int lp = 0; lp < STEP_TILES; lp++) {
-                    const uint64_t ad = adesc0 + (uint64_t)((uint32_t)((i % SA) * A_SLOT + lp * A_TILE) >> 4);
+                    const uint32_t ta = tmem_base + (uint32_t)(A_BASE + (i % SA) * A_COLS + 32 * lp + 8 * iw);
                     const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)((i % SB) * B_SLOT + lp * B_TILE) >> 4);
-                    umma_f16(tmem_acc, ad, bd, idesc, (i > 0 || lp > 0) ? 1u : 0u);
+                    umma_f16_ta(tmem_acc, ta, bd, idesc, (i > 0 || lp > 0) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&step_done[i % NBAR]));
             }
@@ -383,7 +389,7 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
 
     // ---- results.  Dequantizing warp w reads TMEM lanes 32 (w & 3) .. + 31 (one operand row per thread) and the 32
     //      batch columns starting at 32 (w >> 2); the four partial accumulators are added as (0 + 1) + (2 + 3) ----
-    float *red = reinterpret_cast<float *>(a_s);            // staging, reuses the weight slots: [NB cols][128 rows] f32
+    float *red = reinterpret_cast<float *>(b_s);            // staging, reuses the first activation slot: [NB cols][128 rows] f32
     __half *out = p.out[grp];
     const int lrow = 32 * (warp & 3) + lane, c0 = 32 * (warp >> 2);
     float v[32];
@@ -572,7 +578,7 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     if (ks > p.nb) ks = p.nb;
     if (ks < 1) ks = 1;
     int bps = (p.nb + ks - 1) / ks;
-    if (bps > MAX_STEPS / 2) bps = MAX_STEPS / 2;
+    if (bps > MAX_STEPS) bps = MAX_STEPS;
     ks = (p.nb + bps - 1) / bps;
     if (ks > MAX_KS) return -1;   // K too long for one cluster of this kernel
     p.ks = ks;
@@ -581,22 +587,19 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     if ((p.raw_rs / 16) % 2 == 0) p.raw_rs += 16;
     p.status = k->dev_status;
     p.wait_limit = WAIT_LIMIT;
-    // Shared memory: up to three activation slots, then as many weight slots as the rest holds (at least two; with
-    // split K the partial-tile exchange reuses them and must fit).
-    const int total = 2 * bps;
+    // Shared memory: the raw rows and up to three activation slots of one step each (the weight operand lives in
+    // tensor memory); the first slot doubles as the staging of the split-K / GeGLU exchange (32 KB, exactly one slot).
+    const int total = bps;
     const size_t fixed = (size_t)rows * p.raw_rs + (1 + 2 * MAX_STEPS + NBAR) * 8 + 16 + 1024;   // + 1024: tile alignment slack
     const size_t budget = k->ctx->smem_optin > 2048 ? k->ctx->smem_optin - 1024 : 0;
-    const size_t a_slot = (size_t)A_SLOT;
-    static const int sb_cap = []() { const char *e = getenv("LOCAL_CUDA_TCD_SB"); const int v = e ? atoi(e) : 0; return v >= 2 && v <= NBAR ? v : 3; }();
+    static const int sb_cap = []() { const char *e = getenv("LOCAL_CUDA_TCD_SB"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= MAX_STEPS ? v : 3; }();
     int sb = total < sb_cap ? total : sb_cap;
-    while (sb > 2 && fixed + (size_t)sb * B_SLOT + 2 * a_slot > budget) sb--;
-    if (fixed + (size_t)sb * B_SLOT + (total < 2 ? total : 2) * a_slot > budget) return -1;
-    int sa = (int)((budget - fixed - (size_t)sb * B_SLOT) / a_slot);
-    if (sa > total) sa = total;
-    if ((ks > 1 || geglu) && (size_t)sa * a_slot < (size_t)NB * TILE_ROWS * 4) return -1;
-    p.sa = sa;
+    while (sb > 1 && fixed + (size_t)sb * B_SLOT > budget) sb--;
+    if (fixed + (size_t)sb * B_SLOT > budget) return -1;
+    static_assert((size_t)B_SLOT >= (size_t)NB * TILE_ROWS * 4, "the exchange staging must fit one activation slot");
+    p.sa = SA;
     p.sb = sb;
-    const size_t smem = fixed + (size_t)sb * B_SLOT + (size_t)sa * a_slot;
+    const size_t smem = fixed + (size_t)sb * B_SLOT;
     CUtensorMap x_map;
     int st = make_x_map(&x_map, input->dptr, m, kk);
     if (st != LC_OK) return st;
