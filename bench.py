@@ -457,7 +457,7 @@ class DecodeStep:
 
     # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel: mean over one GeGLU and one down
     # launch of an ncu capture (cold cache) of the 5-layer workload, whose launches have the full model's shapes.
-    FFN_TRAFFIC = {"bytes": 4204032, "profile": "profiles/qgemm_tcd_tq2_0_m64.md",
+    FFN_TRAFFIC = {"bytes": 4205056, "profile": "profiles/qgemm_tcd_tq2_0_m64.md",
                    "captured_on": "bench.py --workload decode_b64_small (same launch shapes as decode_b64)"}
 
     def roofline(self, ms_per_step: float, peak: float, peak_kind: str, timed):

@@ -1,4 +1,4 @@
-// tcgen05 decode matmul: C[m, n] = A[m, K] (f16) x W[n, K]^T with W in GGUF TQ2_0 blocks, 8 < m <= 64, f16 out.
+// tcgen05 decode matmul: C[m, n] = A[m, K] (f16) x W[n, K]^T with W in GGUF TQ2_0 blocks, m <= 64, f16 out.
 // Stands in, at decode batch sizes, for the reference's simdgroup-matrix kernel matmul_nt_tq2_0_mma
 // (shaders/matvec_quant.metal:447-577) and, in GeGLU mode, for the pair of projections + gelu_mul of
 // local-engine/src/layer.rs:825-838.
@@ -7,25 +7,32 @@
 // around the length of the dependent chain after that kernel finishes:
 //   * weights take the MMA's M (128 rows per CTA; a GeGLU CTA holds 64 gate rows and the same 64 rows of the up
 //     matrix, so gate and up of an output element meet in one CTA), the batch its N (64, zero padded), f32
-//     accumulators in TMEM;
+//     accumulators in tensor memory (TMEM);
 //   * at most one CTA per SM and one wave per launch: K is split over a thread-block cluster so that the CTA count
 //     stays within the SM count, which also keeps the number of CTAs that re-read the same activations from L2 low;
+//   * the weight operand lives in tensor memory, not in shared memory: the dequantizing warps write f16 weights with
+//     tcgen05.st (thread r of the four lane quarters owns operand row r; 16 consecutive k are eight 32-bit columns),
+//     and the MMA takes A from tensor memory and B, the activations, from shared memory.  All 512 columns are in use:
+//     four 64-column accumulators and two weight slots of 128 columns (256 k) each;
 //   * before the dependency wait: TMEM allocation, barrier set-up, the raw quantized rows of the CTA's K range
-//     brought in by bulk copies (cp.async.bulk, one per row segment, completion counted on an mbarrier), and as many
-//     operand slots dequantized as shared memory holds -- none of it depends on the predecessor;
-//   * the pipeline runs in steps of 128 k (one 32-byte half of a TQ2_0 block per row: both 64-k operand tiles of a
-//     step come from the same code bytes), because every hand-over costs its thread a few hundred cycles: a barrier
-//     test ~150, an MMA issue ~210, a commit ~90 (measured), whatever the amount of data behind it;
-//   * after the wait one thread requests the activations of every step with TMA (cp.async.bulk.tensor, 128-byte
-//     swizzle applied by the copy engine, rows beyond m zero-filled by the tensor map's bounds), the dequantizing
-//     warps keep turning code bytes into f16 weights (the four values a 2-bit code can mean, (q - 1) d, sit in two
-//     registers as a byte table; one prmt assembles two weights; 16-byte stores into the K-major 128-byte-swizzled
-//     operand layout), and four warps issue tcgen05.mma.cta_group::1.kind::f16.  Issuing one MMA costs a warp about
-//     210 cycles whatever its shape (measured: M 64 / 128, N 16 .. 256 all the same), far more than the 32 cycles of
-//     arithmetic in a 128 x 64 x 16 MMA, but MMAs issued by different warps overlap fully (4 warps: 53 cycles per
-//     MMA).  So the four K = 16 slices of a 64-k tile belong to four issuing warps, each with its own TMEM
-//     accumulator (four partial sums over interleaved k, added in a fixed order in the epilogue); every issuer
-//     commits its MMAs of a step to the step's mbarrier, which hands the slots back after the fourth arrival;
+//     brought in by bulk copies (cp.async.bulk, one per row segment, completion counted on an mbarrier), and both
+//     weight slots dequantized -- none of it depends on the predecessor;
+//   * the pipeline runs in steps of 256 k (one TQ2_0 block per row), because every hand-over costs its thread a few
+//     hundred cycles whatever the amount of data behind it: a barrier test ~150, an MMA issue ~210, a commit ~90
+//     (measured), and the hand-overs of a step sit in series (slot released -> dequantize -> weights ready ->
+//     activations ready -> MMAs -> commit).  With 128-k steps and the weight operand staged in shared memory a launch
+//     cost 5.9 us + 0.78 us per step; tensor-memory weights removed the shared-memory stores and made room for twice
+//     the k per step (GeGLU 15.2 -> 12.1 us, the batch-64 decode step 2.91 -> 2.70 ms);
+//   * after the wait one thread requests the activations of every step with TMA (cp.async.bulk.tensor, four 64-k
+//     boxes, 128-byte swizzle applied by the copy engine, rows beyond m zero-filled by the tensor map's bounds) into
+//     a ring of up to three slots, the dequantizing warps keep turning code bytes into f16 weights (the four values
+//     a 2-bit code can mean, (q - 1) d, sit in two registers as a byte table; one prmt assembles two weights), and
+//     four warps issue tcgen05.mma.cta_group::1.kind::f16.  Issuing one MMA costs a warp about 210 cycles whatever its
+//     shape (measured: M 64 / 128, N 16 .. 256 all the same), far more than the 32 cycles of arithmetic in a
+//     128 x 64 x 16 MMA, but MMAs issued by different warps overlap fully (4 warps: 53 cycles per MMA).  So the four
+//     K = 16 slices of a 64-k tile belong to four issuing warps, each with its own TMEM accumulator (four partial
+//     sums over interleaved k, added in a fixed order in the epilogue); every issuer commits its MMAs of a step to
+//     the step's mbarrier, which hands the slots back after the fourth arrival;
 //   * CTAs walk their steps from different starting points so that the CTAs of a launch do not all ask L2 for the
 //     same activation lines at the same moment;
 //   * the accumulators are read back with tcgen05.ld by all dequantizing warps.  When K is split, the CTAs of a tile
@@ -73,7 +80,7 @@ struct TcdParams {
     int m, K, nb;        // nb = blocks per weight row
     int ks, bps;         // split-K: grid.z = cluster size = ks, bps = blocks per split
     int raw_rs;          // bytes reserved per row of raw blocks (odd multiple of 16)
-    int sa, sb;          // operand slots (one step each) in shared memory: weights / activations
+    int sa, sb;          // operand slots (one step each): weights in tensor memory (always SA) / activations in shared memory
     int geglu;           // 1: operand rows 0-63 are gate rows, 64-127 the same rows of the up matrix; out[0] = gelu(gate) * up
     int *status;
     uint32_t wait_limit;
