@@ -13,7 +13,8 @@
 //   * the weight operand lives in tensor memory, not in shared memory: the dequantizing warps write f16 weights with
 //     tcgen05.st (thread r of the four lane quarters owns operand row r; 16 consecutive k are eight 32-bit columns),
 //     and the MMA takes A from tensor memory and B, the activations, from shared memory.  All 512 columns are in use:
-//     four 64-column accumulators and two weight slots of 128 columns (256 k) each;
+//     four 64-column accumulators and two weight slots of 128 columns (256 k) each (127 registers x 416 threads
+//     keep this kernel at one CTA per SM, so no second CTA ever waits for tensor memory behind a cluster barrier);
 //   * before the dependency wait: TMEM allocation, barrier set-up, the raw quantized rows of the CTA's K range
 //     brought in by bulk copies (cp.async.bulk, one per row segment, completion counted on an mbarrier), and both
 //     weight slots dequantized -- none of it depends on the predecessor;
