@@ -30,8 +30,19 @@ __device__ __forceinline__ unsigned tq_unpack(const uint8_t *codes, unsigned d, 
 
 // Unnormalised in-place FWHT over sh[0..d), one element per thread.
 // Pair (j, j+len): new[j] = a+b, new[j+len] = a-b.
+// The strides below 32 pair elements of one warp: they run as shuffles on the thread's own value (the same
+// operands in the same order as the shared-memory form, so the result is bit-identical); only the strides from 32
+// up go through shared memory.  d is a power of two >= 32, every thread of the block calls.
 __device__ __forceinline__ void fwht_block(float *sh, unsigned d, unsigned t) {
-    for (unsigned len = 1; len < d; len <<= 1) {
+    __syncthreads();   // sh[t] was written by its owner; nobody reads it before this point
+    float v = sh[t];
+#pragma unroll
+    for (unsigned len = 1; len < 32; len <<= 1) {
+        const float other_v = __shfl_xor_sync(0xffffffffu, v, len);
+        v = (t & len) ? __fsub_rn(other_v, v) : __fadd_rn(v, other_v);
+    }
+    sh[t] = v;
+    for (unsigned len = 32; len < d; len <<= 1) {
         __syncthreads();
         const float self_v = sh[t], other_v = sh[t ^ len];
         __syncthreads();
@@ -56,8 +67,17 @@ __device__ __forceinline__ void encode_row(float xv, unsigned t, unsigned hd, un
     __syncthreads();
     if (norm_mode == 0) {
         if (t == 0) {
+            // the reference's sequential f32 sum, in index order: the additions are a dependent chain, the loads
+            // are not (16 values per round as four 16-byte loads; hd is a multiple of 32)
+            const float4 *r4 = reinterpret_cast<const float4 *>(red);
             float s = 0.f;
-            for (unsigned i = 0; i < hd; i++) s = __fadd_rn(s, red[i]);
+            for (unsigned i = 0; i < hd / 4; i += 4) {
+                const float4 a = r4[i], b = r4[i + 1], c = r4[i + 2], e = r4[i + 3];
+                s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, a.x), a.y), a.z), a.w);
+                s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, b.x), b.y), b.z), b.w);
+                s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, c.x), c.y), c.z), c.w);
+                s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, e.x), e.y), e.z), e.w);
+            }
             *norm_sh = __fsqrt_rn(s);
         }
     } else {
@@ -110,7 +130,7 @@ __global__ void encode_kv_kernel(const __half *__restrict__ input, const float *
     lc_pdl_trigger();  // successors may be scheduled; they wait for this grid before reading its output
     lc_pdl_wait();     // everything below may read what the predecessor wrote
     __shared__ float sh[MAX_HD];
-    __shared__ float red[MAX_HD];
+    __shared__ __align__(16) float red[MAX_HD];
     __shared__ unsigned code_sh[MAX_HD];
     __shared__ float norm_sh;
     const unsigned t = threadIdx.x, g_in = blockIdx.x;
@@ -149,7 +169,7 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
                                 float rotary_factor, int norm_mode, int *status) {
     lc_pdl_trigger();
     __shared__ float sh[MAX_HD];
-    __shared__ float red[MAX_HD];
+    __shared__ __align__(16) float red[MAX_HD];
     __shared__ unsigned code_sh[MAX_HD];
     __shared__ float norm_sh;
     __shared__ float red2[32];
