@@ -1,5 +1,5 @@
 // Tensor-core decode attention over TurboQuant tq2 codes, head_dim 256, up to 8 q-heads per kv-head:
-// the shape of the synthetic E2B-like decoder and of BASELINE's attention configuration.  Same
+// the shape of the synthetic E2B-like decoder and of the attention benchmark configuration.  Same
 // contract, grid and split-K partial layout as tq_attn_split_kernel (attention_tq.cu), which remains
 // the general path (other head sizes, tq3 / tq4).
 //
