@@ -328,7 +328,8 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
                  const lc_buf *kc, const lc_buf *kn, const lc_buf *vc, const lc_buf *vn, const lc_buf *levels,
                  const lc_buf *signs, lc_buf *out, const lc_buf *positions, uint32_t hd, uint32_t kv_len,
                  uint32_t current_pos, uint32_t lane_capacity, uint32_t n_q, uint32_t n_kv, uint32_t window,
-                 uint32_t bits, uint32_t n_lanes, uint32_t ring, float scale, uint32_t n_rows = 0) {
+                 uint32_t bits, uint32_t n_lanes, uint32_t ring, float scale, uint32_t n_rows = 0,
+                 const lc_buf *qfrag = nullptr) {
     // n_rows != 0: prefill / multi-row verify over one cache: row r at position current_pos + r (n_lanes is ignored)
     const bool prefill = n_rows != 0;
     if (prefill) n_lanes = n_rows;
@@ -448,6 +449,11 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     p.direct_out = direct ? 1 : 0;
     p.scale = scale;
     p.status = k->dev_status;
+    p.qfrag = nullptr;
+    if (qfrag && use_mma && fused && lc_qfrag_supported(hd, bits, n_q, n_kv)) {
+        LC_REQUIRE(qfrag->bytes >= qn * 4, "%s: query fragment buffer too small", name);
+        p.qfrag = (const uint4 *)qfrag->dptr;
+    }
     dim3 grid(n_splits, n_kv * gchunks, n_lanes);
     int st;
     if (use_mma) {
@@ -562,6 +568,22 @@ int lc_tq_attention_batched_into(lc_kernels *k, lc_batch *b, const lc_buf *q, co
 
 }  // extern "C"
 
+bool lc_qfrag_supported(uint32_t head_dim, uint32_t bits, uint32_t n_q_heads, uint32_t n_kv_heads) {
+    return head_dim == 256 && bits == 2 && n_kv_heads >= 1 && n_q_heads % n_kv_heads == 0 &&
+           (n_q_heads / n_kv_heads) % 8 == 0;
+}
+
+int lc_tq_attention_batched_frag(lc_kernels *k, lc_batch *b, const lc_buf *q, const lc_buf *k_codes, const lc_buf *k_norms,
+                                 const lc_buf *v_codes, const lc_buf *v_norms, const lc_buf *levels, const lc_buf *signs,
+                                 lc_buf *attn_out, const lc_buf *positions, uint32_t head_dim, uint32_t lane_capacity,
+                                 uint32_t num_q_heads, uint32_t num_kv_heads, uint32_t window, uint32_t bits,
+                                 uint32_t n_lanes, uint32_t ring_capacity, float softmax_scale, const lc_buf *qfrag) {
+    if (!positions) return lc_fail(LC_ERR_INVALID_ARGUMENT, "tq_attention_batched: positions is NULL");
+    return tq_attention("tq_attention_batched", k, b, q, true, k_codes, k_norms, v_codes, v_norms, levels, signs,
+                        attn_out, positions, head_dim, 0, 0, lane_capacity, num_q_heads, num_kv_heads, window, bits,
+                        n_lanes, ring_capacity, softmax_scale, 0, qfrag);
+}
+
 // ---------------------------------------------------------------------------
 // Allocation-free variant of lc_tq_attention_into.
 //
@@ -674,6 +696,7 @@ extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const 
 
     TqAttnParams p;
     p.out_f16 = nullptr;
+    p.qfrag = nullptr;
     p.cluster_merge = 0;
     p.rq = nullptr;
     p.q = (const __half *)q->dptr;

@@ -187,7 +187,22 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     const size_t q_row = ((size_t)lane_idx * p.n_q + qh0 + warp) * HD + 8 * lane;   // warp w owns head w
     uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
     float4 q_s0 = make_float4(0.f, 0.f, 0.f, 0.f), q_s1 = q_s0;
-    if (warp < gvalid) {
+    // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15.
+    // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
+    // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
+    uint32_t bq[16][2], bql[16][2];
+    const bool have_frag = p.qfrag != nullptr;   // the launch that wrote q left the fragments ready (group % 8 == 0)
+    if (have_frag) {
+        const uint4 *src = p.qfrag + ((size_t)lane_idx * (p.n_q >> 3) + (qh0 >> 3)) * 512 + lane;
+#pragma unroll
+        for (int s = 0; s < 16; s++) {
+            const uint4 v = src[s * 32];
+            bq[s][0] = v.x;
+            bq[s][1] = v.y;
+            bql[s][0] = v.z;
+            bql[s][1] = v.w;
+        }
+    } else if (warp < gvalid) {
         if (p.fused_q) {
             q_raw = *reinterpret_cast<const uint4 *>(p.q + q_row);
             q_s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
@@ -256,7 +271,7 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     }
 
     // ---- prologue 2 (independent of gamma): rotated, scaled query; warp w owns head w ----
-    {
+    if (!have_frag) {
         const int h = warp;   // NW == G
         float x[8];
         if (h < gvalid) {
@@ -306,24 +321,22 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
         *reinterpret_cast<float4 *>(rq_s + rq_index(h, 8 * lane + 4)) = make_float4(x[4], x[5], x[6], x[7]);
     }
     __syncthreads();   // the rotated query is in place; so is every copy of the table
-    // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15
-    // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
-    // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
-    uint32_t bq[16][2], bql[16][2];
+    if (!have_frag) {
 #pragma unroll
-    for (int s = 0; s < 16; s++) {
-        const float4 r4 = *reinterpret_cast<const float4 *>(rq_s + (s * 32 + lane) * 4);
-        const float r[4] = {r4.x, r4.y, r4.z, r4.w};
-        float hi[4], lo[4];
+        for (int s = 0; s < 16; s++) {
+            const float4 r4 = *reinterpret_cast<const float4 *>(rq_s + (s * 32 + lane) * 4);
+            const float r[4] = {r4.x, r4.y, r4.z, r4.w};
+            float hi[4], lo[4];
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            hi[e] = __half2float(__float2half_rn(r[e]));
-            lo[e] = r[e] - hi[e];
+            for (int e = 0; e < 4; e++) {
+                hi[e] = __half2float(__float2half_rn(r[e]));
+                lo[e] = r[e] - hi[e];
+            }
+            bq[s][0] = pack_h2(hi[0], hi[1]);
+            bq[s][1] = pack_h2(hi[2], hi[3]);
+            bql[s][0] = pack_h2(lo[0], lo[1]);
+            bql[s][1] = pack_h2(lo[2], lo[3]);
         }
-        bq[s][0] = pack_h2(hi[0], hi[1]);
-        bq[s][1] = pack_h2(hi[2], hi[3]);
-        bql[s][0] = pack_h2(lo[0], lo[1]);
-        bql[s][1] = pack_h2(lo[2], lo[3]);
     }
     const uint2 *lut_lane = lut + (lane & (LUT_COPIES - 1));
 

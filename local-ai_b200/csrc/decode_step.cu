@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "lc_internal.h"
+#include "attention_tq.h"
 
 int lc_matmul_nt_tq2_0_grouped(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
                                lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk);
@@ -44,7 +45,7 @@ struct lc_model {
     std::vector<lc_model_layer> layers;
     const lc_buf *embed = nullptr, *final_norm = nullptr;
     lc_buf *levels = nullptr, *signs = nullptr, *ones = nullptr;
-    lc_buf *x = nullptr, *x2 = nullptr, *normed = nullptr, *q = nullptr, *kbuf = nullptr, *vbuf = nullptr,
+    lc_buf *x = nullptr, *x2 = nullptr, *normed = nullptr, *q = nullptr, *qfrag = nullptr, *kbuf = nullptr, *vbuf = nullptr,
            *attn = nullptr, *resid = nullptr, *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
     std::vector<lc_buf *> owned;
     // lane-group chains (see chain_count): side streams, their own kernels objects (split-K scratch is per object) and
@@ -121,6 +122,11 @@ int lc_model_create(lc_ctx *ctx, lc_kernels *k, const lc_model_config *cfg, lc_m
         (st = alloc(m, n * qd * 2, &m->attn)) || (st = alloc(m, n * c.hidden * 2, &m->resid)) ||
         (st = alloc(m, n * c.inter * 2, &m->gate)) || (st = alloc(m, n * c.inter * 2, &m->up)) ||
         (st = alloc(m, n * c.hidden * 2, &m->ffn)) || (st = alloc(m, n * (size_t)c.vocab * 4, &m->logits)))
+        return fail(st);
+    // LOCAL_CUDA_QFRAG=0 keeps the attention kernel's own query prologue (same results; for A/B timing and tests)
+    const char *qf_env = getenv("LOCAL_CUDA_QFRAG");
+    if (!(qf_env && qf_env[0] == '0') && lc_qfrag_supported(c.head_dim, c.kv_bits, c.n_q_heads, c.n_kv_heads) &&
+        (st = alloc(m, n * qd * 4, &m->qfrag)))
         return fail(st);
     {
         const char *e = getenv("LOCAL_CUDA_DECODE_CHAINS");
@@ -253,6 +259,8 @@ static int run_layers(lc_model *m, lc_kernels *k, lc_batch *b, const lc_buf *pos
     lc_buf attn = view(m->attn, (size_t)lane0 * qd * 2), resid = view(m->resid, (size_t)lane0 * H * 2);
     lc_buf gate = view(m->gate, (size_t)lane0 * I * 2), up = view(m->up, (size_t)lane0 * I * 2);
     lc_buf ffn = view(m->ffn, (size_t)lane0 * H * 2);
+    lc_buf qfrag_v = m->qfrag ? view(m->qfrag, (size_t)lane0 * qd * 4) : lc_buf();
+    lc_buf *qf = m->qfrag ? &qfrag_v : nullptr;
     lc_buf *x = &xa, *xn = &xb;
     const size_t nl = m->layers.size();
     int st;
@@ -269,10 +277,12 @@ static int run_layers(lc_model *m, lc_kernels *k, lc_batch *b, const lc_buf *pos
             const uint32_t ns[3] = {qd, kd, kd};
             STEP(lc_matmul_nt_tq2_0_grouped(k, b, &normed, 3, ws, os, ns, n, H));
         }
-        STEP(lc_qkv_post_batched_into(k, b, &q, L.q_norm, NQ, &kbuf, &vbuf, L.k_norm, &pos, m->levels, m->signs, &kc, &kn,
-                                      &vc, &vn, HD, NKV, L.lane_rows, c.kv_bits, n, L.ring, c.rms_eps, c.rope_theta, 1.0f));
-        STEP(lc_tq_attention_batched_into(k, b, &q, &kc, &kn, &vc, &vn, m->levels, m->signs, &attn, &pos, HD, L.lane_rows,
-                                          NQ, NKV, L.window, c.kv_bits, n, L.ring, c.softmax_scale));
+        // where the tensor-core attention kernel runs, the launch that finishes q also leaves its rotated, scaled
+        // fragments, so attention starts on the keys as soon as it may read them
+        STEP(lc_qkv_post_frag(k, b, &q, L.q_norm, NQ, &kbuf, &vbuf, L.k_norm, &pos, m->levels, m->signs, &kc, &kn, &vc, &vn,
+                              HD, NKV, L.lane_rows, c.kv_bits, n, L.ring, c.rms_eps, c.rope_theta, 1.0f, qf, c.softmax_scale));
+        STEP(lc_tq_attention_batched_frag(k, b, &q, &kc, &kn, &vc, &vn, m->levels, m->signs, &attn, &pos, HD, L.lane_rows,
+                                          NQ, NKV, L.window, c.kv_bits, n, L.ring, c.softmax_scale, qf));
         STEP(lc_matmul_nt_tq2_0_into(k, b, &attn, L.wo, &ffn, n, qd, H));
         // resid = rms_norm(ffn, post_attn) + x ; normed = rms_norm(resid, ffn_norm)
         STEP(lc_rms_norm_add_norm_into(k, b, &ffn, L.post_attn_norm, x, &resid, L.ffn_norm, &normed, H, n, c.rms_eps));

@@ -15,6 +15,7 @@
 #include <string.h>
 
 #include "lc_internal.h"
+#include "attention_tq.h"
 
 namespace {
 
@@ -166,7 +167,7 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
                                 uint8_t *__restrict__ k_packed, __half *__restrict__ k_norms,
                                 uint8_t *__restrict__ v_packed, __half *__restrict__ v_norms, unsigned hd, unsigned n_kv,
                                 unsigned lane_capacity, unsigned bits, unsigned ring, float eps, float theta,
-                                float rotary_factor, int norm_mode, int *status) {
+                                float rotary_factor, int norm_mode, int *status, uint4 *qfrag, float q_scale) {
     lc_pdl_trigger();
     __shared__ float sh[MAX_HD];
     __shared__ __align__(16) float red[MAX_HD];
@@ -212,6 +213,27 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
     }
     if (role == 0) {
         qrow[t] = __float2half_rn(xr);
+        if (qfrag) {
+            // The tensor-core attention kernel's first steps, done here where the row is already in registers: signs,
+            // 256-point Walsh-Hadamard transform, softmax scale / sqrt(hd), split into an f16 and the f16 of the
+            // remainder, stored in that kernel's fragment order (hd == 256 and heads in groups of 8: host-checked).
+            // Same operations in the same order as the kernel's own prologue, so attention results do not change.
+            sh[t] = __fmul_rn(xr, signs[t]);
+            fwht_block(sh, hd, t);
+            const float v = __fmul_rn(sh[t], __fdiv_rn(q_scale, __fsqrt_rn((float)hd)));
+            const __half hi = __float2half_rn(v), lo = __float2half_rn(__fsub_rn(v, __half2float(hi)));
+            const uint32_t own = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
+            const uint32_t p1 = __shfl_down_sync(0xffffffffu, own, 1), p2 = __shfl_down_sync(0xffffffffu, own, 2),
+                           p3 = __shfl_down_sync(0xffffffffu, own, 3);
+            if ((t & 3) == 0) {
+                uint4 e;
+                e.x = (own & 0xFFFFu) | (p1 << 16);
+                e.y = (p2 & 0xFFFFu) | (p3 << 16);
+                e.z = (own >> 16) | (p1 & 0xFFFF0000u);
+                e.w = (p2 >> 16) | (p3 & 0xFFFF0000u);
+                qfrag[((size_t)row * (n_q >> 3) + (head >> 3)) * 512 + ((t & 63) >> 2) * 32 + 4 * (head & 7) + (t >> 6)] = e;
+            }
+        }
         return;
     }
     const unsigned ppos = ring ? pos % ring : pos;
@@ -507,7 +529,8 @@ static int kv_write_common(const char *name, lc_kernels *k, lc_batch *b, lc_buf 
                            const lc_buf *positions, const lc_buf *levels, const lc_buf *signs, lc_buf *k_packed,
                            lc_buf *k_norms, lc_buf *v_packed, lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads,
                            uint32_t lane_capacity, uint32_t bits, uint32_t n_lanes, uint32_t ring_capacity, float eps,
-                           float rope_theta, float partial_rotary_factor) {
+                           float rope_theta, float partial_rotary_factor, lc_buf *qfrag = nullptr,
+                           float softmax_scale = 0.f) {
     if (!k || !b || !k_in || !v_in || !k_norm_weight || !positions || !levels || !signs || !k_packed || !k_norms ||
         !v_packed || !v_norms || (n_q_heads && (!q || !q_norm_weight)))
         return lc_fail(LC_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
@@ -523,6 +546,12 @@ static int kv_write_common(const char *name, lc_kernels *k, lc_batch *b, lc_buf 
         LC_REQUIRE(q->bytes >= (size_t)n_lanes * n_q_heads * head_dim * 2 && q_norm_weight->bytes >= head_dim * 2u,
                    "%s: query buffers too small", name);
     LC_REQUIRE(levels->bytes >= (4u << bits) && signs->bytes >= head_dim * 4u, "%s: codec buffers too small", name);
+    if (qfrag) {
+        LC_REQUIRE(n_q_heads && lc_qfrag_supported(head_dim, bits, n_q_heads, n_kv_heads),
+                   "%s: query fragments need head_dim 256, 2-bit codes and q heads in groups of 8 per kv head", name);
+        LC_REQUIRE(qfrag->bytes >= (size_t)n_lanes * n_q_heads * head_dim * 4 && lc_aligned(qfrag->dptr, 16),
+                   "%s: query fragment buffer too small or misaligned", name);
+    }
     LC_REQUIRE(ring_capacity <= lane_capacity, "%s: ring %u exceeds lane capacity %u", name, ring_capacity, lane_capacity);
     const size_t rows = (size_t)n_lanes * lane_capacity * n_kv_heads;
     LC_REQUIRE(k_packed->bytes >= rows * cb && v_packed->bytes >= rows * cb && k_norms->bytes >= rows * 2 &&
@@ -536,7 +565,8 @@ static int kv_write_common(const char *name, lc_kernels *k, lc_batch *b, lc_buf 
                                 (const float *)levels->dptr, (const float *)signs->dptr, (uint8_t *)k_packed->dptr,
                                 (__half *)k_norms->dptr, (uint8_t *)v_packed->dptr, (__half *)v_norms->dptr, head_dim,
                                 n_kv_heads, lane_capacity, bits, ring_capacity, eps, rope_theta, partial_rotary_factor,
-                                k->kv_norm_mode, k->dev_status));
+                                k->kv_norm_mode, k->dev_status, qfrag ? (uint4 *)qfrag->dptr : (uint4 *)nullptr,
+                                softmax_scale));
     b->dispatch_count++;
     return LC_OK;
 }
@@ -565,3 +595,16 @@ int lc_qkv_post_batched_into(lc_kernels *k, lc_batch *b, lc_buf *q, const lc_buf
 }
 
 }  // extern "C"
+
+int lc_qkv_post_frag(lc_kernels *k, lc_batch *b, lc_buf *q, const lc_buf *q_norm_weight, uint32_t n_q_heads,
+                     const lc_buf *k_in, const lc_buf *v_in, const lc_buf *k_norm_weight, const lc_buf *positions,
+                     const lc_buf *levels, const lc_buf *signs, lc_buf *k_packed, lc_buf *k_norms, lc_buf *v_packed,
+                     lc_buf *v_norms, uint32_t head_dim, uint32_t n_kv_heads, uint32_t lane_capacity, uint32_t bits,
+                     uint32_t n_lanes, uint32_t ring_capacity, float eps, float rope_theta, float partial_rotary_factor,
+                     lc_buf *qfrag, float softmax_scale) {
+    if (!q || !q_norm_weight || n_q_heads == 0)
+        return lc_fail(LC_ERR_INVALID_ARGUMENT, "qkv_post_batched: the query buffer, its norm weight and n_q_heads are required");
+    return kv_write_common("qkv_post_batched", k, b, q, q_norm_weight, n_q_heads, k_in, v_in, k_norm_weight, positions, levels,
+                           signs, k_packed, k_norms, v_packed, v_norms, head_dim, n_kv_heads, lane_capacity, bits, n_lanes,
+                           ring_capacity, eps, rope_theta, partial_rotary_factor, qfrag, softmax_scale);
+}

@@ -252,3 +252,32 @@ def test_step_at_the_benchmark_kernel_routes(la, orc, ctx, kernels, bench_route_
     if mism == 0:
         hs = max(1.0, float(np.abs(want_h.astype(np.float32)).max()))
         assert np.abs(got_h.astype(np.float32) - want_h.astype(np.float32)).max() <= 4e-3 * hs
+
+
+def test_query_fragments_from_the_kv_write_change_nothing(la, ctx, kernels, monkeypatch):
+    """At the benchmark's head shape the launch that finishes q also writes the attention kernel's rotated, scaled
+    query fragments.  They are the values the attention kernel would derive itself, so a model built with that
+    hand-over switched off must produce the same logits bit for bit, over steps that fill and then read the pools."""
+    cfg = bench_route_cfg(la, 9, max_context=256, vocab=4096)
+    layers = [la.model.synth_layer(cfg, i, seed=21) for i in range(cfg.n_layers)]
+    emb, fnorm = la.model.synth_embedding(cfg, seed=21)
+
+    def run():
+        gm = la.DecodeModel(ctx, kernels, cfg)
+        for i, t in enumerate(layers):
+            gm.set_layer(i, t)
+        gm.set_embedding(emb, fnorm)
+        rng = np.random.default_rng(5)
+        outs = []
+        for step in range(6):
+            tokens = rng.integers(0, cfg.vocab, 9).astype(np.uint32)
+            positions = np.full(9, step, np.uint32)
+            logits, _, _ = gpu_step(la, ctx, gm, tokens, positions, 9)
+            outs.append(logits.copy())
+        return np.stack(outs)
+
+    with_frag = run()
+    monkeypatch.setenv("LOCAL_CUDA_QFRAG", "0")
+    without = run()
+    assert np.all(np.isfinite(with_frag))
+    assert np.array_equal(with_frag.view(np.uint32), without.view(np.uint32))
