@@ -271,23 +271,9 @@ __global__ void tq_attn_merge_kernel(const float *__restrict__ partial, const fl
         out_f32[qh * hd + t] = v;
         return;
     }
-    // inverse rotation: the butterflies whose partner sits in the same warp (strides below 32) run as shuffles on
-    // the thread's own value, the rest through shared memory; same operands in the same order either way
-    float w = v;
-#pragma unroll
-    for (unsigned len = 1; len < 32; len <<= 1) {
-        const float other_v = __shfl_xor_sync(0xffffffffu, w, len);
-        w = (t & len) ? (other_v - w) : (w + other_v);
-    }
-    sh[t] = w;
-    for (unsigned len = 32; len < hd; len <<= 1) {
-        __syncthreads();
-        const float self_v = sh[t], other_v = sh[t ^ len];
-        __syncthreads();
-        sh[t] = (t & len) ? (other_v - self_v) : (self_v + other_v);
-    }
-    __syncthreads();
-    out_f16[qh * hd + t] = __float2half_rn(sh[t] * (1.0f / sqrtf((float)hd)) * signs[t]);
+    // inverse rotation
+    const float w = lc_fwht_value(v, sh, hd, t);
+    out_f16[qh * hd + t] = __float2half_rn(w * (1.0f / sqrtf((float)hd)) * signs[t]);
 }
 
 template <int HD, int BITS, int G>

@@ -125,6 +125,47 @@ static inline cudaError_t lc_launch(void (*kern)(KArgs...), dim3 grid, dim3 bloc
 #ifdef __CUDACC__
 __device__ __forceinline__ void lc_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void lc_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Walsh-Hadamard transform (unnormalised) over d = 32 .. 512 elements held one per thread of a d-thread block;
+// returns the thread's element of the result.  Butterflies run in ascending stride, lower = a + b, upper = a - b.
+// The strides below 32 pair lanes of one warp and run as shuffles.  For the strides from 32 up every thread
+// publishes its value once in `sh` and rebuilds the butterflies its result depends on from the d / 32 values it
+// needs: the same additions on the same operands as stage-by-stage passes through shared memory, hence bit-identical
+// to them, with one barrier in all instead of two per stage.  No thread may still be reading `sh` from earlier code
+// when the block enters (callers that used it since their last barrier place one), and callers that reuse `sh`
+// afterwards synchronise first.
+template <int P>
+__device__ __forceinline__ float lc_fwht_cross_warp(float v, float *sh, unsigned t) {
+    sh[t] = v;
+    __syncthreads();
+    float a[P];
+#pragma unroll
+    for (int j = 0; j < P; j++) a[j] = sh[t ^ ((unsigned)j << 5)];
+#pragma unroll
+    for (int s = 0; (1 << s) < P; s++) {
+        const bool upper = t & (32u << s);
+#pragma unroll
+        for (int j = 0; j < P; j += 2 << s) {
+            const float self_v = a[j], other_v = a[j | (1 << s)];
+            a[j] = upper ? __fsub_rn(other_v, self_v) : __fadd_rn(self_v, other_v);
+        }
+    }
+    return a[0];
+}
+__device__ __forceinline__ float lc_fwht_value(float v, float *sh, unsigned d, unsigned t) {
+#pragma unroll
+    for (unsigned len = 1; len < 32; len <<= 1) {
+        const float other_v = __shfl_xor_sync(0xffffffffu, v, len);
+        v = (t & len) ? __fsub_rn(other_v, v) : __fadd_rn(v, other_v);
+    }
+    switch (d) {
+        case 64: return lc_fwht_cross_warp<2>(v, sh, t);
+        case 128: return lc_fwht_cross_warp<4>(v, sh, t);
+        case 256: return lc_fwht_cross_warp<8>(v, sh, t);
+        case 512: return lc_fwht_cross_warp<16>(v, sh, t);
+        default: return v;   // d == 32
+    }
+}
 #endif
 
 // The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of a kernel.  One

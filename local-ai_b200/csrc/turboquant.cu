@@ -29,29 +29,6 @@ __device__ __forceinline__ unsigned tq_unpack(const uint8_t *codes, unsigned d, 
     return (v >> shift) & ((1u << bits) - 1u);
 }
 
-// Unnormalised in-place FWHT over sh[0..d), one element per thread.
-// Pair (j, j+len): new[j] = a+b, new[j+len] = a-b.
-// The strides below 32 pair elements of one warp: they run as shuffles on the thread's own value (the same
-// operands in the same order as the shared-memory form, so the result is bit-identical); only the strides from 32
-// up go through shared memory.  d is a power of two >= 32, every thread of the block calls.
-__device__ __forceinline__ void fwht_block(float *sh, unsigned d, unsigned t) {
-    __syncthreads();   // sh[t] was written by its owner; nobody reads it before this point
-    float v = sh[t];
-#pragma unroll
-    for (unsigned len = 1; len < 32; len <<= 1) {
-        const float other_v = __shfl_xor_sync(0xffffffffu, v, len);
-        v = (t & len) ? __fsub_rn(other_v, v) : __fadd_rn(v, other_v);
-    }
-    sh[t] = v;
-    for (unsigned len = 32; len < d; len <<= 1) {
-        __syncthreads();
-        const float self_v = sh[t], other_v = sh[t ^ len];
-        __syncthreads();
-        sh[t] = (t & len) ? __fsub_rn(other_v, self_v) : __fadd_rn(self_v, other_v);
-    }
-    __syncthreads();
-}
-
 // One CTA of `hd` threads per (token|lane, kv head) row.
 //   slot rule, single sequence (BATCHED == false), dequantize_kv.metal:236-244:
 //     ring ? ((position + tok) % ring) * n_kv + head : (position + tok) * n_kv + head
@@ -93,10 +70,9 @@ __device__ __forceinline__ void encode_row(float xv, unsigned t, unsigned hd, un
     float v = xv;
     if (norm > 0.f) v = __fmul_rn(xv, __fdiv_rn(1.0f, norm));
     else if (norm_mode == 1) v = __fmul_rn(xv, 0.f);
-    sh[t] = __fmul_rn(v, signs[t]);
-    fwht_block(sh, hd, t);
+    const float rotated = lc_fwht_value(__fmul_rn(v, signs[t]), sh, hd, t);
     const float inv_sqrt_d = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-    const float y = __fmul_rn(sh[t], inv_sqrt_d);
+    const float y = __fmul_rn(rotated, inv_sqrt_d);
 
     const unsigned k = 1u << bits;
     unsigned best = 0;
@@ -105,10 +81,19 @@ __device__ __forceinline__ void encode_row(float xv, unsigned t, unsigned hd, un
         const float dd = fabsf(__fsub_rn(y, levels[i]));
         if (dd < bd) { bd = dd; best = i; }
     }
-    code_sh[t] = best;
     if (t == 0) *norm_out = __float2half_rn(norm);
+    // LSB-first packing: code i of the row sits at bit i * bits
+    if (bits != 3) {
+        // 2- and 4-bit codes never straddle a byte: the 8 / bits neighbouring lanes of a warp OR their codes together
+        const unsigned per = 8 / bits;
+        unsigned byte_val = best << (bits * (t & (per - 1)));
+        for (unsigned o = 1; o < per; o <<= 1) byte_val |= __shfl_xor_sync(0xffffffffu, byte_val, o);
+        if ((t & (per - 1)) == 0) packed_row[t / per] = (uint8_t)byte_val;
+        return;
+    }
+    code_sh[t] = best;
     __syncthreads();
-    // LSB-first packing, one thread per output byte.
+    // one thread per output byte
     if (t < code_bytes) {
         unsigned byte_val = 0;
         for (unsigned bp = 0; bp < 8; bp++) {
@@ -119,7 +104,6 @@ __device__ __forceinline__ void encode_row(float xv, unsigned t, unsigned hd, un
         }
         packed_row[t] = (uint8_t)byte_val;
     }
-    __syncthreads();
 }
 
 template <bool BATCHED>
@@ -209,7 +193,7 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
             const float c = cosf(ang), sn = sinf(ang);
             xr = __half2float(__float2half_rn(t < half ? x0 * c - x1 * sn : x0 * sn + x1 * c));
         }
-        __syncthreads();
+        // `sh` is next written two barriers further on (encode_row); the query path below uses `red` instead
     }
     if (role == 0) {
         qrow[t] = __float2half_rn(xr);
@@ -218,9 +202,8 @@ __global__ void kv_write_kernel(__half *q, const __half *__restrict__ q_norm_w, 
             // 256-point Walsh-Hadamard transform, softmax scale / sqrt(hd), split into an f16 and the f16 of the
             // remainder, stored in that kernel's fragment order (hd == 256 and heads in groups of 8: host-checked).
             // Same operations in the same order as the kernel's own prologue, so attention results do not change.
-            sh[t] = __fmul_rn(xr, signs[t]);
-            fwht_block(sh, hd, t);
-            const float v = __fmul_rn(sh[t], __fdiv_rn(q_scale, __fsqrt_rn((float)hd)));
+            const float rotated = lc_fwht_value(__fmul_rn(xr, signs[t]), red, hd, t);
+            const float v = __fmul_rn(rotated, __fdiv_rn(q_scale, __fsqrt_rn((float)hd)));
             const __half hi = __float2half_rn(v), lo = __float2half_rn(__fsub_rn(v, __half2float(hi)));
             const uint32_t own = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
             const uint32_t p1 = __shfl_down_sync(0xffffffffu, own, 1), p2 = __shfl_down_sync(0xffffffffu, own, 2),
@@ -263,11 +246,10 @@ __global__ void dequantize_kv_kernel(const uint8_t *__restrict__ packed, const _
         src = (token % ring) * n_kv + head;
     }
     const unsigned code_bytes = (hd * bits + 7) >> 3;
-    sh[t] = levels[tq_unpack(packed + src * code_bytes, t, bits)];
-    fwht_block(sh, hd, t);
+    const float rotated = lc_fwht_value(levels[tq_unpack(packed + src * code_bytes, t, bits)], sh, hd, t);
     const float inv_sqrt_d = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
     const float norm = __half2float(norms[src]);
-    output[g * hd + t] = __float2half_rn(sh[t] * inv_sqrt_d * signs[t] * norm);
+    output[g * hd + t] = __float2half_rn(rotated * inv_sqrt_d * signs[t] * norm);
 }
 
 __device__ __forceinline__ float ld_as_float(const float *p) { return *p; }
@@ -285,9 +267,7 @@ __global__ void hadamard_rotate_kernel(const TIn *__restrict__ input, const floa
     const unsigned t = threadIdx.x;
     const size_t base = (size_t)blockIdx.x * hd;
     const float x = ld_as_float(input + base + t);
-    sh[t] = pre ? x * signs[t] : x;
-    fwht_block(sh, hd, t);
-    float y = sh[t] * __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    float y = lc_fwht_value(pre ? x * signs[t] : x, sh, hd, t) * __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
     if (post) y *= signs[t];
     st_from_float(output + base + t, y);
 }
