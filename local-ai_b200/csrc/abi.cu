@@ -386,6 +386,7 @@ int lc_kernels_create(lc_ctx *ctx, lc_kernels **out) {
     k->mma = env_enabled("LOCAL_AI_MMA");
     k->decode_mma = env_enabled("LOCAL_CUDA_DECODE_MMA");
     k->decode_tc = env_enabled("LOCAL_CUDA_DECODE_TC");
+    k->vocab_tc = env_enabled("LOCAL_CUDA_VOCAB_TC");
     if (const char *e = getenv("LOCAL_CUDA_SMALL_M")) {
         const long v = strtol(e, nullptr, 10);
         if (v >= 0 && v <= 8) k->small_m = (uint32_t)v;

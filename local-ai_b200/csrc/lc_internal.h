@@ -52,6 +52,7 @@ struct lc_kernels {
     bool mma = true;     // LOCAL_AI_MMA: tensor-core path for larger M
     bool decode_tc = true;   // LOCAL_CUDA_DECODE_TC: lean tcgen05 kernel for TQ2_0 at small_m < M <= 64
     uint32_t small_m = 0;    // LOCAL_CUDA_SMALL_M (0..8): TQ2_0 matmuls of up to this many rows keep the CUDA-core kernel
+    bool vocab_tc = true;    // LOCAL_CUDA_VOCAB_TC: persistent tcgen05 kernel for very tall Q4_0 matrices, f32 out, M <= 64
     bool decode_mma = true;  // LOCAL_CUDA_DECODE_MMA: register-direct mma.sync path for 8 < M <= 64 (0: tcgen05 there too)
     int kv_norm_mode = 0;  // LOCAL_CUDA_TQ_NORM: 0 sequential (Rust codec order), 1 tree (Metal order)
     // Library-owned scratch for split-K partials (grown outside graph capture).

@@ -35,6 +35,11 @@ int lc_qgemm_mma_grouped(int fmt, bool f32out, lc_kernels *k, lc_batch *b, const
 int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng, const lc_buf *const *weights,
                         lc_buf *const *outputs, const uint32_t *ns, uint32_t m, uint32_t kk, bool geglu);
 
+// qmatmul_tcv.cu: persistent tcgen05 kernel for very tall Q4_0 matrices (the vocabulary projection), f32 out, m <= 64;
+// same return contract.
+int lc_qgemm_tcv_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight, lc_buf *output, uint32_t m,
+                        uint32_t kk, uint32_t n);
+
 static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch *b, const lc_buf *input,
                  const lc_buf *weight, lc_buf *output, uint32_t m, uint32_t kk, uint32_t n) {
     int st = lc_check_qargs(fmt, name, k, b, weight, input, output, m, kk, n, f32out ? 4 : 2);
@@ -45,6 +50,10 @@ static int route(int fmt, bool f32out, const char *name, lc_kernels *k, lc_batch
     const uint32_t ns[1] = {n};
     if (k->mma && k->decode_tc && fmt == 1 && !f32out && m > k->small_m && m <= 64) {
         st = lc_qgemm_tcd_launch(k, b, input, 1, ws, os, ns, m, kk, false);
+        if (st >= 0) return st;
+    }
+    if (k->mma && k->vocab_tc && fmt == 0 && f32out && m > 8 && m <= 64) {
+        st = lc_qgemm_tcv_launch(k, b, input, weight, output, m, kk, n);
         if (st >= 0) return st;
     }
     if (k->mma && m > 8) {

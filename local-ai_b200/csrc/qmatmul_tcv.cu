@@ -1,0 +1,356 @@
+// tcgen05 matmul for very tall Q4_0 matrices at decode batch sizes: C[m, n] = A[m, K] (f16) x W[n, K]^T, m <= 64,
+// f32 out, n of the order of a vocabulary.  Stands in for the reference's matmul_nt_q4_0 dispatch on the tied
+// embedding table (local-engine/src/pipeline/batched.rs:330-352 calls it once per step for all lanes).
+//
+// One persistent CTA per SM walks 128-row tiles of the table.  Per tile and 128 k ("step"):
+//   * a loader thread brings the raw blocks in with TMA: the table is a byte matrix [n][K / 32 * 18], and 256 k of
+//     128 rows are one box of 144 bytes x 128 rows (a ring of four boxes; 144 = 9 x 16, so every box starts on a
+//     16-byte boundary as the copy engine requires; rows past n read as zero blocks);
+//   * eight warps dequantize: thread r of a lane quarter owns operand row r and, per step, two of its four blocks.
+//     A Q4_0 weight d (q - 8) needs up to 15 significant bits, so it is written to tensor memory as two f16 operands,
+//     hi = f16(d (q - 8)) and lo = d (q - 8) - hi (one fused multiply-add, exact): the sum of the two MMAs is the
+//     f32-accumulated product with the exact weight, the contract of the register-direct kernel (qmatmul_mma.cu)
+//     that this one replaces for large n;
+//   * a second loader thread brings the step's activations (two 64-k boxes, 128-byte swizzle) from L2;
+//   * four warps issue the MMAs, weights from tensor memory, activations from shared memory.  An MMA issue costs its
+//     thread about 210 cycles whatever the shape, issues of different warps overlap, so the 16 MMAs of a step (eight
+//     K = 16 slices x {hi, lo}) are spread over four issuers with one accumulator each;
+//   * four more warps read the accumulators back once a tile's last step completes, add the four partial sums in a
+//     fixed order and store f32 rows (a warp writes 32 consecutive rows of one batch column: 128 bytes); the issuers
+//     start the next tile's MMAs as soon as the loads have left tensor memory, while the dequantizing warps are
+//     already ahead by the two weight slots.
+// Tensor memory: 4 accumulators x 64 columns + 2 weight slots x (64 hi + 64 lo) columns = 512.
+//
+// Every wait on an mbarrier is bounded; on expiry the CTA raises the kernels object's status word, lets every role
+// run out, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "lc_internal.h"
+#include "tcgen05_util.cuh"
+
+namespace {
+
+constexpr int V_ROWS = 128;                 // weight rows per tile (UMMA M)
+constexpr int V_NB = 64;                    // batch columns (UMMA N)
+constexpr int V_KT = 64;                    // k per activation box (one 128-byte swizzled row)
+constexpr int V_STEP_K = 128;               // k per pipeline step
+constexpr int V_B_TILE = V_NB * V_KT * 2;   // 8 KB
+constexpr int V_B_SLOT = (V_STEP_K / V_KT) * V_B_TILE;   // 16 KB
+constexpr int V_SB = 4;                     // activation slots
+constexpr int V_CHUNK_K = 256;              // k per raw box: 8 blocks
+constexpr int V_BB = 18;                    // bytes per Q4_0 block
+constexpr int V_CHUNK_RB = V_CHUNK_K / 32 * V_BB;        // 144 bytes per row and box
+constexpr int V_RAW_SLOT = V_ROWS * V_CHUNK_RB;          // 18432
+constexpr int V_RS = 4;                     // raw slots
+constexpr int V_NISS = 4;                   // MMA-issuing warps, one accumulator each
+constexpr int V_SA = 2;                     // weight slots in tensor memory
+constexpr int V_A_COLS = 128;               // columns per weight slot: 64 hi | 64 lo
+constexpr int V_A_BASE = V_NISS * V_NB;     // 256
+constexpr int V_TMEM_COLS = V_A_BASE + V_SA * V_A_COLS;  // 512
+constexpr int V_NBAR = 8;                   // step-release barriers, one per step index mod 8
+constexpr int V_NDQ = 8, V_NEPI = 4;
+constexpr int V_NT = (V_NDQ + 2 + V_NISS + V_NEPI) * 32;   // 576
+constexpr uint32_t V_WAIT_LIMIT = 1u << 22;
+
+struct TcvParams {
+    float *out;
+    int n, m, K, tiles;
+    int *status;
+    uint32_t wait_limit;
+};
+
+// bounded wait by lane 0, result shared with the warp
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_t limit, int lane) {
+    uint32_t ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, limit) ? 1u : 0u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+
+__global__ void __launch_bounds__(V_NT, 1)
+qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CUtensorMap x_map,
+                 const __grid_constant__ CUtensorMap w_map) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *b_s = smem;                                   // [V_SB][V_B_SLOT]
+    uint8_t *raw = b_s + V_SB * V_B_SLOT;                  // [V_RS][V_RAW_SLOT]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(raw + V_RS * V_RAW_SLOT);
+    uint64_t *raw_full = bars;                             // [V_RS]   the box has landed
+    uint64_t *raw_empty = raw_full + V_RS;                 // [V_RS]   all dequantizing warps are done with it
+    uint64_t *a_full = raw_empty + V_RS;                   // [V_SA]   weights of a step are in tensor memory
+    uint64_t *b_full = a_full + V_SA;                      // [V_SB]   activations of a step have landed
+    uint64_t *step_done = b_full + V_SB;                   // [V_NBAR] the step's MMAs have completed
+    uint64_t *acc_empty = step_done + V_NBAR;              // [1]      the tile's accumulators have been read
+    uint64_t *acc_full = acc_empty + 1;                    // [1]      the tile's last MMAs have completed
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    lc_pdl_trigger();
+    const int S = p.K / V_STEP_K;                          // steps per tile (even: K is a multiple of 256)
+    const int my_tiles = ((int)p.tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total = my_tiles * S;                        // this CTA's steps, numbered across its tiles
+    auto tile_of = [&](int j) -> int { return (int)blockIdx.x + j * (int)gridDim.x; };
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)V_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    if (tid == 0) {
+        for (int i = 0; i < V_RS; i++) mbar_init(smem_u32(&raw_full[i]), 1);
+        for (int i = 0; i < V_RS; i++) mbar_init(smem_u32(&raw_empty[i]), V_NDQ);
+        for (int i = 0; i < V_SA; i++) mbar_init(smem_u32(&a_full[i]), V_NDQ);
+        for (int i = 0; i < V_SB; i++) mbar_init(smem_u32(&b_full[i]), 1);
+        for (int i = 0; i < V_NBAR; i++) mbar_init(smem_u32(&step_done[i]), V_NISS);
+        mbar_init(smem_u32(acc_empty), V_NEPI);
+        mbar_init(smem_u32(acc_full), V_NISS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(V_NB >> 3) << 17) | ((uint32_t)(V_ROWS >> 4) << 24);
+
+    if (warp < V_NDQ) {
+        // =========================== dequantizing warps ===========================
+        const int r = 32 * (warp & 3) + lane, bq = warp >> 2;
+        const uint32_t ta0 = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)V_A_BASE;
+        const __half2 c1032 = __float2half2_rn(1032.0f);
+        const uint32_t raw_a = smem_u32(raw) + (uint32_t)(r * V_CHUNK_RB + bq * 2 * V_BB);
+        bool dead = false;
+        for (int g = 0; g < total && !dead; g++) {
+            const int cg = g >> 1, rs = cg % V_RS, s = g % V_SA;
+            if ((g & 1) == 0 && !warp_wait(smem_u32(&raw_full[rs]), (uint32_t)((cg / V_RS) & 1), p.wait_limit, lane)) dead = true;
+            if (!dead && g >= V_SA) {   // the MMAs that read this weight slot two steps ago have completed
+                const int u = g - V_SA;
+                if (!warp_wait(smem_u32(&step_done[u % V_NBAR]), (uint32_t)((u / V_NBAR) & 1), p.wait_limit, lane)) dead = true;
+                tc_fence_after();
+            }
+            if (dead || *abort_flag) { *abort_flag = 1; dead = true; break; }
+#pragma unroll
+            for (int bi = 0; bi < 2; bi++) {
+                // block 4 (g & 1) + 2 bq + bi of the box: f16 scale, then 16 bytes of nibbles (2-byte aligned)
+                const uint32_t ba = raw_a + (uint32_t)(rs * V_RAW_SLOT + (g & 1) * 4 * V_BB + bi * V_BB);
+                const uint32_t dbits = lds16(ba);
+                const __half2 d2 = bits_h2(dbits | (dbits << 16));
+                const uint32_t ca = ba + 2, sh = (ca & 3u) * 8u, wa = ca & ~3u;
+                const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8), w3 = lds32(wa + 12), w4 = sh ? lds32(wa + 16) : 0u;
+                const uint32_t cw[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                                        __funnelshift_r(w3, w4, sh)};
+                // low nibbles are elements 0-15 of the block, high nibbles 16-31: eight columns (16 k) each
+                const uint32_t col = (uint32_t)(s * V_A_COLS + 16 * (2 * bq + bi));
+#pragma unroll
+                for (int part = 0; part < 2; part++) {
+                    uint32_t vh[8], vl[8];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const uint32_t codes = (cw[q] >> (4 * part)) & 0x0F0F0F0Fu;
+                        // bytes -> f16 1024 + q by byte placement under exponent 0x64, minus 1032 -> q - 8 (exact)
+                        const __half2 q01 = __hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032);
+                        const __half2 q23 = __hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032);
+                        const __half2 h01 = __hmul2(q01, d2), h23 = __hmul2(q23, d2);
+                        vh[2 * q] = h2_bits(h01);
+                        vh[2 * q + 1] = h2_bits(h23);
+                        vl[2 * q] = h2_bits(__hfma2(q01, d2, __hneg2(h01)));
+                        vl[2 * q + 1] = h2_bits(__hfma2(q23, d2, __hneg2(h23)));
+                    }
+                    tmem_st8(ta0 + col + (uint32_t)(8 * part), vh);
+                    tmem_st8(ta0 + col + (uint32_t)(64 + 8 * part), vl);
+                }
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&a_full[s]));
+                if (g & 1) mbar_arrive(smem_u32(&raw_empty[rs]));   // both steps of the box are in tensor memory
+            }
+        }
+    } else if (warp == V_NDQ) {
+        // =========================== activation loader (one thread) ===========================
+        if (lane == 0) {
+            lc_pdl_wait();   // the activations are the predecessor's output
+            bool dead = false;
+            for (int g = 0; g < total && !dead; g++) {
+                if (g >= V_SB) {   // its slot was last read by the MMAs of step g - V_SB
+                    const int u = g - V_SB;
+                    if (!mbar_wait(smem_u32(&step_done[u % V_NBAR]), (uint32_t)((u / V_NBAR) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+                }
+                const int k0 = (g % S) * V_STEP_K;
+                const uint32_t bar = smem_u32(&b_full[g % V_SB]), dst = smem_u32(b_s) + (uint32_t)((g % V_SB) * V_B_SLOT);
+                mbar_expect_tx(bar, (uint32_t)V_B_SLOT);
+                tma_load_2d(dst, &x_map, k0, 0, bar);
+                tma_load_2d(dst + V_B_TILE, &x_map, k0 + V_KT, 0, bar);
+            }
+            if (dead) *abort_flag = 1;
+        }
+        __syncwarp();
+    } else if (warp == V_NDQ + 1) {
+        // =========================== raw block loader (one thread); the table does not depend on the predecessor ====
+        if (lane == 0) {
+            bool dead = false;
+            const int chunks = total >> 1, cpt = S >> 1;
+            for (int cg = 0; cg < chunks && !dead; cg++) {
+                const int rs = cg % V_RS;
+                if (cg >= V_RS) {   // the box that held this slot has been dequantized
+                    if (!mbar_wait(smem_u32(&raw_empty[rs]), (uint32_t)((cg / V_RS - 1) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+                }
+                const int tile = tile_of(cg / cpt), c = cg % cpt;
+                const uint32_t bar = smem_u32(&raw_full[rs]);
+                mbar_expect_tx(bar, (uint32_t)V_RAW_SLOT);
+                tma_load_2d(smem_u32(raw) + (uint32_t)(rs * V_RAW_SLOT), &w_map, c * V_CHUNK_RB, tile * V_ROWS, bar);
+            }
+            if (dead) *abort_flag = 1;
+        }
+        __syncwarp();
+    } else if (warp < V_NDQ + 2 + V_NISS) {
+        // =========================== MMA issue (four warps, one thread each) ===========================
+        // Issuer iw owns accumulator iw and takes the K = 16 slices iw and iw + 4 of every step, hi then lo.
+        const int iw = warp - V_NDQ - 2;
+        if (lane == 0) {
+            const uint64_t bdesc0 = make_desc(smem_u32(b_s));
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(iw * V_NB);
+            bool dead = false;
+            for (int g = 0; g < total && !dead; g++) {
+                const int i = g % S;
+                if (i == 0 && g > 0) {   // the previous tile's sums have left tensor memory
+                    if (!mbar_wait(smem_u32(acc_empty), (uint32_t)((g / S - 1) & 1), p.wait_limit)) { dead = true; break; }
+                }
+                if (!mbar_wait(smem_u32(&a_full[g % V_SA]), (uint32_t)((g / V_SA) & 1), p.wait_limit) ||
+                    !mbar_wait(smem_u32(&b_full[g % V_SB]), (uint32_t)((g / V_SB) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const int ks = iw + 4 * q;   // slice 0..7: box ks / 4, 32 bytes per slice inside its 128-byte rows
+                    const uint32_t ta = tmem_base + (uint32_t)(V_A_BASE + (g % V_SA) * V_A_COLS + 8 * ks);
+                    const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)((g % V_SB) * V_B_SLOT + (ks >> 2) * V_B_TILE + (ks & 3) * 32) >> 4);
+                    umma_f16_ta(tmem_acc, ta, bd, idesc, (i > 0 || q > 0) ? 1u : 0u);
+                    umma_f16_ta(tmem_acc, ta + 64u, bd, idesc, 1u);
+                }
+                umma_commit(smem_u32(&step_done[g % V_NBAR]));
+                // A waiter on a phase must have seen the phase before it complete; the result warps look only once
+                // per tile, so they get a barrier of their own rather than the step ring.
+                if (i == S - 1) umma_commit(smem_u32(acc_full));
+            }
+            if (dead) *abort_flag = 1;
+        }
+        __syncwarp();
+    } else {
+        // =========================== results (four warps, one per lane quarter) ===========================
+        const int qtr = warp & 3;
+        bool dead = false;
+        for (int j = 0; j < my_tiles && !dead; j++) {
+            if (!warp_wait(smem_u32(acc_full), (uint32_t)(j & 1), p.wait_limit, lane) || *abort_flag) { dead = true; break; }
+            tc_fence_after();
+            const int row = tile_of(j) * V_ROWS + 32 * qtr + lane;
+            const uint32_t ta = tmem_base + ((uint32_t)(32 * qtr) << 16);
+#pragma unroll
+            for (int cc = 0; cc < V_NB; cc += 16) {
+                uint32_t a0[16], a1[16], a2[16], a3[16];
+                tmem_ld16(ta + (uint32_t)cc, a0);
+                tmem_ld16(ta + (uint32_t)(cc + V_NB), a1);
+                tmem_ld16(ta + (uint32_t)(cc + 2 * V_NB), a2);
+                tmem_ld16(ta + (uint32_t)(cc + 3 * V_NB), a3);
+                tmem_ld_wait();
+                if (cc + 16 == V_NB) {   // everything has been read: the next tile's MMAs may overwrite
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+                }
+                if (row < p.n) {
+#pragma unroll
+                    for (int e = 0; e < 16; e++)
+                        if (cc + e < p.m)
+                            p.out[(size_t)(cc + e) * p.n + row] =
+                                (__uint_as_float(a0[e]) + __uint_as_float(a1[e])) + (__uint_as_float(a2[e]) + __uint_as_float(a3[e]));
+                }
+            }
+        }
+        if (dead) *abort_flag = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (*abort_flag != 0 && tid == 0) atomicExch(p.status, LC_DEV_STATUS_WAIT_EXPIRED_TCD);
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)V_TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_tiled_fn encode_tiled() {
+    static encode_tiled_fn fn = []() -> encode_tiled_fn {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<encode_tiled_fn>(ptr);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+// One Q4_0 matrix [n, kk] against activations [m, kk], m <= 64, f32 out.  Returns LC_OK after a launch, a positive
+// status on error, or -1 when the shape is outside what this kernel covers (the caller then uses another path).
+int lc_qgemm_tcv_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, const lc_buf *weight, lc_buf *output, uint32_t m,
+                        uint32_t kk, uint32_t n) {
+    if (m < 1 || m > (uint32_t)V_NB || kk % V_CHUNK_K != 0 || kk == 0 || !lc_aligned(input->dptr, 16) ||
+        !lc_aligned(weight->dptr, 16) || !lc_aligned(output->dptr, 4))
+        return -1;
+    // worth it only when every SM gets tiles to walk; smaller matrices stay with the split-K kernels
+    if (n < (uint32_t)(V_ROWS * k->ctx->sm_count)) return -1;
+    const size_t smem = (size_t)V_SB * V_B_SLOT + (size_t)V_RS * V_RAW_SLOT + (2 * V_RS + V_SA + V_SB + V_NBAR + 2) * 8 + 16 + 1024;
+    if (smem > k->ctx->smem_optin) return -1;
+    encode_tiled_fn fn = encode_tiled();
+    if (!fn) return -1;
+    CUtensorMap x_map, w_map;
+    {
+        const cuuint64_t dims[2] = {kk, m};
+        const cuuint64_t strides[1] = {(cuuint64_t)kk * 2};
+        const cuuint32_t box[2] = {V_KT, V_NB};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = fn(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, input->dptr, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return lc_fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled (activations) failed (%d)", (int)r);
+    }
+    {
+        const cuuint64_t rb = (cuuint64_t)(kk / 32) * V_BB;   // a multiple of 144
+        const cuuint64_t dims[2] = {rb, n};
+        const cuuint64_t strides[1] = {rb};
+        const cuuint32_t box[2] = {V_CHUNK_RB, V_ROWS};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = fn(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight->dptr, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return lc_fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (%d)", (int)r);
+    }
+    TcvParams p;
+    p.out = (float *)output->dptr;
+    p.n = (int)n;
+    p.m = (int)m;
+    p.K = (int)kk;
+    p.tiles = (int)((n + V_ROWS - 1) / V_ROWS);
+    p.status = k->dev_status;
+    p.wait_limit = V_WAIT_LIMIT;
+    static lc_smem_optin optin;
+    LC_CUDA_TRY(lc_ensure_smem(qgemm_tcv_kernel, optin, b->ctx, smem));
+    const int grid = p.tiles < k->ctx->sm_count ? p.tiles : k->ctx->sm_count;
+    LC_LAUNCH_CHECKED(lc_launch(qgemm_tcv_kernel, dim3(grid), dim3(V_NT), smem, b, p, x_map, w_map));
+    b->dispatch_count++;
+    return LC_OK;
+}
