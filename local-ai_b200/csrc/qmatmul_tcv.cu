@@ -49,8 +49,8 @@ constexpr int V_A_COLS = 128;               // columns per weight slot: 64 hi | 
 constexpr int V_A_BASE = V_NISS * V_NB;     // 256
 constexpr int V_TMEM_COLS = V_A_BASE + V_SA * V_A_COLS;  // 512
 constexpr int V_NBAR = 8;                   // step-release barriers, one per step index mod 8
-constexpr int V_NDQ = 8, V_NEPI = 4;
-constexpr int V_NT = (V_NDQ + 2 + V_NISS + V_NEPI) * 32;   // 576
+constexpr int V_NDQ = 16, V_NDQ_STEP = 8, V_NEPI = 4;   // dequantizing warps in all / per step
+constexpr int V_NT = (V_NDQ + 2 + V_NISS + V_NEPI) * 32;   // 832
 constexpr uint32_t V_WAIT_LIMIT = 1u << 22;
 
 struct TcvParams {
@@ -84,9 +84,8 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
     uint64_t *bars = reinterpret_cast<uint64_t *>(raw + V_RS * V_RAW_SLOT);
     uint64_t *raw_full = bars;                             // [V_RS]   the box has landed
     uint64_t *raw_empty = raw_full + V_RS;                 // [V_RS]   all dequantizing warps are done with it
-    uint64_t *a_full = raw_empty + V_RS;                   // [V_SA]   weights of a step are in tensor memory
-    uint64_t *b_full = a_full + V_SA;                      // [V_SB]   activations of a step have landed
-    uint64_t *step_done = b_full + V_SB;                   // [V_NBAR] the step's MMAs have completed
+    uint64_t *ab_full = raw_empty + V_RS;                  // [V_SB]   a step's weights are in tensor memory and its activations have landed
+    uint64_t *step_done = ab_full + V_SB;                   // [V_NBAR] the step's MMAs have completed
     uint64_t *acc_empty = step_done + V_NBAR;              // [1]      the tile's accumulators have been read
     uint64_t *acc_full = acc_empty + 1;                    // [1]      the tile's last MMAs have completed
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
@@ -108,8 +107,10 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
     if (tid == 0) {
         for (int i = 0; i < V_RS; i++) mbar_init(smem_u32(&raw_full[i]), 1);
         for (int i = 0; i < V_RS; i++) mbar_init(smem_u32(&raw_empty[i]), V_NDQ);
-        for (int i = 0; i < V_SA; i++) mbar_init(smem_u32(&a_full[i]), V_NDQ);
-        for (int i = 0; i < V_SB; i++) mbar_init(smem_u32(&b_full[i]), 1);
+        // one barrier per step for both operands, so the issuers test one: eight dequantizing warps arrive, and the
+        // activation loader arrives with the byte count of its boxes.  The ring has the depth of the activation ring,
+        // the deeper of the two, so no arrival for a later step can reach a barrier before its current phase is over.
+        for (int i = 0; i < V_SB; i++) mbar_init(smem_u32(&ab_full[i]), V_NDQ_STEP + 1);
         for (int i = 0; i < V_NBAR; i++) mbar_init(smem_u32(&step_done[i]), V_NISS);
         mbar_init(smem_u32(acc_empty), V_NEPI);
         mbar_init(smem_u32(acc_full), V_NISS);
@@ -124,35 +125,32 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
 
     if (warp < V_NDQ) {
         // =========================== dequantizing warps ===========================
-        const int r = 32 * (warp & 3) + lane, bq = warp >> 2;
-        const uint32_t ta0 = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)V_A_BASE;
+        // Two groups of eight warps take alternate steps, group `grp` always into weight slot `grp`: what a warp
+        // does per step besides arithmetic (two barrier tests, stores into tensor memory and the wait for them, an
+        // arrival) takes longer than the MMAs of a step, so one group alone cannot keep the issuers busy.
+        const int grp = warp >> 3, wq = warp & 7;
+        const int r = 32 * (wq & 3) + lane, bq = wq >> 2;
+        const uint32_t ta0 = tmem_base + ((uint32_t)(32 * (wq & 3)) << 16) + (uint32_t)(V_A_BASE + grp * V_A_COLS);
         const __half2 c1032 = __float2half2_rn(1032.0f);
-        const uint32_t raw_a = smem_u32(raw) + (uint32_t)(r * V_CHUNK_RB + bq * 2 * V_BB);
+        const uint32_t raw_a = smem_u32(raw) + (uint32_t)(r * V_CHUNK_RB + grp * 4 * V_BB + bq * 2 * V_BB);
         bool dead = false;
-        for (int g = 0; g < total && !dead; g++) {
-            const int cg = g >> 1, rs = cg % V_RS, s = g % V_SA;
-            if ((g & 1) == 0 && !warp_wait(smem_u32(&raw_full[rs]), (uint32_t)((cg / V_RS) & 1), p.wait_limit, lane)) dead = true;
-            if (!dead && g >= V_SA) {   // the MMAs that read this weight slot two steps ago have completed
-                const int u = g - V_SA;
-                if (!warp_wait(smem_u32(&step_done[u % V_NBAR]), (uint32_t)((u / V_NBAR) & 1), p.wait_limit, lane)) dead = true;
-                tc_fence_after();
-            }
-            if (dead || *abort_flag) { *abort_flag = 1; dead = true; break; }
+        for (int g = grp; g < total && !dead; g += 2) {
+            const int cg = g >> 1, rs = cg % V_RS;
+            if (!warp_wait(smem_u32(&raw_full[rs]), (uint32_t)((cg / V_RS) & 1), p.wait_limit, lane) || *abort_flag) { *abort_flag = 1; dead = true; break; }
 #pragma unroll
             for (int bi = 0; bi < 2; bi++) {
-                // block 4 (g & 1) + 2 bq + bi of the box: f16 scale, then 16 bytes of nibbles (2-byte aligned)
-                const uint32_t ba = raw_a + (uint32_t)(rs * V_RAW_SLOT + (g & 1) * 4 * V_BB + bi * V_BB);
+                // block 4 grp + 2 bq + bi of the box: f16 scale, then 16 bytes of nibbles (2-byte aligned)
+                const uint32_t ba = raw_a + (uint32_t)(rs * V_RAW_SLOT + bi * V_BB);
                 const uint32_t dbits = lds16(ba);
                 const __half2 d2 = bits_h2(dbits | (dbits << 16));
                 const uint32_t ca = ba + 2, sh = (ca & 3u) * 8u, wa = ca & ~3u;
                 const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8), w3 = lds32(wa + 12), w4 = sh ? lds32(wa + 16) : 0u;
                 const uint32_t cw[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
                                         __funnelshift_r(w3, w4, sh)};
-                // low nibbles are elements 0-15 of the block, high nibbles 16-31: eight columns (16 k) each
-                const uint32_t col = (uint32_t)(s * V_A_COLS + 16 * (2 * bq + bi));
+                // low nibbles are elements 0-15 of the block (columns 0-7), high nibbles 16-31 (columns 8-15)
+                uint32_t vh[16], vl[16];
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
-                    uint32_t vh[8], vl[8];
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const uint32_t codes = (cw[q] >> (4 * part)) & 0x0F0F0F0Fu;
@@ -160,38 +158,50 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
                         const __half2 q01 = __hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4140)), c1032);
                         const __half2 q23 = __hsub2(bits_h2(__byte_perm(codes, 0x64u, 0x4342)), c1032);
                         const __half2 h01 = __hmul2(q01, d2), h23 = __hmul2(q23, d2);
-                        vh[2 * q] = h2_bits(h01);
-                        vh[2 * q + 1] = h2_bits(h23);
-                        vl[2 * q] = h2_bits(__hfma2(q01, d2, __hneg2(h01)));
-                        vl[2 * q + 1] = h2_bits(__hfma2(q23, d2, __hneg2(h23)));
+                        vh[8 * part + 2 * q] = h2_bits(h01);
+                        vh[8 * part + 2 * q + 1] = h2_bits(h23);
+                        vl[8 * part + 2 * q] = h2_bits(__hfma2(q01, d2, __hneg2(h01)));
+                        vl[8 * part + 2 * q + 1] = h2_bits(__hfma2(q23, d2, __hneg2(h23)));
                     }
-                    tmem_st8(ta0 + col + (uint32_t)(8 * part), vh);
-                    tmem_st8(ta0 + col + (uint32_t)(64 + 8 * part), vl);
                 }
+                if (bi == 0 && g >= V_SA) {
+                    // the first block is in registers; the stores have to wait for the MMAs that read this slot two steps ago
+                    const int u = g - V_SA;
+                    if (!warp_wait(smem_u32(&step_done[u % V_NBAR]), (uint32_t)((u / V_NBAR) & 1), p.wait_limit, lane)) { *abort_flag = 1; dead = true; break; }
+                    tc_fence_after();
+                }
+                if (bi == 1) {   // every lane of this warp has read its bytes of the box
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+                }
+                const uint32_t col = (uint32_t)(16 * (2 * bq + bi));
+                tmem_st16(ta0 + col, vh);
+                tmem_st16(ta0 + col + 64u, vl);
             }
+            if (dead) break;
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&a_full[s]));
-                if (g & 1) mbar_arrive(smem_u32(&raw_empty[rs]));   // both steps of the box are in tensor memory
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&ab_full[g % V_SB]));
         }
     } else if (warp == V_NDQ) {
         // =========================== activation loader (one thread) ===========================
         if (lane == 0) {
             lc_pdl_wait();   // the activations are the predecessor's output
             bool dead = false;
-            for (int g = 0; g < total && !dead; g++) {
-                if (g >= V_SB) {   // its slot was last read by the MMAs of step g - V_SB
-                    const int u = g - V_SB;
-                    if (!mbar_wait(smem_u32(&step_done[u % V_NBAR]), (uint32_t)((u / V_NBAR) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+            int g = 0;
+            for (int j = 0; j < my_tiles && !dead; j++) {
+                for (int i = 0; i < S; i++, g++) {
+                    if (g >= V_SB) {   // its slot was last read by the MMAs of step g - V_SB
+                        const int u = g - V_SB;
+                        if (!mbar_wait(smem_u32(&step_done[u % V_NBAR]), (uint32_t)((u / V_NBAR) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+                    }
+                    const int k0 = i * V_STEP_K;
+                    const uint32_t bar = smem_u32(&ab_full[g % V_SB]), dst = smem_u32(b_s) + (uint32_t)((g % V_SB) * V_B_SLOT);
+                    mbar_expect_tx(bar, (uint32_t)V_B_SLOT);
+                    tma_load_2d(dst, &x_map, k0, 0, bar);
+                    tma_load_2d(dst + V_B_TILE, &x_map, k0 + V_KT, 0, bar);
                 }
-                const int k0 = (g % S) * V_STEP_K;
-                const uint32_t bar = smem_u32(&b_full[g % V_SB]), dst = smem_u32(b_s) + (uint32_t)((g % V_SB) * V_B_SLOT);
-                mbar_expect_tx(bar, (uint32_t)V_B_SLOT);
-                tma_load_2d(dst, &x_map, k0, 0, bar);
-                tma_load_2d(dst + V_B_TILE, &x_map, k0 + V_KT, 0, bar);
             }
             if (dead) *abort_flag = 1;
         }
@@ -200,48 +210,56 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
         // =========================== raw block loader (one thread); the table does not depend on the predecessor ====
         if (lane == 0) {
             bool dead = false;
-            const int chunks = total >> 1, cpt = S >> 1;
-            for (int cg = 0; cg < chunks && !dead; cg++) {
-                const int rs = cg % V_RS;
-                if (cg >= V_RS) {   // the box that held this slot has been dequantized
-                    if (!mbar_wait(smem_u32(&raw_empty[rs]), (uint32_t)((cg / V_RS - 1) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+            const int cpt = S >> 1;
+            int cg = 0;
+            for (int j = 0; j < my_tiles && !dead; j++) {
+                const int row0 = tile_of(j) * V_ROWS;
+                for (int c = 0; c < cpt; c++, cg++) {
+                    const int rs = cg % V_RS;
+                    if (cg >= V_RS) {   // the box that held this slot has been dequantized
+                        if (!mbar_wait(smem_u32(&raw_empty[rs]), (uint32_t)((cg / V_RS - 1) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+                    }
+                    const uint32_t bar = smem_u32(&raw_full[rs]);
+                    mbar_expect_tx(bar, (uint32_t)V_RAW_SLOT);
+                    tma_load_2d(smem_u32(raw) + (uint32_t)(rs * V_RAW_SLOT), &w_map, c * V_CHUNK_RB, row0, bar);
                 }
-                const int tile = tile_of(cg / cpt), c = cg % cpt;
-                const uint32_t bar = smem_u32(&raw_full[rs]);
-                mbar_expect_tx(bar, (uint32_t)V_RAW_SLOT);
-                tma_load_2d(smem_u32(raw) + (uint32_t)(rs * V_RAW_SLOT), &w_map, c * V_CHUNK_RB, tile * V_ROWS, bar);
             }
             if (dead) *abort_flag = 1;
         }
         __syncwarp();
     } else if (warp < V_NDQ + 2 + V_NISS) {
         // =========================== MMA issue (four warps, one thread each) ===========================
-        // Issuer iw owns accumulator iw and takes the K = 16 slices iw and iw + 4 of every step, hi then lo.
+        // Issuer iw owns accumulator iw and takes the K = 16 slices iw and iw + 4 of every step, hi then lo
+        // (slice ks: weight columns 8 ks of the hi half, + 64 for lo; activations: box ks / 4, 32 bytes per slice).
         const int iw = warp - V_NDQ - 2;
         if (lane == 0) {
-            const uint64_t bdesc0 = make_desc(smem_u32(b_s));
+            // This loop is the pace of the whole kernel and runs on one thread: nothing in it but the barrier test, the
+            // MMAs and the commits (counters instead of divisions; a role that gives up stops arriving, so this
+            // thread's own bounded waits are its only failure path).
+            const uint64_t bdesc0 = make_desc(smem_u32(b_s) + (uint32_t)((iw & 3) * 32));   // slice iw of the first box
+            const uint64_t bdesc1 = bdesc0 + (uint64_t)((uint32_t)V_B_TILE >> 4);              // slice iw + 4: second box
             const uint32_t tmem_acc = tmem_base + (uint32_t)(iw * V_NB);
+            const uint32_t ta_first = tmem_base + (uint32_t)(V_A_BASE + 8 * iw);
+            const uint32_t ab0 = smem_u32(ab_full), sd0 = smem_u32(step_done);
             bool dead = false;
-            for (int g = 0; g < total && !dead; g++) {
-                const int i = g % S;
-                if (i == 0 && g > 0) {   // the previous tile's sums have left tensor memory
-                    if (!mbar_wait(smem_u32(acc_empty), (uint32_t)((g / S - 1) & 1), p.wait_limit)) { dead = true; break; }
+            uint32_t g = 0;
+            for (int j = 0; j < my_tiles && !dead; j++) {
+                if (j > 0 && !mbar_wait(smem_u32(acc_empty), (uint32_t)((j - 1) & 1), p.wait_limit)) { dead = true; break; }   // the previous tile's sums have left tensor memory
+                for (int i = 0; i < S; i++, g++) {
+                    const uint32_t sb = g & (V_SB - 1);
+                    if (!mbar_wait(ab0 + 8u * sb, (g / V_SB) & 1u, p.wait_limit)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t ta = ta_first + (g & (V_SA - 1)) * (uint32_t)V_A_COLS;
+                    const uint64_t boff = (uint64_t)((sb * (uint32_t)V_B_SLOT) >> 4);
+                    umma_f16_ta(tmem_acc, ta, bdesc0 + boff, idesc, i > 0 ? 1u : 0u);
+                    umma_f16_ta(tmem_acc, ta + 64u, bdesc0 + boff, idesc, 1u);
+                    umma_f16_ta(tmem_acc, ta + 32u, bdesc1 + boff, idesc, 1u);
+                    umma_f16_ta(tmem_acc, ta + 96u, bdesc1 + boff, idesc, 1u);
+                    umma_commit(sd0 + 8u * (g & (V_NBAR - 1)));
                 }
-                if (!mbar_wait(smem_u32(&a_full[g % V_SA]), (uint32_t)((g / V_SA) & 1), p.wait_limit) ||
-                    !mbar_wait(smem_u32(&b_full[g % V_SB]), (uint32_t)((g / V_SB) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    const int ks = iw + 4 * q;   // slice 0..7: box ks / 4, 32 bytes per slice inside its 128-byte rows
-                    const uint32_t ta = tmem_base + (uint32_t)(V_A_BASE + (g % V_SA) * V_A_COLS + 8 * ks);
-                    const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)((g % V_SB) * V_B_SLOT + (ks >> 2) * V_B_TILE + (ks & 3) * 32) >> 4);
-                    umma_f16_ta(tmem_acc, ta, bd, idesc, (i > 0 || q > 0) ? 1u : 0u);
-                    umma_f16_ta(tmem_acc, ta + 64u, bd, idesc, 1u);
-                }
-                umma_commit(smem_u32(&step_done[g % V_NBAR]));
                 // A waiter on a phase must have seen the phase before it complete; the result warps look only once
                 // per tile, so they get a barrier of their own rather than the step ring.
-                if (i == S - 1) umma_commit(smem_u32(acc_full));
+                if (!dead) umma_commit(smem_u32(acc_full));
             }
             if (dead) *abort_flag = 1;
         }
@@ -256,21 +274,21 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
             const int row = tile_of(j) * V_ROWS + 32 * qtr + lane;
             const uint32_t ta = tmem_base + ((uint32_t)(32 * qtr) << 16);
 #pragma unroll
-            for (int cc = 0; cc < V_NB; cc += 16) {
-                uint32_t a0[16], a1[16], a2[16], a3[16];
-                tmem_ld16(ta + (uint32_t)cc, a0);
-                tmem_ld16(ta + (uint32_t)(cc + V_NB), a1);
-                tmem_ld16(ta + (uint32_t)(cc + 2 * V_NB), a2);
-                tmem_ld16(ta + (uint32_t)(cc + 3 * V_NB), a3);
+            for (int cc = 0; cc < V_NB; cc += 8) {
+                uint32_t a0[8], a1[8], a2[8], a3[8];
+                tmem_ld8(ta + (uint32_t)cc, a0);
+                tmem_ld8(ta + (uint32_t)(cc + V_NB), a1);
+                tmem_ld8(ta + (uint32_t)(cc + 2 * V_NB), a2);
+                tmem_ld8(ta + (uint32_t)(cc + 3 * V_NB), a3);
                 tmem_ld_wait();
-                if (cc + 16 == V_NB) {   // everything has been read: the next tile's MMAs may overwrite
+                if (cc + 8 == V_NB) {   // everything has been read: the next tile's MMAs may overwrite
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(acc_empty));
                 }
                 if (row < p.n) {
 #pragma unroll
-                    for (int e = 0; e < 16; e++)
+                    for (int e = 0; e < 8; e++)
                         if (cc + e < p.m)
                             p.out[(size_t)(cc + e) * p.n + row] =
                                 (__uint_as_float(a0[e]) + __uint_as_float(a1[e])) + (__uint_as_float(a2[e]) + __uint_as_float(a3[e]));
@@ -313,7 +331,7 @@ int lc_qgemm_tcv_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, const l
         return -1;
     // worth it only when every SM gets tiles to walk; smaller matrices stay with the split-K kernels
     if (n < (uint32_t)(V_ROWS * k->ctx->sm_count)) return -1;
-    const size_t smem = (size_t)V_SB * V_B_SLOT + (size_t)V_RS * V_RAW_SLOT + (2 * V_RS + V_SA + V_SB + V_NBAR + 2) * 8 + 16 + 1024;
+    const size_t smem = (size_t)V_SB * V_B_SLOT + (size_t)V_RS * V_RAW_SLOT + (2 * V_RS + V_SB + V_NBAR + 2) * 8 + 16 + 1024;
     if (smem > k->ctx->smem_optin) return -1;
     encode_tiled_fn fn = encode_tiled();
     if (!fn) return -1;
