@@ -81,7 +81,8 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *b_s = smem;                                   // [V_SB][V_B_SLOT]
     uint8_t *raw = b_s + V_SB * V_B_SLOT;                  // [V_RS][V_RAW_SLOT]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(raw + V_RS * V_RAW_SLOT);
+    float *stage = reinterpret_cast<float *>(raw + V_RS * V_RAW_SLOT);   // [V_NB][V_ROWS] f32 sums of a tile
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stage + V_NB * V_ROWS);
     uint64_t *raw_full = bars;                             // [V_RS]   the box has landed
     uint64_t *raw_empty = raw_full + V_RS;                 // [V_RS]   all dequantizing warps are done with it
     uint64_t *ab_full = raw_empty + V_RS;                  // [V_SB]   a step's weights are in tensor memory and its activations have landed
@@ -271,8 +272,11 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
         for (int j = 0; j < my_tiles && !dead; j++) {
             if (!warp_wait(smem_u32(acc_full), (uint32_t)(j & 1), p.wait_limit, lane) || *abort_flag) { dead = true; break; }
             tc_fence_after();
-            const int row = tile_of(j) * V_ROWS + 32 * qtr + lane;
+            // The sums go to shared memory first (a warp writes 32 consecutive floats per batch column), so that the
+            // accumulators are handed back after the loads alone; the stores to global memory, 16 bytes per thread,
+            // then run beside the next tile's MMAs.  Every warp copies out what it staged itself.
             const uint32_t ta = tmem_base + ((uint32_t)(32 * qtr) << 16);
+            float *st_w = stage + 32 * qtr;
 #pragma unroll
             for (int cc = 0; cc < V_NB; cc += 8) {
                 uint32_t a0[8], a1[8], a2[8], a3[8];
@@ -286,14 +290,30 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(acc_empty));
                 }
-                if (row < p.n) {
 #pragma unroll
-                    for (int e = 0; e < 8; e++)
-                        if (cc + e < p.m)
-                            p.out[(size_t)(cc + e) * p.n + row] =
-                                (__uint_as_float(a0[e]) + __uint_as_float(a1[e])) + (__uint_as_float(a2[e]) + __uint_as_float(a3[e]));
+                for (int e = 0; e < 8; e++)
+                    st_w[(cc + e) * V_ROWS + lane] =
+                        (__uint_as_float(a0[e]) + __uint_as_float(a1[e])) + (__uint_as_float(a2[e]) + __uint_as_float(a3[e]));
+            }
+            __syncwarp();
+            const int row0 = tile_of(j) * V_ROWS + 32 * qtr, r4 = 4 * (lane & 7);
+            const bool vec = (p.n & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;   // every (column, 4-row group) then starts on a 16-byte boundary
+#pragma unroll 4
+            for (int c4 = 0; c4 < V_NB; c4 += 4) {
+                const int col = c4 + (lane >> 3);
+                if (col >= p.m) break;   // columns ascend with the lane: once a lane is past m, so are the later rounds
+                const float4 v = *reinterpret_cast<const float4 *>(st_w + col * V_ROWS + r4);
+                float *dst = p.out + (size_t)col * p.n + row0 + r4;
+                if (vec && row0 + r4 + 3 < p.n) {
+                    *reinterpret_cast<float4 *>(dst) = v;
+                } else {
+                    const float ev[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        if (row0 + r4 + q < p.n) dst[q] = ev[q];
                 }
             }
+            __syncwarp();   // the staging rows are free for the next tile
         }
         if (dead) *abort_flag = 1;
     }
@@ -331,7 +351,7 @@ int lc_qgemm_tcv_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, const l
         return -1;
     // worth it only when every SM gets tiles to walk; smaller matrices stay with the split-K kernels
     if (n < (uint32_t)(V_ROWS * k->ctx->sm_count)) return -1;
-    const size_t smem = (size_t)V_SB * V_B_SLOT + (size_t)V_RS * V_RAW_SLOT + (2 * V_RS + V_SB + V_NBAR + 2) * 8 + 16 + 1024;
+    const size_t smem = (size_t)V_SB * V_B_SLOT + (size_t)V_RS * V_RAW_SLOT + (size_t)V_NB * V_ROWS * 4 + (2 * V_RS + V_SB + V_NBAR + 2) * 8 + 16 + 1024;
     if (smem > k->ctx->smem_optin) return -1;
     encode_tiled_fn fn = encode_tiled();
     if (!fn) return -1;
