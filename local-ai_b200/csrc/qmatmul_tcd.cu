@@ -250,13 +250,15 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
         if (lane == 0) {
             lc_pdl_wait();   // the activations are the predecessor's output
             bool dead = false;
+            uint32_t sbi = 0;   // i % SB without the division
             for (int i = 0; i < total_steps && !dead; i++) {
                 if (i >= SB) {   // its slot was last read by the MMAs of step i - SB
                     const int u = i - SB;
                     if (!mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
                 }
                 const int k0 = (kbs + block_of(i)) * 256;
-                const uint32_t bar = smem_u32(&b_full[i % SB]), dst = smem_u32(b_s) + (uint32_t)((i % SB) * B_SLOT);
+                const uint32_t bar = smem_u32(&b_full[sbi]), dst = smem_u32(b_s) + sbi * (uint32_t)B_SLOT;
+                if (++sbi == (uint32_t)SB) sbi = 0;
                 mbar_expect_tx(bar, (uint32_t)B_SLOT);
 #pragma unroll
                 for (int lp = 0; lp < STEP_TILES; lp++) tma_load_2d(dst + lp * B_TILE, &x_map, k0 + lp * KT, 0, bar);
@@ -274,18 +276,22 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
         if (lane == 0) {
             const uint64_t bdesc0 = make_desc(smem_u32(b_s) + (uint32_t)(iw * 32));
             const uint32_t tmem_acc = tmem_base + (uint32_t)(iw * NB);
+            const uint32_t ta0 = tmem_base + (uint32_t)(A_BASE + 8 * iw);
+            const uint32_t af0 = smem_u32(a_full), bf0 = smem_u32(b_full), sd0 = smem_u32(step_done);
             bool dead = false;
-            for (int i = 0; i < total_steps && !dead; i++) {
-                if (!mbar_wait(smem_u32(&a_full[i % SA]), (uint32_t)((i / SA) & 1), p.wait_limit) ||
-                    !mbar_wait(smem_u32(&b_full[i % SB]), (uint32_t)((i / SB) & 1), p.wait_limit) || *abort_flag) { dead = true; break; }
+            // counters instead of divisions by the (run-time) ring depth: this thread's loop is the pace of the CTA
+            uint32_t sbi = 0, sbp = 0;   // activation slot of step i and the parity of its barrier's phase
+            for (int i = 0; i < total_steps; i++) {
+                const uint32_t sa = (uint32_t)i & (SA - 1);
+                if (!mbar_wait(af0 + 8u * sa, ((uint32_t)i / SA) & 1u, p.wait_limit) || !mbar_wait(bf0 + 8u * sbi, sbp, p.wait_limit)) { dead = true; break; }
                 tc_fence_after();
+                const uint32_t ta = ta0 + sa * (uint32_t)A_COLS;
+                const uint64_t bd = bdesc0 + (uint64_t)((sbi * (uint32_t)B_SLOT) >> 4);
 #pragma unroll
-                for (int lp = 0; lp < STEP_TILES; lp++) {
-                    const uint32_t ta = tmem_base + (uint32_t)(A_BASE + (i % SA) * A_COLS + 32 * lp + 8 * iw);
-                    const uint64_t bd = bdesc0 + (uint64_t)((uint32_t)((i % SB) * B_SLOT + lp * B_TILE) >> 4);
-                    umma_f16_ta(tmem_acc, ta, bd, idesc, (i > 0 || lp > 0) ? 1u : 0u);
-                }
-                umma_commit(smem_u32(&step_done[i % NBAR]));
+                for (int lp = 0; lp < STEP_TILES; lp++)
+                    umma_f16_ta(tmem_acc, ta + (uint32_t)(32 * lp), bd + (uint64_t)((uint32_t)(lp * B_TILE) >> 4), idesc, (i > 0 || lp > 0) ? 1u : 0u);
+                umma_commit(sd0 + 8u * ((uint32_t)i & (NBAR - 1)));
+                if (++sbi == (uint32_t)SB) { sbi = 0; sbp ^= 1u; }
             }
             // drain: the last step's barrier completes when all four issuers' MMAs are done
             if (!dead && total_steps > 0) {
