@@ -337,23 +337,38 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
                 for (int j = 0; j < 16; j++) v[cc + j] = 0.f;
             }
         }
-        if (p.ks > 1 || (p.geglu && lrow >= 64)) {   // partial tiles of a split, or the up half of a GeGLU tile
+        if (p.ks > 1 || p.geglu) {   // partial tiles of a split, or the two halves of a GeGLU tile
 #pragma unroll
             for (int j = 0; j < 32; j++) red[(c0 + j) * TILE_ROWS + lrow] = v[j];
-        } else if (!p.geglu && n0 + lrow < n_rows && !failed) {
+        } else if (n0 + lrow < n_rows && !failed) {
 #pragma unroll
             for (int j = 0; j < 32; j++)
                 if (c0 + j < p.m) out[(size_t)(c0 + j) * n_rows + n0 + lrow] = __float2half_rn(v[j]);
         }
     }
     if (p.ks == 1 && p.geglu) {
-        // gate rows (operand rows 0-63) meet their up rows (64-127) through shared memory
+        // Gate rows (operand rows 0-63) meet their up rows (64-127) through shared memory.  All eight warps share the
+        // activation: a thread takes two neighbouring output rows of eight batch columns, so a warp stores 128
+        // contiguous bytes per column.
         __syncthreads();
-        if (warp < NDQ && lrow < 64 && n0 + lrow < n_rows && !failed) {
+        if (warp < NDQ && !failed) {
+            const int r2 = 2 * lane, cg = 8 * warp;
+            const bool pair_ok = n0 + r2 + 1 < n_rows && ((n_rows | n0) & 1) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0;
 #pragma unroll
-            for (int j = 0; j < 32; j++)
-                if (c0 + j < p.m)
-                    out[(size_t)(c0 + j) * n_rows + n0 + lrow] = __float2half_rn(geglu_f(v[j], red[(c0 + j) * TILE_ROWS + 64 + lrow]));
+            for (int j = 0; j < 8; j++) {
+                const int col = cg + j;
+                if (col >= p.m) break;
+                const float2 gt = *reinterpret_cast<const float2 *>(red + col * TILE_ROWS + r2);
+                const float2 up = *reinterpret_cast<const float2 *>(red + col * TILE_ROWS + 64 + r2);
+                const float o0 = geglu_f(gt.x, up.x), o1 = geglu_f(gt.y, up.y);
+                __half *dst = out + (size_t)col * n_rows + n0 + r2;
+                if (pair_ok) {
+                    *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(o0, o1);
+                } else {
+                    if (n0 + r2 < n_rows) dst[0] = __float2half_rn(o0);
+                    if (n0 + r2 + 1 < n_rows) dst[1] = __float2half_rn(o1);
+                }
+            }
         }
     }
     if (p.ks > 1) {
