@@ -286,12 +286,12 @@ def test_split_k_is_deterministic_and_lane_isolated(la, orc, ctx, tc_kernels):
     device_status_ok(kernels)
 
 
-@pytest.mark.parametrize("m,k,n", [(64, 256, 76000), (40, 384, 75800), (64, 1536, 20000), (33, 512, 19001), (9, 768, 40000)])
+@pytest.mark.parametrize("m,k,n", [(64, 256, 76000), (40, 384, 75800), (64, 1536, 20000), (33, 512, 19001), (9, 768, 40000), (130, 256, 19200)])
 def test_matmul_nt_q4_0_wide_matrix(la, orc, ctx, kernels, m, k, n):
     """Vocabulary-sized Q4_0 projections at decode batch sizes take a persistent kernel: with f32 out and K a multiple
     of 256 the tcgen05 one (128-row tiles, weights as two f16 operands in tensor memory), else the 512-row mma.sync one
-    (ragged last tile, several tiles per CTA, steps that outnumber the barrier ring); results must meet the
-    f32-weight oracle."""
+    (ragged last tile, several tiles per CTA, steps that outnumber the barrier ring; more than 64 batch rows go
+    through the tcgen05 kernel in chunks of 64); results must meet the f32-weight oracle."""
     raw = la.synth.q4_0_weights(n, k, 31)
     a = la.synth.normal_f16((m, k), 32)
     want32 = orc.matmul_nt(orc.Q4_0, a, raw, m, k, n)
