@@ -436,6 +436,7 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
     p.scale = scale;
     p.status = k->dev_status;
     p.qfrag = nullptr;
+    p.early_kv = (qfrag && use_mma && positions) ? 1u : 0u;   // only the decode step passes fragments: its positions are a step input
     if (qfrag && use_mma && fused && lc_qfrag_supported(hd, bits, n_q, n_kv)) {
         LC_REQUIRE(qfrag->bytes >= qn * 4, "%s: query fragment buffer too small", name);
         p.qfrag = (const uint4 *)qfrag->dptr;
@@ -683,6 +684,7 @@ extern "C" int lc_tq_attention_noalloc_into(lc_batch *b, const lc_buf *q, const 
     TqAttnParams p;
     p.out_f16 = nullptr;
     p.qfrag = nullptr;
+    p.early_kv = 0;
     p.cluster_merge = 0;
     p.rq = nullptr;
     p.q = (const __half *)q->dptr;

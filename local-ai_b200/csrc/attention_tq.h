@@ -32,6 +32,9 @@ struct TqAttnParams {
     // the kernel's B fragments by the launch that wrote q (lc_qkv_post_frag): uint4 {hi01, hi23, lo01, lo23} at
     // [(lane * n_q / 8 + head / 8) * 512 + s * 32 + 4 * (head % 8) + t] for dims 64 t + 4 s + 0..3.  NULL: build from q.
     const uint4 *qfrag;
+    // 1: `positions` and every key below the lanes' positions were complete before the predecessor kernels started, so
+    // the kernel may read them ahead of its dependency wait (tensor-core kernel, per-lane positions only).
+    uint32_t early_kv;
 };
 
 // Tensor-core variant for tq2 / head_dim 256 (attention_tq_mma.cu). Same grid and partial layout as the

@@ -182,36 +182,12 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
 #pragma unroll 8
     for (int e = threadIdx.x; e < 256 * LUT_COPIES; e += NT) lut[e] = ent_s[e / LUT_COPIES];
 
-    lc_pdl_wait();
-    // ---- after the wait: the query, the positions and the first tiles of codes; their loads leave first ----
-    const size_t q_row = ((size_t)lane_idx * p.n_q + qh0 + warp) * HD + 8 * lane;   // warp w owns head w
-    uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
-    float4 q_s0 = make_float4(0.f, 0.f, 0.f, 0.f), q_s1 = q_s0;
-    // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15.
-    // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
-    // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
-    uint32_t bq[16][2], bql[16][2];
-    const bool have_frag = p.qfrag != nullptr;   // the launch that wrote q left the fragments ready (group % 8 == 0)
-    if (have_frag) {
-        const uint4 *src = p.qfrag + ((size_t)lane_idx * (p.n_q >> 3) + (qh0 >> 3)) * 512 + lane;
-#pragma unroll
-        for (int s = 0; s < 16; s++) {
-            const uint4 v = src[s * 32];
-            bq[s][0] = v.x;
-            bq[s][1] = v.y;
-            bql[s][0] = v.z;
-            bql[s][1] = v.w;
-        }
-    } else if (warp < gvalid) {
-        if (p.fused_q) {
-            q_raw = *reinterpret_cast<const uint4 *>(p.q + q_row);
-            q_s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
-            q_s1 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane + 4);
-        } else {
-            q_s0 = *reinterpret_cast<const float4 *>(p.rq + q_row);
-            q_s1 = *reinterpret_cast<const float4 *>(p.rq + q_row + 4);
-        }
-    }
+    // Codes and norms of keys below the lanes' positions were written by earlier steps; only the key at the position
+    // itself comes from the predecessor.  A caller that also guarantees that `positions` was written before the
+    // predecessor kernels started (the decode step: it is an input of the step) sets early_kv, and the first tiles'
+    // copies are then in flight while the predecessor finishes.
+    const bool early = p.early_kv != 0u && p.positions != nullptr && p.row_positions == 0u;
+    if (!early) lc_pdl_wait();
     uint32_t pos, seq_len;
     if (p.positions) {
         pos = p.positions[lane_idx];
@@ -263,13 +239,60 @@ __global__ void __launch_bounds__(NT) tq2_attn_mma_kernel(const TqAttnParams p) 
     };
     const uint32_t t_first = k_begin + warp * KT;
     uint32_t t_issue = t_first;
+    // With early_kv the first tiles leave before the dependency wait, up to the tile that holds the key the
+    // predecessor is writing (position pos: the last key of the last split); that tile and the ones after it follow
+    // the wait.  Groups are committed in tile order either way.
+    int issued = 0;
+    if (early) {
+#pragma unroll
+        for (int i = 0; i < DEPTH - 1; i++) {
+            if (issued == i && !(t_issue <= pos && pos < t_issue + KT)) {
+                if (t_issue < k_end) issue(t_issue, i);
+                cp_async_commit();
+                t_issue += NW * KT;
+                issued = i + 1;
+            }
+        }
+        lc_pdl_wait();
+    }
 #pragma unroll
     for (int i = 0; i < DEPTH - 1; i++) {
-        if (t_issue < k_end) issue(t_issue, i);
-        cp_async_commit();
-        t_issue += NW * KT;
+        if (i >= issued) {
+            if (t_issue < k_end) issue(t_issue, i);
+            cp_async_commit();
+            t_issue += NW * KT;
+        }
     }
 
+    // ---- after the wait: the query ----
+    const size_t q_row = ((size_t)lane_idx * p.n_q + qh0 + warp) * HD + 8 * lane;   // warp w owns head w
+    uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
+    float4 q_s0 = make_float4(0.f, 0.f, 0.f, 0.f), q_s1 = q_s0;
+    // B fragments of the query: thread (g, t) holds head g, dims 64t + 4s + {0,1} and + {2,3}, s = 0..15.
+    // The query is the one operand f16 cannot hold well enough when logits are large (softmax scale 1.0):
+    // it is split into a high f16 part and the f16 of the remainder, and each k-step issues two MMAs.
+    uint32_t bq[16][2], bql[16][2];
+    const bool have_frag = p.qfrag != nullptr;   // the launch that wrote q left the fragments ready (group % 8 == 0)
+    if (have_frag) {
+        const uint4 *src = p.qfrag + ((size_t)lane_idx * (p.n_q >> 3) + (qh0 >> 3)) * 512 + lane;
+#pragma unroll
+        for (int s = 0; s < 16; s++) {
+            const uint4 v = src[s * 32];
+            bq[s][0] = v.x;
+            bq[s][1] = v.y;
+            bql[s][0] = v.z;
+            bql[s][1] = v.w;
+        }
+    } else if (warp < gvalid) {
+        if (p.fused_q) {
+            q_raw = *reinterpret_cast<const uint4 *>(p.q + q_row);
+            q_s0 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane);
+            q_s1 = *reinterpret_cast<const float4 *>(p.signs + 8 * lane + 4);
+        } else {
+            q_s0 = *reinterpret_cast<const float4 *>(p.rq + q_row);
+            q_s1 = *reinterpret_cast<const float4 *>(p.rq + q_row + 4);
+        }
+    }
     // ---- prologue 2 (independent of gamma): rotated, scaled query; warp w owns head w ----
     if (!have_frag) {
         const int h = warp;   // NW == G
