@@ -305,7 +305,7 @@ class TqAttention:
         achieved = self.alg_bytes_per_launch / (us * 1e-6) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_kind": peak_kind,
-                "kernel": "tq2_attn_mma_kernel + tq_attn_merge_kernel (one fused call)", "us_per_launch": us,
+                "kernel": "tq2_attn_mma_kernel (splits merged in the kernel through a thread-block cluster)", "us_per_launch": us,
                 "algorithmic_bytes_per_launch": self.alg_bytes_per_launch, "frac_of_nominal_8tbs": achieved / 8000.0}
 
     def cpu_sample(self, orc, threads: int):

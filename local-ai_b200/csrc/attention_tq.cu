@@ -394,12 +394,13 @@ int tq_attention(const char *name, lc_kernels *k, lc_batch *b, const lc_buf *rq_
         }
     }
     const bool direct = (n_splits == 1 && !fused);
-    // The tensor-core kernel can merge up to 8 splits itself (one thread-block cluster per lane and kv head, exchange
-    // through distributed shared memory, inverse rotation in the kernel).  Alone that is faster than split + merge
-    // launches (57 vs 59 us at 8193 keys x 64 lanes, 12.4 vs 14.6 us for a 512-key window), inside the decode step it
-    // is slower (3.48 vs 3.36 ms per step: the small merge launch is where the following projection's weight
-    // prefetch overlaps), so it is opt-in: LOCAL_CUDA_ATTN_CLUSTER=1.
-    static const bool cluster_allowed = []() { const char *e = getenv("LOCAL_CUDA_ATTN_CLUSTER"); return e && e[0] == '1'; }();
+    // The tensor-core kernel merges up to 8 splits itself (one thread-block cluster per lane and kv head, exchange
+    // through distributed shared memory, inverse rotation in the kernel): one launch instead of split + merge, the same
+    // arithmetic in the same order, bit-identical output.  Alone 57 vs 59 us at 8193 keys x 64 lanes, 12.4 vs 14.6 us
+    // for a 512-key window; inside the decode step 2.314 vs 2.331 ms.  (Before the step's other kernels did their
+    // weight prefetch ahead of their dependency wait it was the slower form in situ, 3.48 vs 3.36 ms.)
+    // LOCAL_CUDA_ATTN_CLUSTER=0 selects the two-launch form.
+    static const bool cluster_allowed = []() { const char *e = getenv("LOCAL_CUDA_ATTN_CLUSTER"); return !(e && e[0] == '0'); }();
     const bool cluster_merge = use_mma && cluster_allowed && n_splits <= 8 &&
                                lc_aligned(out->dptr, 16) && (!fused || lc_aligned(signs->dptr, 16));
 

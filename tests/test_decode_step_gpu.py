@@ -228,9 +228,9 @@ def test_step_at_the_benchmark_kernel_routes(la, orc, ctx, kernels, bench_route_
     nt = la.CudaBuffer.empty(ctx, lanes * 4)
     b = la.CommandBatch.new(ctx)
     gm.decode_batch_step_into(b, tb, pb, lanes, True, nt)
-    # embed, first norm, 2 x (Q/K/V, q/k/v post, attention split + merge, O, norm pair, GeGLU, down, norm pair),
-    # vocabulary, argmax: the grouped and fused forms were taken
-    assert b.dispatch_count() == 2 + 2 * 9 + 2
+    # embed, first norm, 2 x (Q/K/V, q/k/v post, attention with its in-kernel merge, O, norm pair, GeGLU, down,
+    # norm pair), vocabulary, argmax: the grouped and fused forms were taken
+    assert b.dispatch_count() == 2 + 2 * 8 + 2
     b.commit_and_wait()
     got = gm.logits_buffer().as_slice(np.float32, lanes * cfg.vocab).reshape(lanes, cfg.vocab)
     got_h = gm.hidden_buffer().as_slice(np.float16, lanes * cfg.hidden).reshape(lanes, cfg.hidden)
