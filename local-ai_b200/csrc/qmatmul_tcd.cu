@@ -510,12 +510,18 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     const int rows = TILE_ROWS;
     // One wave: split K over a cluster of at most 8 CTAs while the CTA count stays within about 7/8 of the SM count
     // (a cluster needs all its SMs in one GPC, so the last few SMs cannot always be used; a launch that does not fit
-    // runs a second wave and takes twice as long), and no CTA takes more than MAX_STEPS steps (six blocks per row).
+    // runs a second wave and takes twice as long), no CTA takes more than MAX_STEPS steps (six blocks per row), and,
+    // where K allows, every CTA keeps two steps: both weight slots are dequantized before the dependency wait, so a
+    // second step costs only its MMAs, while every further split adds a partial tile to the exchange that follows
+    // (Q/K/V 3 x 2 steps instead of 6 x 1, O 4 x 2 instead of 8 x 1: step 2.328 -> 2.281 ms; three steps per CTA
+    // 2.333 ms, four 2.350 ms; LOCAL_CUDA_TCD_MIN_BPS overrides).
     static const int ks_cap = []() { const char *e = getenv("LOCAL_CUDA_TCD_KS"); const int v = e ? atoi(e) : 0; return v > 0 ? v : MAX_KS; }();
     int ks = (k->ctx->sm_count * 7 / 8) / tiles;
     if (ks > ks_cap) ks = ks_cap;
     if (ks > MAX_KS) ks = MAX_KS;
     if (ks > p.nb) ks = p.nb;
+    static const int min_bps = []() { const char *e = getenv("LOCAL_CUDA_TCD_MIN_BPS"); const int v = e ? atoi(e) : 2; return v >= 1 && v <= MAX_STEPS ? v : 2; }();
+    if (ks > (p.nb + min_bps - 1) / min_bps) ks = (p.nb + min_bps - 1) / min_bps;
     if (ks < 1) ks = 1;
     int bps = (p.nb + ks - 1) / ks;
     if (bps > MAX_STEPS) bps = MAX_STEPS;
