@@ -210,9 +210,8 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
             const uint32_t p01 = (uint32_t)__half_as_ushort(__hneg(d));
             const uint32_t p23 = (uint32_t)__half_as_ushort(d) | ((uint32_t)__half_as_ushort(__hadd(d, d)) << 16);
             const uint32_t lut_lo = __byte_perm(p01, p23, 0x6420), lut_hi = __byte_perm(p01, p23, 0x7531);
-            // All 128 weights of the step are converted into registers first: only the stores into the weight slot
-            // have to wait for the MMAs that read the slot SA steps ago.
-            uint32_t v[2][4][8];
+            // The first half block is converted before the wait for the slot (only the stores depend on the MMAs that
+            // read the slot SA steps ago); its stores then run beside the conversion of the second half.
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 // 16 code bytes, 2-byte aligned: five aligned words, funnel-shifted into place
@@ -222,28 +221,28 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
                                         __funnelshift_r(w3, w4, sh)};
                 // element k = 128 h + 32 l + j of the block is bit pair l of code byte 32 h + j: for a given l this
                 // thread's bytes j = 16 bq .. + 15 are 16 consecutive k, i.e. the eight columns from (128 h + 32 l + 16 bq) / 2
+                uint32_t v[4][8];
 #pragma unroll
                 for (int l = 0; l < 4; l++) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const uint32_t sel = ((cw[q] >> (2 * l)) & 0x03030303u) * 0x11u + 0x40404040u;
-                        v[h][l][2 * q] = __byte_perm(lut_lo, lut_hi, sel);
-                        v[h][l][2 * q + 1] = __byte_perm(lut_lo, lut_hi, sel >> 16);
+                        v[l][2 * q] = __byte_perm(lut_lo, lut_hi, sel);
+                        v[l][2 * q + 1] = __byte_perm(lut_lo, lut_hi, sel >> 16);
                     }
                 }
-            }
-            if (i >= SA) {   // the MMAs that read this slot SA steps ago have completed
-                uint32_t ok = 1;
-                const int u = i - SA;
-                if (lane == 0) ok = mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) ? 1u : 0u;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
-                tc_fence_after();
-            }
+                if (h == 0 && i >= SA) {   // the MMAs that read this slot SA steps ago have completed
+                    uint32_t ok = 1;
+                    const int u = i - SA;
+                    if (lane == 0) ok = mbar_wait(smem_u32(&step_done[u % NBAR]), (uint32_t)((u / NBAR) & 1), p.wait_limit) ? 1u : 0u;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok || *abort_flag) { *abort_flag = 1; dead = true; break; }
+                    tc_fence_after();
+                }
 #pragma unroll
-            for (int h = 0; h < 2; h++)
-#pragma unroll
-                for (int l = 0; l < 4; l++) tmem_st8(ta0 + (uint32_t)(s * A_COLS + 64 * h + 16 * l + 8 * bq), v[h][l]);
+                for (int l = 0; l < 4; l++) tmem_st8(ta0 + (uint32_t)(s * A_COLS + 64 * h + 16 * l + 8 * bq), v[l]);
+            }
+            if (dead) break;
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
