@@ -446,13 +446,12 @@ class DecodeStep:
         self.h2d, self.d2h = 2 * self.lanes * 4, self.lanes * 4
 
     def step_e2e(self):
-        # host tokens + positions in, greedy tokens out, fed back as the next step's input
+        # host tokens + positions in, greedy tokens out, fed back as the next step's input.  The copies and the step's
+        # graph go to the context's stream in order; the host waits once, for the tokens.
         b = self.la.CommandBatch.new(self.ctx)
         b.upload(self.tokens, 0, self.h_in.ptr, self.lanes * 4)
         b.upload(self.positions, 0, self.h_in.ptr + self.lanes * 4, self.lanes * 4)
-        b.commit_and_wait()
         self.graph.launch()
-        b = self.la.CommandBatch.new(self.ctx)
         b.download(self.next_tokens, 0, self.h_out.ptr, self.lanes * 4)
         b.commit_and_wait()
         self.e2e_steps += 1
