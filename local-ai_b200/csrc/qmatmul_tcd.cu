@@ -86,6 +86,7 @@ struct TcdParams {
     int geglu;           // 1: operand rows 0-63 are gate rows, 64-127 the same rows of the up matrix; out[0] = gelu(gate) * up
     int *status;
     uint32_t wait_limit;
+    uint32_t extra_arrivals;   // 0; 1 in the expiry self-test: the "weights ready" barriers then expect an arrival nobody makes
 };
 
 // gelu_tanh(gate) * up with gate and up rounded to f16 first, as the separate projections would store them, and the
@@ -151,7 +152,7 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
     }
     if (tid == 0) {
         mbar_init(smem_u32(raw_full), ROWS);
-        for (int i = 0; i < MAX_STEPS; i++) mbar_init(smem_u32(&a_full[i]), NDQ);
+        for (int i = 0; i < MAX_STEPS; i++) mbar_init(smem_u32(&a_full[i]), NDQ + p.extra_arrivals);
         for (int i = 0; i < MAX_STEPS; i++) mbar_init(smem_u32(&b_full[i]), 1);
         for (int i = 0; i < NBAR; i++) mbar_init(smem_u32(&step_done[i]), NISS);
         *abort_flag = 0;
@@ -411,7 +412,7 @@ qgemm_tcd_kernel(const __grid_constant__ TcdParams p, const __grid_constant__ CU
         }
         cluster_sync();   // no CTA leaves while a peer may still read its shared memory
     }
-    if (failed && tid == 0) atomicExch(p.status, LC_DEV_STATUS_WAIT_EXPIRED_TCD);
+    if (failed) tc_wait_expired(p.status, LC_DEV_STATUS_WAIT_EXPIRED_TCD, tid);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -531,7 +532,8 @@ int lc_qgemm_tcd_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, int ng,
     p.raw_rs = ((bps * BB + 15 + 15) / 16) * 16;
     if ((p.raw_rs / 16) % 2 == 0) p.raw_rs += 16;
     p.status = k->dev_status;
-    p.wait_limit = WAIT_LIMIT;
+    p.wait_limit = k->test_wait_expiry ? 4096u : WAIT_LIMIT;
+    p.extra_arrivals = k->test_wait_expiry ? 1u : 0u;
     // Shared memory: the raw rows and up to three activation slots of one step each (the weight operand lives in
     // tensor memory); the first slot doubles as the staging of the split-K / GeGLU exchange (32 KB, exactly one slot).
     const int total = bps;

@@ -58,6 +58,7 @@ struct TcvParams {
     int n, m, K, tiles;
     int *status;
     uint32_t wait_limit;
+    uint32_t extra_arrivals;   // 0; 1 in the expiry self-test: the readiness barriers then expect an arrival nobody makes
 };
 
 // bounded wait by lane 0, result shared with the warp
@@ -111,7 +112,7 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
         // one barrier per step for both operands, so the issuers test one: eight dequantizing warps arrive, and the
         // activation loader arrives with the byte count of its boxes.  The ring has the depth of the activation ring,
         // the deeper of the two, so no arrival for a later step can reach a barrier before its current phase is over.
-        for (int i = 0; i < V_SB; i++) mbar_init(smem_u32(&ab_full[i]), V_NDQ_STEP + 1);
+        for (int i = 0; i < V_SB; i++) mbar_init(smem_u32(&ab_full[i]), V_NDQ_STEP + 1 + p.extra_arrivals);
         for (int i = 0; i < V_NBAR; i++) mbar_init(smem_u32(&step_done[i]), V_NISS);
         mbar_init(smem_u32(acc_empty), V_NEPI);
         mbar_init(smem_u32(acc_full), V_NISS);
@@ -320,7 +321,7 @@ qgemm_tcv_kernel(const __grid_constant__ TcvParams p, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (*abort_flag != 0 && tid == 0) atomicExch(p.status, LC_DEV_STATUS_WAIT_EXPIRED_TCD);
+    if (*abort_flag != 0) tc_wait_expired(p.status, LC_DEV_STATUS_WAIT_EXPIRED_TCD, tid);
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)V_TMEM_COLS) : "memory");
     }
@@ -384,7 +385,8 @@ int lc_qgemm_tcv_launch(lc_kernels *k, lc_batch *b, const lc_buf *input, const l
     p.K = (int)kk;
     p.tiles = (int)((n + V_ROWS - 1) / V_ROWS);
     p.status = k->dev_status;
-    p.wait_limit = V_WAIT_LIMIT;
+    p.wait_limit = k->test_wait_expiry ? 4096u : V_WAIT_LIMIT;
+    p.extra_arrivals = k->test_wait_expiry ? 1u : 0u;
     static lc_smem_optin optin;
     LC_CUDA_TRY(lc_ensure_smem(qgemm_tcv_kernel, optin, b->ctx, smem));
     const int grid = p.tiles < k->ctx->sm_count ? p.tiles : k->ctx->sm_count;

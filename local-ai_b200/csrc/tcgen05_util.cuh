@@ -116,4 +116,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t addr, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(addr), "r"(bytes) : "memory");
 }
 
+// The failure path of the tcgen05 kernels, kept out of line: a bounded wait ran out.  The CTA gives the copies it
+// still has in flight time to land before its shared memory is released, then raises the status word.
+__device__ __noinline__ void tc_wait_expired(int *status, int code, int tid) {
+    for (int i = 0; i < 64; i++) __nanosleep(1000);
+    if (tid == 0) atomicExch(status, code);
+}
+
 }  // namespace

@@ -256,6 +256,34 @@ def test_expired_barrier_wait_reports_timeout(la, orc, ctx, monkeypatch):
     rel_close(got, orc.matmul_nt(orc.TQ2_0, a, raw, m, k, n), TC_TOL_TQ2, "after an expired wait")
 
 
+@pytest.mark.parametrize("which", ["decode_matmul", "vocabulary"])
+def test_expired_wait_in_the_decode_kernels_reports_timeout(la, orc, ctx, monkeypatch, which):
+    """The same self-test for the two tcgen05 kernels of the decode step: with LOCAL_CUDA_TEST_WAIT_EXPIRY=1 their
+    readiness barriers expect an arrival nobody makes and every wait has a short limit.  The launch must return, the
+    status word must read Timeout, and a regular kernels object must work afterwards on the same context."""
+    import ctypes as C
+    if which == "decode_matmul":
+        m, k, n, fmt, entry, f32 = 64, 1536, 512, orc.TQ2_0, "matmul_nt_tq2_0_into", False
+        raw = la.synth.tq2_0_weights(n, k, 83)
+    else:
+        m, k, n, fmt, entry, f32 = 64, 256, 19200, orc.Q4_0, "matmul_nt_q4_0_f32out_into", True
+        raw = la.synth.q4_0_weights(n, k, 83)
+    a = la.synth.normal_f16((m, k), 84)
+    monkeypatch.setenv("LOCAL_CUDA_TEST_WAIT_EXPIRY", "1")
+    k2 = la.Kernels.new(ctx)
+    monkeypatch.delenv("LOCAL_CUDA_TEST_WAIT_EXPIRY")
+    run_matmul(la, ctx, k2, entry, a, raw, m, k, n, f32out=f32)   # returns: no wait is endless
+    st = C.c_int(0)
+    with pytest.raises(la.Error) as ei:
+        k2.kernels_device_status(C.addressof(st))
+    assert ei.value.kind == "Timeout" and st.value != 0
+    k2.close()
+    k3 = la.Kernels.new(ctx)
+    got = run_matmul(la, ctx, k3, entry, a, raw, m, k, n, f32out=f32)
+    k3.close()
+    rel_close(got, orc.matmul_nt(fmt, a, raw, m, k, n), TC_TOL_TQ2 if fmt == orc.TQ2_0 else 2e-4, "after an expired wait")
+
+
 def test_tensor_core_and_cuda_core_paths_agree(la, orc, ctx, kernels, monkeypatch):
     """LOCAL_AI_MMA=0 forces the CUDA-core path (kernels.rs:6290-6298); both must give the same TQ2_0 result
     up to summation order."""
