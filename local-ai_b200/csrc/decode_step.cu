@@ -260,7 +260,9 @@ static int run_layers(lc_model *m, lc_kernels *k, lc_batch *b, const lc_buf *pos
     lc_buf gate = view(m->gate, (size_t)lane0 * I * 2), up = view(m->up, (size_t)lane0 * I * 2);
     lc_buf ffn = view(m->ffn, (size_t)lane0 * H * 2);
     lc_buf qfrag_v = m->qfrag ? view(m->qfrag, (size_t)lane0 * qd * 4) : lc_buf();
-    lc_buf *qf = m->qfrag ? &qfrag_v : nullptr;
+    // Worth it while the attention launch is a wave or two (2.34 vs 2.39 ms at 64 lanes); at 512 lanes the KV-write
+    // launch's extra transform costs more than the attention prologue saves (11.90 vs 11.85 ms).
+    lc_buf *qf = (m->qfrag && n <= 128) ? &qfrag_v : nullptr;
     lc_buf *x = &xa, *xn = &xb;
     const size_t nl = m->layers.size();
     int st;
